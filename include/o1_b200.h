@@ -1,0 +1,356 @@
+/*
+ * o1_b200.h -- C ABI of libo1b200.so: the HiDream-O1 denoising hot path of
+ * o1.c (decoder blocks, full forward, flow-matching scheduler / CFG update,
+ * load-time LoRA merge) re-implemented for NVIDIA B200 (sm_100a).
+ *
+ * Three groups of entry points:
+ *   1. hd_*  primitive level: same names, argument order and error behaviour as
+ *      o1.c's src/cuda/hd_cuda.h:34-198 and src/cuda/gemm.h:35-68 (void
+ *      functions on device pointers, errors through hd_cuda_last_error()).
+ *   2. hd_*  model level: hd_decoder_block / hd_forward / hd_sdpa_* /
+ *      hd_lora_merge_gpu with the signatures of src/model/block.h:26-98,
+ *      src/model/forward.h:40-181, include/hd_cudnn_sdpa.h:30-94 and
+ *      include/hd_lora.h:32-79, returning hd_status (include/hidream.h:24-35).
+ *   3. o1_*  explicit entry points added by this library (stream selection,
+ *      fused kernels, the CFG denoise step, seeded initialisers, multi-GPU).
+ *
+ * All pointers are CUDA device pointers unless a name ends in _host.  No
+ * entry point takes or returns a PyTorch type.  Work is enqueued on the
+ * library's current stream (o1_set_stream; default: the legacy default
+ * stream, as in o1.c).  The library is not re-entrant: one thread at a time,
+ * as o1.c's engine (src/server/o1_server.c:926-940 guarantees this).
+ */
+#ifndef O1_B200_H
+#define O1_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------ status */
+/* include/hidream.h:24-35 */
+typedef enum {
+    HD_OK = 0,
+    HD_ERR_IO = 1,
+    HD_ERR_PARSE = 2,
+    HD_ERR_PROFILE = 3,
+    HD_ERR_MANIFEST = 4,
+    HD_ERR_MISMATCH = 5,
+    HD_ERR_MISSING = 6,
+    HD_ERR_OOM = 7,
+    HD_ERR_RUNTIME = 8,
+    HD_ERR_UNSUPPORTED = 9
+} hd_status;
+
+/* include/hidream.h:37-40 (model-level message buffer) */
+const char *hd_last_error(void);
+void hd_set_error(const char *fmt, ...);
+/* src/cuda/hd_cuda.h:46-47, src/cuda/cuda_internal.h:16 (primitive-level buffer) */
+const char *hd_cuda_last_error(void);
+void hd_cuda_clear_error(void);
+char *hd_cuda_errbuf(void);
+
+/* --------------------------------------------------- 1. primitive level */
+/* src/cuda/hd_cuda.h:30-41 -- host bf16 helpers (RNE, no NaN special case) */
+float hd_bf16_to_f32(uint16_t b);
+uint16_t hd_f32_to_bf16(float f);
+void hd_bf16_buf_to_f32(const void *src, float *dst, size_t n);
+void hd_f32_buf_to_bf16(const float *src, void *dst, size_t n);
+
+/* src/cuda/hd_cuda.h:58-59 */
+void hd_rmsnorm(const void *x_dev, const void *w_dev, void *y_dev, int rows, int cols, float eps);
+/* src/cuda/hd_cuda.h:62-68 */
+void hd_silu(const void *x_dev, void *y_dev, size_t n);
+void hd_swiglu(const void *gate_dev, const void *up_dev, void *y_dev, size_t n);
+void hd_residual_add(const void *x_dev, const void *a_dev, void *y_dev, size_t n);
+/* src/cuda/hd_cuda.h:76-77, src/cuda/gemm.h:47-58.  y = x W^T (+bias); only
+ * transpose_w == 1 is supported, as in the reference. */
+void hd_linear(const void *x_dev, const void *w_dev, const void *bias_dev, void *y_dev, int M,
+               int N, int K, int transpose_w);
+void hd_linear_reference(const void *x_dev, const void *w_dev, const void *bias_dev, void *y_dev,
+                         int M, int N, int K, int transpose_w);
+/* src/cuda/hd_cuda.h:83 */
+void hd_timestep_embed(const float *t_dev, float *y_dev, int N, int dim);
+/* src/cuda/hd_cuda.h:90-93 */
+void hd_mrope_cos_sin(const float *pos_dev, int bs, int seq, const int64_t *section_dev,
+                      int n_section, int head_dim, float theta, float attention_scaling,
+                      int interleaved, float *cos_dev, float *sin_dev);
+/* src/cuda/hd_cuda.h:99-111 */
+void hd_apply_rotary(const void *x_dev, const float *cos_dev, const float *sin_dev, void *y_dev,
+                     int heads, int seq, int dim);
+void hd_apply_rotary_f32(const void *x_dev, const float *cos_dev, const float *sin_dev,
+                         void *y_dev, int heads, int seq, int dim);
+/* src/cuda/hd_cuda.h:118-122.  q [heads,seq,dim], k/v [kv_heads,seq,dim],
+ * mask [seq,seq] bf16 additive (must be prefix-causal, see hd_sdpa_execute),
+ * out [seq,heads,dim].  scores_dev / probs_dev are accepted and left
+ * untouched: this implementation never materialises S x S tensors. */
+void hd_attention_eager(const void *q_dev, const void *k_dev, const void *v_dev,
+                        const void *mask_dev, void *scores_dev, void *probs_dev, void *out_dev,
+                        int heads, int kv_heads, int seq, int dim, float scaling);
+/* src/cuda/hd_cuda.h:128-129 */
+void hd_head_split(const void *in_dev, void *out_dev, int seq, int heads, int dim);
+void hd_head_merge(const void *in_dev, void *out_dev, int seq, int heads, int dim);
+/* src/cuda/hd_cuda.h:136-146 */
+void hd_gather_rows(const void *table_dev, const void *idx_dev, void *out_dev, int M, int cols,
+                    int64_t nrows);
+void hd_apply_tms_condition(const void *idx_dev, const void *emb_dev, const void *t_emb_dev,
+                            void *out_dev, int M, int H, int64_t tms_id);
+/* src/cuda/hd_cuda.h:149-151 */
+void hd_scale_f32(const float *in_dev, float *out_dev, float s, int n);
+void hd_f32_convert_bf16(const float *in_dev, void *out_dev, int n);
+/* src/cuda/hd_cuda.h:158-175 -- scheduler pointwise kernels */
+void hd_sched_bf16_upcast(const void *in_dev, float *out_dev, int n);
+void hd_sched_denoised(const float *z_dev, const float *mo_dev, float sigma, float *denoised_dev,
+                       int n);
+void hd_sched_z_next(const float *noise_dev, const float *denoised_dev, float sigma_next,
+                     float s_noise, float *z_next_dev, int n);
+void hd_sched_vcond(const void *z_dev, const void *xp_dev, float sigma, float *mo_dev, int n);
+void hd_sched_flow_match_step(const void *z_dev, const float *mo_dev, float sigma,
+                              float sigma_next, void *z_next_dev, int n);
+/* src/cuda/hd_cuda.h:181-182 */
+void hd_sched_cfg_guided(const float *mo_cond, const float *mo_uncond, float g, float *mo_guided,
+                         int n);
+/* src/cuda/hd_cuda.h:188-198 -- FlowUniPC bh2 pointwise updates */
+void hd_unipc_convert(const float *sample_dev, const float *mo_dev, float sigma_cur,
+                      float *conv_dev, int n);
+void hd_unipc_correct(const float *last_dev, const float *mo0_dev, const float *mo_old_dev,
+                      const float *conv_dev, float sig_t, float sig_s0, float alpha_t,
+                      float h_phi_1, float B_h, float rhos_c0, float rhos_c1, float inv_rks0,
+                      int order_c, float *out_dev, int n);
+void hd_unipc_predict(const float *sample_dev, const float *mo0_dev, const float *mo_old_dev,
+                      float sig_t, float sig_s0, float alpha_t, float h_phi_1, float B_h,
+                      float rhos_p, float inv_rks0, int order_p, float *out_dev, int n);
+/* src/cuda/vision_kernels.h:46-51 -- the two vision kernels hd_forward calls */
+void hd_vision_masked_scatter(const void *dst, const uint8_t *mask, const void *src, void *out,
+                              int rows, int cols);
+void hd_vision_deepstack_inject(const void *in, const uint8_t *mask, const void *emb, void *out,
+                                int rows, int cols);
+
+/* src/cuda/gemm.h:23-68 -- runtime handle kept for source compatibility.  No
+ * library handles exist here; init returns a small tag object. */
+typedef struct hd_gemm_runtime hd_gemm_runtime;
+hd_gemm_runtime *hd_gemm_runtime_init(int device_id, size_t workspace_bytes);
+void hd_gemm_runtime_destroy(hd_gemm_runtime *rt);
+void *hd_gemm_workspace(hd_gemm_runtime *rt);
+size_t hd_gemm_workspace_bytes(hd_gemm_runtime *rt);
+void hd_gemm_set_backend(int use_production);      /* accepted, no effect */
+void hd_gemm_set_prod_backend(int backend);        /* accepted, no effect */
+
+/* ------------------------------------------------------ 2. model level */
+/* include/hd_cudnn_sdpa.h:30-94.  A plan only records (seq, heads, ar_len,
+ * scale): there is nothing to build.  q/k/v/out are head-major [H,S,128]
+ * as in the reference.  A plan made by hd_sdpa_create (no ar_len) takes
+ * ar_len from the mask passed to hd_sdpa_execute: the mask must be the
+ * prefix-causal one of src/runtime/sequence.c:120-142, anything else fails. */
+typedef struct hd_sdpa_plan hd_sdpa_plan;
+int hd_sdpa_create(hd_sdpa_plan **out, int batch, int q_heads, int kv_heads, int seq_q, int seq_kv,
+                   int head_dim, float scale);
+int hd_sdpa_create_split(hd_sdpa_plan **out, int batch, int q_heads, int kv_heads, int seq,
+                         int ar_len, int head_dim, float scale);
+int hd_sdpa_create_prod(hd_sdpa_plan **out, int batch, int q_heads, int kv_heads, int seq,
+                        int ar_len, int head_dim, float scale);
+int hd_sdpa_execute(hd_sdpa_plan *plan, const void *q, const void *k, const void *v,
+                    const void *mask, void *out, void *stream);
+int hd_sdpa_execute_split(hd_sdpa_plan *plan, const void *q, const void *k, const void *v,
+                          void *out, void *stream);
+int hd_sdpa_execute_split_pass(hd_sdpa_plan *plan, int which, const void *q, const void *k,
+                               const void *v, void *out, void *stream);
+void hd_sdpa_destroy(hd_sdpa_plan *plan);
+
+/* src/model/block.h:34-40 */
+typedef struct {
+    void *ln0;
+    void *attn_hidden;
+    void *attn_resid;
+    void *post_ln;
+    void *mlp_out;
+} hd_block_internals;
+
+/* src/model/block.h:48-62 -- all bf16, [out,in] row-major */
+typedef struct {
+    int layer_idx;
+    const void *q_proj;
+    const void *k_proj;
+    const void *v_proj;
+    const void *o_proj;
+    const void *input_ln;
+    const void *post_ln;
+    const void *gate_proj;
+    const void *up_proj;
+    const void *down_proj;
+    const void *q_norm;
+    const void *k_norm;
+} hd_block_binding;
+
+/* src/model/block.h:26-28.  Returns what THIS implementation needs, which is
+ * O(seq): no heads*seq*seq score buffers (src/model/block.c:106-131 has two). */
+int64_t hd_decoder_block_scratch_bytes(int64_t seq, int heads, int kv_heads, int hidden,
+                                       int ff_hidden, int head_dim);
+/* src/model/block.h:90-98.  mask_dev is only read when sdpa == NULL (to
+ * recover ar_len); sec_dev is accepted for signature compatibility (the
+ * section [24,20,20] is a compile-time constant of the path). */
+hd_status hd_decoder_block(const void *in_dev, const float *pos_dev, const void *mask_dev,
+                           const hd_block_binding *bw, const int64_t *sec_dev, void *scratch,
+                           int64_t scratch_bytes, hd_block_internals *ints, void *out_dev,
+                           int64_t seq, int heads, int kv_heads, int hidden, int ff_hidden,
+                           int head_dim, hd_sdpa_plan *sdpa);
+
+/* src/model/forward.h:40-59 */
+typedef struct {
+    const void *embed_tokens;
+    const void *te0_w;
+    const void *te0_b;
+    const void *te2_w;
+    const void *te2_b;
+    const void *xe1_w;
+    const void *xe2_w;
+    const void *xe2_b;
+    const void *fl_w;
+    const void *fl_b;
+    const void *fnorm_w;
+    int n_layers;
+    hd_block_binding *blocks;
+} hd_forward_binding;
+
+/* src/model/forward.h:66-93.  Only hidden_a (base of the caller's buffer),
+ * xe_ref / n_ref, block_scratch_bytes and sdpa are read. */
+typedef struct {
+    void *hidden_a;
+    void *hidden_b;
+    void *h_text;
+    void *norm_out;
+    void *head_out;
+    void *t_emb;
+    void *te_hidden;
+    void *freq;
+    void *freq_bf16;
+    void *t_scaled;
+    void *xe_stage;
+    void *xe_out;
+    void *xe_ref;
+    int n_ref;
+    void *block_scratch;
+    int64_t block_scratch_bytes;
+    hd_sdpa_plan *sdpa;
+} hd_forward_workspace;
+
+/* src/model/forward.h:96-107 */
+typedef struct {
+    void *after_embedding;
+    void *after_timestep_conditioning;
+    void *after_target_embedding;
+    void *after_block_0_input;
+    void *after_block_0;
+    void *after_block_mid;
+    void *after_block_last;
+    void *before_final_norm;
+    void *after_final_norm;
+    void *after_final_head;
+} hd_forward_diagnostics;
+
+/* src/model/forward.h:129-134 */
+typedef struct {
+    const void *image_embeds;
+    const void *deepstack[3];
+    const uint8_t *visual_mask;
+    int v_tokens;
+} hd_visual_cond;
+
+/* src/model/forward.h:122-124 */
+int64_t hd_forward_workspace_bytes(int64_t seq, int img_tokens, int heads, int kv_heads, int hidden,
+                                   int ff_hidden, int head_dim, int64_t *block_scratch_bytes);
+/* src/model/forward.h:152-166.  `stream`, when non-NULL, is a cudaStream_t the
+ * forward runs on (the reference ignores it); NULL = the library's current
+ * stream. */
+hd_status hd_forward(const hd_forward_binding *bw, hd_forward_workspace *ws,
+                     const int64_t *input_ids, int text_len, const float *pos_f32,
+                     const void *mask_dev, const void *vinputs, int img_tokens,
+                     const hd_visual_cond *visual, const float *timestep, const int64_t *sec_dev,
+                     int seq, int heads, int kv_heads, int hidden, int ff_hidden, int head_dim,
+                     int tms_token_id, hd_forward_diagnostics *diag, void *out_dev, void *stream);
+int hd_forward_num_layers(const hd_forward_binding *bw);
+/* src/model/forward.h:177-181 */
+int64_t hd_forward_ws_offset(const char *name, int64_t seq, int text_len, int img_tokens, int heads,
+                             int kv_heads, int hidden, int ff_hidden, int head_dim,
+                             int64_t *block_scratch_bytes);
+
+/* include/hd_lora.h:32-45 */
+typedef struct {
+    char lora_prefix[256];
+    char base_tensor[256];
+    uint32_t rank;
+    uint32_t in_dim;
+    uint32_t out_dim;
+    float alpha;
+    float multiplier;
+    void *down_dev; /* [rank, in_dim]  fp32 */
+    void *up_dev;   /* [out_dim, rank] fp32 */
+    void *base_dev; /* [out_dim, in_dim] bf16, merged in place */
+} hd_lora_entry;
+/* include/hd_lora.h:75-76.  W = bf16(f32(W) + multiplier*alpha/rank * up@down). */
+hd_status hd_lora_merge_gpu(hd_lora_entry *entries, size_t count, void *stream /* cudaStream_t */);
+const char *hd_lora_last_error(void);
+
+/* ------------------------------------------------ 3. added entry points */
+/* Stream every later call enqueues on (a cudaStream_t; NULL = legacy default). */
+void o1_set_stream(void *stream);
+void *o1_get_stream(void);
+/* Kernels whose bounded waits ran out record a code in a device word;
+ * this reads and clears it (synchronises the current stream). 0 = clean. */
+int o1_device_error(void);
+int o1_sm_count(void);
+/* Number of kernels this library launched since the last reset. */
+int64_t o1_launch_count(int reset);
+
+/* Tensor-core GEMM with a choice of fused epilogue and explicit row pitches.
+ * epi: 0 store, 1 +bias, 2 +residual, 3 SwiGLU (w = gate, w2 = up, N = ff),
+ * 4 LoRA read-modify-write.  force_bn: 0 auto, 128 or 256.  Returns 0 on success. */
+int o1_gemm(const void *x, int ldx, const void *w, const void *w2, void *y, int ldy, int M, int N,
+            int K, int epi, const void *bias, const void *resid, int ldr, float scale, int force_bn);
+/* Prefix-causal flash attention on seq-major operands: q [S, ldq], k [S, ldk],
+ * v [S, ldv], out [S, ldo]; head h at columns [128h, 128h+128). */
+int o1_flash_attention(const void *q, int ldq, const void *k, int ldk, const void *v, int ldv,
+                       void *out, int ldo, int S, int heads, int kv_heads, int ar_len, float scale);
+/* cos|sin table [S,128] fp32 for section [24,20,20], theta 5e6 (built once per forward). */
+int o1_mrope_table(const float *pos_dev, int seq, float theta, float *cs_dev);
+/* Per-head RMSNorm + rotary, in place on [S, ld] holding `heads` heads. */
+int o1_qk_norm_rope(void *x, int ld, int S, int heads, const void *w, const float *cs_dev, float eps);
+/* z' = bf16(z + (sigma_next-sigma) * ((1-g)*(z-xu)/sigma + g*(z-xc)/sigma)):
+ * hd_sched_vcond x2 + hd_sched_cfg_guided + hd_sched_flow_match_step in one pass. */
+int o1_sched_cfg_flow_step(const void *z, const void *xp_cond, const void *xp_uncond, float sigma,
+                           float sigma_next, float g, void *z_next, size_t n);
+/* Seeded counter-based N(mean, std) fill (integer hash, identical on host). */
+int o1_fill_normal_bf16(void *dst, size_t n, uint64_t seed, float mean, float std);
+int o1_fill_normal_f32(float *dst, size_t n, uint64_t seed, float mean, float std);
+float o1_hash_normal_host(uint64_t seed, uint64_t index);
+
+/* One CFG denoise step on device-resident state: x_c = forward(ids_cond),
+ * x_u = forward(ids_uncond), z' = cfg_flow_step(z, x_c, x_u).  Composition of
+ * src/runtime/generate.c:1314-1360 with the flow-match update of :900-905.
+ * timestep_dev holds t = 1 - sigma.  ws is used for both branches in turn;
+ * xp_scratch holds 2 * seq * 3072 bf16. */
+hd_status o1_denoise_step_cfg(const hd_forward_binding *bw, hd_forward_workspace *ws,
+                              const int64_t *ids_cond, const int64_t *ids_uncond, int text_len,
+                              const float *pos_f32, int ar_len, const void *z, int img_tokens,
+                              const float *timestep_dev, float sigma, float sigma_next,
+                              float guidance, void *xp_scratch, void *z_next, int heads,
+                              int kv_heads, int hidden, int ff_hidden, int head_dim,
+                              int tms_token_id);
+/* Same step with HOST latents: copies z_host -> device, runs the step, copies
+ * z_next back and synchronises.  z_dev / z_next_dev are caller-owned staging. */
+hd_status o1_denoise_step_cfg_host(const hd_forward_binding *bw, hd_forward_workspace *ws,
+                                   const int64_t *ids_cond, const int64_t *ids_uncond,
+                                   int text_len, const float *pos_f32, int ar_len,
+                                   const void *z_host, void *z_dev, int img_tokens, float sigma,
+                                   float sigma_next, float guidance, float *timestep_dev,
+                                   void *xp_scratch, void *z_next_dev, void *z_next_host,
+                                   int heads, int kv_heads, int hidden, int ff_hidden,
+                                   int head_dim, int tms_token_id);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* O1_B200_H */

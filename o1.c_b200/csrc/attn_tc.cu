@@ -1,0 +1,385 @@
+// Prefix-causal flash attention on the sm_100a tensor cores.  Replaces the
+// cuDNN SDPA graphs (o1.c src/cuda/hd_cudnn_sdpa.cu:114-441) and the eager
+// S x S path (src/cuda/attn.cu:22-174): scores are never written to HBM.
+//
+//   out[s, h, :] = softmax_t( q[s,h,:] . k[t,kh,:] / sqrt(128) + mask[s,t] ) v[t,kh,:]
+//   kh = h / (heads / kv_heads); mask: rows s < ar_len see keys t <= s,
+//   rows s >= ar_len see every key (o1.c src/runtime/sequence.c:120-142).
+//
+// One CTA = 128 query rows of one head.  Operands stay seq-major
+// ([S, heads*128]); head split / merge (attn.cu:180-218) disappear into the
+// TMA coordinates and the output addressing.
+//   warp 0     : TMA producer (Q once, then K/V tiles of 128 keys, 2 stages each)
+//   warp 1     : tcgen05.mma issuer.  S_j = Q K_j^T into TMEM (double buffered),
+//                O += P_j V_j with P from shared memory, V as an MN-major operand
+//   warps 2..5 : softmax, one thread per query row (TMEM lane == row): fp32
+//                scores -> running max / sum in the exp2 domain -> bf16 P tile
+//                written in the 128B-swizzled K-major layout the MMA reads.
+// O is only rescaled when the running max grows by more than 2^8 (the sum and
+// O then share the same stale max, so the final division is still exact).
+#include "common.cuh"
+#include "ptx.cuh"
+#include "kernels.h"
+
+namespace o1 {
+
+static constexpr int AQ = 128;      // query rows per CTA
+static constexpr int AKV = 128;     // keys per tile
+static constexpr int AD = 128;      // head dim
+static constexpr int TILE_BYTES = 128 * 128 * 2;   // 32 KB: two 64-column panels of 16 KB
+static constexpr int PANEL_BYTES = 128 * 64 * 2;
+static constexpr int KV_STAGES = 2;
+static constexpr int ATTN_THREADS = 192;
+// Q | K x2 | V x2 | P x2
+static constexpr int ATTN_SMEM = TILE_BYTES * (1 + 2 * KV_STAGES + 2) + 1024 + 256;
+
+struct AttnArgs {
+    uint16_t* out;
+    int ldo;
+    int S, heads, kv_heads, ar_len;
+    float scale_log2;   // scale * log2(e)
+    // head h of q sits at TMA coordinates (h*q_hc + d, h*q_hr + s); same for k/v with
+    // the kv head.  seq-major [S, H*128]: hc = 128, hr = 0; head-major [H,S,128]: hc = 0, hr = S.
+    int q_hc, q_hr, kv_hc, kv_hr;
+    long out_hoff;      // element offset of head h in the output: h * out_hoff
+    int* err;
+};
+
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t cvt_bf16x2(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+__global__ void __launch_bounds__(ATTN_THREADS, 1)
+flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                  const __grid_constant__ CUtensorMap tmV, const AttnArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                               ~(uintptr_t)1023);
+    uint8_t* q_s = smem;
+    uint8_t* k_s = q_s + TILE_BYTES;
+    uint8_t* v_s = k_s + KV_STAGES * TILE_BYTES;
+    uint8_t* p_s = v_s + KV_STAGES * TILE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + 2 * TILE_BYTES);
+    uint64_t* q_full = bars;                // 1
+    uint64_t* k_full = bars + 1;            // KV_STAGES
+    uint64_t* k_empty = k_full + KV_STAGES;
+    uint64_t* v_full = k_empty + KV_STAGES;
+    uint64_t* v_empty = v_full + KV_STAGES;
+    uint64_t* s_full = v_empty + KV_STAGES; // 2
+    uint64_t* p_ready = s_full + 2;         // 2
+    uint64_t* o_ready = p_ready + 2;        // 1
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_ready + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int q0 = blockIdx.x * AQ;
+    const int h = blockIdx.y;
+    const int kh = h / (a.heads / a.kv_heads);
+
+    // keys this query tile can see
+    int kv_end = a.S;
+    if (q0 + AQ - 1 < a.ar_len) kv_end = q0 + AQ;   // all rows causal: keys <= last row
+    if (kv_end > a.S) kv_end = a.S;
+    const int n_tiles = (kv_end + AKV - 1) / AKV;
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int s = 0; s < KV_STAGES; ++s) {
+            mbar_init(&k_full[s], 1);
+            mbar_init(&k_empty[s], 1);
+            mbar_init(&v_full[s], 1);
+            mbar_init(&v_empty[s], 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&s_full[s], 1);
+            mbar_init(&p_ready[s], 4);
+        }
+        mbar_init(o_ready, 1);
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_S = tmem_base;         // two score buffers: columns [0,128), [128,256)
+    const uint32_t tmem_O = tmem_base + 256;   // output accumulator: columns [256,384)
+
+    if (warp == 0) {
+        // -------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            tma_prefetch_desc(&tmQ);
+            tma_prefetch_desc(&tmK);
+            tma_prefetch_desc(&tmV);
+            mbar_expect_tx(q_full, TILE_BYTES);
+            tma_load_2d(q_s, &tmQ, q_full, h * a.q_hc, h * a.q_hr + q0);
+            tma_load_2d(q_s + PANEL_BYTES, &tmQ, q_full, h * a.q_hc + 64, h * a.q_hr + q0);
+            int st = 0;
+            uint32_t ph = 0;
+            for (int j = 0; j < n_tiles; ++j) {
+                const int kv0 = j * AKV;
+                if (!mbar_wait(&k_empty[st], ph ^ 1)) { atomicExch(a.err, 11); break; }
+                mbar_expect_tx(&k_full[st], TILE_BYTES);
+                tma_load_2d(k_s + st * TILE_BYTES, &tmK, &k_full[st], kh * a.kv_hc, kh * a.kv_hr + kv0);
+                tma_load_2d(k_s + st * TILE_BYTES + PANEL_BYTES, &tmK, &k_full[st], kh * a.kv_hc + 64, kh * a.kv_hr + kv0);
+                if (!mbar_wait(&v_empty[st], ph ^ 1)) { atomicExch(a.err, 12); break; }
+                mbar_expect_tx(&v_full[st], TILE_BYTES);
+                tma_load_2d(v_s + st * TILE_BYTES, &tmV, &v_full[st], kh * a.kv_hc, kh * a.kv_hr + kv0);
+                tma_load_2d(v_s + st * TILE_BYTES + PANEL_BYTES, &tmV, &v_full[st], kh * a.kv_hc + 64, kh * a.kv_hr + kv0);
+                if (++st == KV_STAGES) { st = 0; ph ^= 1; }
+            }
+        }
+    } else if (warp == 1) {
+        // -------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc_qk = umma_idesc_bf16(128, 128, 0, 0);
+            constexpr uint32_t idesc_pv = umma_idesc_bf16(128, 128, 0, 1);  // V is MN-major
+            const uint32_t q_addr = smem_u32(q_s);
+            bool ok = mbar_wait(q_full, 0);
+            if (!ok) atomicExch(a.err, 13);
+            auto issue_qk = [&](int j) -> bool {
+                const int st = j % KV_STAGES;
+                const uint32_t ph = (j / KV_STAGES) & 1;
+                if (!mbar_wait(&k_full[st], ph)) { atomicExch(a.err, 14); return false; }
+                tc_fence_after();
+                const uint32_t k_addr = smem_u32(k_s + st * TILE_BYTES);
+                const uint32_t d = tmem_S + (j & 1) * 128;
+#pragma unroll
+                for (int kk = 0; kk < AD / 16; ++kk) {
+                    const uint32_t off = (kk >> 2) * PANEL_BYTES + (kk & 3) * 32;
+                    umma_ss(d, umma_desc_sw128(q_addr + off, 16, 1024),
+                            umma_desc_sw128(k_addr + off, 16, 1024), idesc_qk, kk != 0);
+                }
+                umma_commit(&k_empty[st]);
+                umma_commit(&s_full[j & 1]);
+                return true;
+            };
+            if (ok) ok = issue_qk(0);
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                if (j + 1 < n_tiles) {
+                    // S buffer (j+1)&1 is free: the softmax of tile j-1 finished reading it
+                    // before it signalled p_ready(j-1), which PV(j-1) already waited on.
+                    ok = issue_qk(j + 1);
+                    if (!ok) break;
+                }
+                const int st = j % KV_STAGES;
+                const uint32_t ph = (j / KV_STAGES) & 1;
+                if (!mbar_wait(&v_full[st], ph)) { atomicExch(a.err, 15); ok = false; break; }
+                if (!mbar_wait(&p_ready[j & 1], (j >> 1) & 1)) { atomicExch(a.err, 16); ok = false; break; }
+                tc_fence_after();
+                const uint32_t p_addr = smem_u32(p_s + (j & 1) * TILE_BYTES);
+                const uint32_t v_addr = smem_u32(v_s + st * TILE_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < AKV / 16; ++kk) {
+                    const uint32_t p_off = (kk >> 2) * PANEL_BYTES + (kk & 3) * 32;
+                    const uint32_t v_off = kk * 16 * 128;  // 16 keys down, 128 B per key row
+                    umma_ss(tmem_O, umma_desc_sw128(p_addr + p_off, 16, 1024),
+                            umma_desc_sw128(v_addr + v_off, PANEL_BYTES, 1024), idesc_pv,
+                            (j | kk) != 0);
+                }
+                umma_commit(&v_empty[st]);
+                umma_commit(o_ready);
+            }
+        }
+    } else {
+        // -------------------------------------------------------- softmax + output
+        const int qd = warp & 3;                 // TMEM lane quadrant of this warp
+        const int row = qd * 32 + lane;          // row within the query tile
+        const int row_g = q0 + row;              // global query index
+        const uint32_t lane_off = (uint32_t)(qd * 32) << 16;
+        const bool tile_has_causal = q0 < a.ar_len;
+        float m_used = -INFINITY;                // max the stored P / l / O are relative to
+        float l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            const int kv0 = j * AKV;
+            if (!mbar_wait(&s_full[j & 1], (j >> 1) & 1)) { atomicExch(a.err, 17); ok = false; break; }
+            tc_fence_after();
+            uint32_t r[4][32];
+            const uint32_t t_s = tmem_S + (j & 1) * 128 + lane_off;
+            tmem_ld32(t_s + 0, r[0]);
+            tmem_ld32(t_s + 32, r[1]);
+            tmem_ld32(t_s + 64, r[2]);
+            tmem_ld32(t_s + 96, r[3]);
+            tmem_ld_wait();
+            const bool need_mask = (kv0 + AKV > a.S) || (tile_has_causal && kv0 + AKV - 1 > q0);
+            float mx = -INFINITY;
+            if (need_mask) {
+                const bool row_causal = row_g < a.ar_len;
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int key = kv0 + c * 32 + i;
+                        const bool allow = key < a.S && (!row_causal || key <= row_g);
+                        const float v = allow ? __uint_as_float(r[c][i]) : -INFINITY;
+                        r[c][i] = __float_as_uint(v);
+                        mx = fmaxf(mx, v);
+                    }
+            } else {
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[c][i]));
+            }
+            const float m_tile = mx * a.scale_log2;
+            const bool grow = (m_tile - m_used) > 8.0f;      // also true while m_used == -inf
+            if (__any_sync(0xffffffffu, grow)) {
+                float alpha = 1.0f;
+                if (grow) {
+                    alpha = ex2_approx(m_used - m_tile);         // 0 on the first tile
+                    m_used = m_tile;
+                    l *= alpha;
+                }
+                if (j > 0) {
+                    // O of tiles < j must be complete before it is rescaled
+                    if (!mbar_wait(o_ready, (j - 1) & 1)) { atomicExch(a.err, 18); ok = false; }
+                    tc_fence_after();
+#pragma unroll 1
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t o[32];
+                        tmem_ld32(tmem_O + lane_off + c * 32, o);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tmem_st32(tmem_O + lane_off + c * 32, o);
+                    }
+                    tmem_st_wait();
+                }
+            }
+            // P = exp2(s * scale_log2 - m_used), bf16, into the swizzled K-major tile
+            uint8_t* p_row = p_s + (j & 1) * TILE_BYTES + row * 128;
+            const float neg_m = -m_used;
+            float lsum = 0.f;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+#pragma unroll
+                for (int g8 = 0; g8 < 4; ++g8) {
+                    float p[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        p[i] = ex2_approx(fmaf(__uint_as_float(r[c][g8 * 8 + i]), a.scale_log2, neg_m));
+                        lsum += p[i];
+                    }
+                    uint4 pk;
+                    pk.x = cvt_bf16x2(p[0], p[1]);
+                    pk.y = cvt_bf16x2(p[2], p[3]);
+                    pk.z = cvt_bf16x2(p[4], p[5]);
+                    pk.w = cvt_bf16x2(p[6], p[7]);
+                    const int col = c * 32 + g8 * 8;          // key column of this 16-byte chunk
+                    const int panel = col >> 6;
+                    const int chunk = (col & 63) >> 3;
+                    *reinterpret_cast<uint4*>(p_row + panel * PANEL_BYTES +
+                                              ((chunk ^ (row & 7)) << 4)) = pk;
+                }
+            }
+            l += lsum;
+            fence_proxy_async_smem();   // generic-proxy smem writes -> visible to the MMA (async proxy)
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&p_ready[j & 1]);
+        }
+        // ---- output: O / l -> bf16 -> out[row_g, h*128 ..]
+        if (ok && n_tiles > 0) {
+            if (!mbar_wait(o_ready, (n_tiles - 1) & 1)) { atomicExch(a.err, 19); ok = false; }
+            tc_fence_after();
+        }
+        if (ok) {
+            const float inv_l = 1.0f / l;
+            uint16_t* dst = a.out + (size_t)row_g * a.ldo + (size_t)h * a.out_hoff;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t o[32];
+                tmem_ld32(tmem_O + lane_off + c * 32, o);
+                tmem_ld_wait();
+                if (row_g < a.S) {
+                    uint4* d4 = reinterpret_cast<uint4*>(dst + c * 32);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        uint4 pk;
+                        pk.x = cvt_bf16x2(__uint_as_float(o[i * 8 + 0]) * inv_l, __uint_as_float(o[i * 8 + 1]) * inv_l);
+                        pk.y = cvt_bf16x2(__uint_as_float(o[i * 8 + 2]) * inv_l, __uint_as_float(o[i * 8 + 3]) * inv_l);
+                        pk.z = cvt_bf16x2(__uint_as_float(o[i * 8 + 4]) * inv_l, __uint_as_float(o[i * 8 + 5]) * inv_l);
+                        pk.w = cvt_bf16x2(__uint_as_float(o[i * 8 + 6]) * inv_l, __uint_as_float(o[i * 8 + 7]) * inv_l);
+                        d4[i] = pk;
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
+static bool flash_attention_impl(const void* q, int ldq, const void* k, int ldk, const void* v,
+                                 int ldv, void* out, int ldo, int S, int heads, int kv_heads,
+                                 int ar_len, float scale, bool in_head_major, bool out_head_major,
+                                 cudaStream_t st) {
+    if (!q || !k || !v || !out || S <= 0 || heads <= 0 || kv_heads <= 0 || (heads % kv_heads) != 0) {
+        set_error("attention: bad args");
+        return false;
+    }
+    if ((ldo % 8) != 0 || (((uintptr_t)out) & 15)) { set_error("attention: output not 16-byte aligned"); return false; }
+    if (ar_len < 0) ar_len = 0;
+    if (ar_len > S) ar_len = S;
+    const CUtensorMap *tq, *tk, *tv;
+    if (in_head_major) {
+        tq = cached_tmap(q, (uint64_t)heads * S, AD, AD, 128);
+        tk = cached_tmap(k, (uint64_t)kv_heads * S, AD, AD, 128);
+        tv = cached_tmap(v, (uint64_t)kv_heads * S, AD, AD, 128);
+    } else {
+        tq = cached_tmap(q, S, (uint64_t)heads * AD, ldq, 128);
+        tk = cached_tmap(k, S, (uint64_t)kv_heads * AD, ldk, 128);
+        tv = cached_tmap(v, S, (uint64_t)kv_heads * AD, ldv, 128);
+    }
+    if (!tq || !tk || !tv) return false;
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(flash_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             ATTN_SMEM);
+        if (e != cudaSuccess) { set_error("attention: smem attribute: %s", cudaGetErrorString(e)); return false; }
+        attr_done = true;
+    }
+    AttnArgs a;
+    a.out = (uint16_t*)out; a.ldo = ldo;
+    a.S = S; a.heads = heads; a.kv_heads = kv_heads; a.ar_len = ar_len;
+    a.scale_log2 = scale * 1.4426950408889634f;
+    a.q_hc = in_head_major ? 0 : AD;  a.q_hr = in_head_major ? S : 0;
+    a.kv_hc = a.q_hc;                 a.kv_hr = a.q_hr;
+    a.out_hoff = out_head_major ? (long)S * AD : AD;
+    if (out_head_major) a.ldo = AD;
+    a.err = device_error_word();
+    dim3 grid((S + AQ - 1) / AQ, heads);
+    flash_attn_kernel<<<grid, ATTN_THREADS, ATTN_SMEM, st>>>(*tq, *tk, *tv, a);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { set_error("attention: launch: %s", cudaGetErrorString(e)); return false; }
+    return true;
+}
+
+bool flash_attention(const void* q, int ldq, const void* k, int ldk, const void* v, int ldv,
+                     void* out, int ldo, int S, int heads, int kv_heads, int ar_len, float scale,
+                     cudaStream_t st) {
+    return flash_attention_impl(q, ldq, k, ldk, v, ldv, out, ldo, S, heads, kv_heads, ar_len, scale,
+                                false, false, st);
+}
+// q [heads,S,128], k/v [kv_heads,S,128]; out head-major [heads,S,128] or seq-major [S, heads*128]
+bool flash_attention_hm(const void* q, const void* k, const void* v, void* out, int S, int heads,
+                        int kv_heads, int ar_len, float scale, bool out_head_major, cudaStream_t st) {
+    return flash_attention_impl(q, AD, k, AD, v, AD, out, heads * AD, S, heads, kv_heads, ar_len,
+                                scale, true, out_head_major, st);
+}
+
+}  // namespace o1

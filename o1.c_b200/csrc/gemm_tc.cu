@@ -1,0 +1,461 @@
+// Dense linear layer  Y[M,N] = X[M,K] * W[N,K]^T  (bf16 in, fp32 accumulate,
+// bf16 out) on the sm_100a tensor cores.  Replaces the cuBLASLt path of
+// o1.c's hd_linear (src/cuda/gemm.cu:413-461, 506-525).
+//
+// Structure: persistent CTAs (one per SM), 128 x BN x 64 tiles.
+//   warp 0      : TMA producer  (global -> 128B-swizzled shared, 4-6 stages)
+//   warp 1      : tcgen05.mma issuer, accumulators in TMEM, double buffered
+//   warps 2..5  : epilogue (tcgen05.ld -> registers -> fused op -> global)
+// The epilogue of tile i overlaps the main loop of tile i+1.
+//
+// Fused epilogues keep the reference's bf16 rounding points:
+//   BIAS   : bf16(bf16(acc) + bias)            (gemm.cu:226-236 second pass)
+//   RESID  : bf16(bf16(acc) + resid)           (residual.cu:14-23)
+//   SWIGLU : B tile = 128 gate rows + 128 up rows of the same columns;
+//            bf16(bf16(silu(bf16 g)) * bf16 u) (act.cu:22-34)
+//   LORA   : W = bf16(f32(W) + scale*acc)      (lora_merge.cu:26-33)
+#include "common.cuh"
+#include "ptx.cuh"
+#include "kernels.h"
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+namespace o1 {
+
+static constexpr int BM = 128;
+static constexpr int BK = 64;
+static constexpr int GEMM_THREADS = 192;
+
+struct GemmArgs {
+    int M, N, K;
+    uint16_t* out;
+    int ldo;
+    const uint16_t* bias;
+    const uint16_t* resid;
+    int ldr;
+    float scale;
+    int num_m, num_n, group_m;
+    int* err;
+};
+
+template <int BN>
+struct GemmCfg {
+    static constexpr int A_BYTES = BM * BK * 2;
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int STAGES = (BN == 256) ? 4 : 6;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+    static constexpr int TMEM_COLS = 2 * BN;
+};
+
+__device__ __forceinline__ void tile_coords(int tile, const GemmArgs& g, int& mb, int& nb) {
+    const int per_group = g.group_m * g.num_n;
+    const int grp = tile / per_group;
+    const int r = tile - grp * per_group;
+    const int m_first = grp * g.group_m;
+    int gm = g.num_m - m_first;
+    if (gm > g.group_m) gm = g.group_m;
+    mb = m_first + r % gm;
+    nb = r / gm;
+}
+
+__device__ __forceinline__ void store32_bf16(uint16_t* dst, const float (&v)[32]) {
+    uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        uint4 o;
+        o.x = pack_bf16x2(v[i * 8 + 0], v[i * 8 + 1]);
+        o.y = pack_bf16x2(v[i * 8 + 2], v[i * 8 + 3]);
+        o.z = pack_bf16x2(v[i * 8 + 4], v[i * 8 + 5]);
+        o.w = pack_bf16x2(v[i * 8 + 6], v[i * 8 + 7]);
+        d4[i] = o;
+    }
+}
+__device__ __forceinline__ void load32_bf16(const uint16_t* src, float (&v)[32]) {
+    const uint4* s4 = reinterpret_cast<const uint4*>(src);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        uint4 o = s4[i];
+        v[i * 8 + 0] = bf16lo(o.x); v[i * 8 + 1] = bf16hi(o.x);
+        v[i * 8 + 2] = bf16lo(o.y); v[i * 8 + 3] = bf16hi(o.y);
+        v[i * 8 + 4] = bf16lo(o.z); v[i * 8 + 5] = bf16hi(o.z);
+        v[i * 8 + 6] = bf16lo(o.w); v[i * 8 + 7] = bf16hi(o.w);
+    }
+}
+
+template <int EPI, int BN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const __grid_constant__ CUtensorMap tmB2, const GemmArgs g) {
+    using Cfg = GemmCfg<BN>;
+    constexpr int STAGES = Cfg::STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                               ~(uintptr_t)1023);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+    uint64_t* empty = full + STAGES;
+    uint64_t* tfull = empty + STAGES;
+    uint64_t* tempty = tfull + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&tfull[s], 1);
+            mbar_init(&tempty[s], 4);
+        }
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int num_tiles = g.num_m * g.num_n;
+    const int kblocks = g.K / BK;
+
+    if (warp == 0) {
+        // ------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            tma_prefetch_desc(&tmA);
+            tma_prefetch_desc(&tmB);
+            if (EPI == EPI_SWIGLU) tma_prefetch_desc(&tmB2);
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                int mb, nb;
+                tile_coords(tile, g, mb, nb);
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    if (!mbar_wait(&empty[stage], phase ^ 1)) { ok = false; atomicExch(g.err, 1); break; }
+                    uint8_t* a_s = smem + stage * Cfg::STAGE_BYTES;
+                    uint8_t* b_s = a_s + Cfg::A_BYTES;
+                    mbar_expect_tx(&full[stage], Cfg::STAGE_BYTES);
+                    tma_load_2d(a_s, &tmA, &full[stage], kb * BK, mb * BM);
+                    if (EPI == EPI_SWIGLU) {
+                        // 128 gate rows then 128 up rows of the same output columns
+                        tma_load_2d(b_s, &tmB, &full[stage], kb * BK, nb * 128);
+                        tma_load_2d(b_s + 128 * BK * 2, &tmB2, &full[stage], kb * BK, nb * 128);
+                    } else {
+#pragma unroll
+                        for (int h = 0; h < BN / 128; ++h)
+                            tma_load_2d(b_s + h * 128 * BK * 2, &tmB, &full[stage], kb * BK,
+                                        nb * BN + h * 128);
+                    }
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, 0, 0);
+            int stage = 0;
+            uint32_t phase = 0;
+            int as = 0;
+            uint32_t aphase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                if (!mbar_wait(&tempty[as], aphase ^ 1)) { atomicExch(g.err, 2); break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + as * BN;
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    if (!mbar_wait(&full[stage], phase)) { ok = false; atomicExch(g.err, 3); break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(smem + stage * Cfg::STAGE_BYTES);
+                    const uint32_t b_addr = a_addr + Cfg::A_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k) {
+                        const uint64_t ad = umma_desc_sw128(a_addr + k * 32, 16, 1024);
+                        const uint64_t bd = umma_desc_sw128(b_addr + k * 32, 16, 1024);
+                        umma_ss(d_tmem, ad, bd, idesc, (kb | k) != 0);
+                    }
+                    umma_commit(&empty[stage]);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                umma_commit(&tfull[as]);
+                if (++as == 2) { as = 0; aphase ^= 1; }
+            }
+        }
+    } else {
+        // ------------------------------------------------------ epilogue
+        const int q = warp & 3;  // TMEM lane quadrant this warp may access
+        int as = 0;
+        uint32_t aphase = 0;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+            int mb, nb;
+            tile_coords(tile, g, mb, nb);
+            if (!mbar_wait(&tfull[as], aphase)) { atomicExch(g.err, 4); break; }
+            tc_fence_after();
+            const int row = mb * BM + q * 32 + lane;
+            const bool row_ok = row < g.M;
+            const uint32_t t_row = tmem_base + as * BN + ((uint32_t)(q * 32) << 16);
+            if (EPI == EPI_SWIGLU) {
+#pragma unroll 1
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t rg[32], ru[32];
+                    tmem_ld32(t_row + c * 32, rg);
+                    tmem_ld32(t_row + 128 + c * 32, ru);
+                    tmem_ld_wait();
+                    if (row_ok) {
+                        float v[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const float gg = bf16_round(__uint_as_float(rg[j]));
+                            const float uu = bf16_round(__uint_as_float(ru[j]));
+                            const float sg = 1.0f / (1.0f + expf(-gg));
+                            v[j] = bf16_round(gg * sg) * uu;
+                        }
+                        store32_bf16(g.out + (size_t)row * g.ldo + nb * 128 + c * 32, v);
+                    }
+                }
+            } else {
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; ++c) {
+                    uint32_t r[32];
+                    tmem_ld32(t_row + c * 32, r);
+                    tmem_ld_wait();
+                    if (row_ok) {
+                        const int col = nb * BN + c * 32;
+                        float v[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+                        if (EPI == EPI_BIAS) {
+                            float b[32];
+                            load32_bf16(g.bias + col, b);
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) v[j] = bf16_round(v[j]) + b[j];
+                        } else if (EPI == EPI_RESID) {
+                            float b[32];
+                            load32_bf16(g.resid + (size_t)row * g.ldr + col, b);
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) v[j] = bf16_round(v[j]) + b[j];
+                        } else if (EPI == EPI_LORA) {
+                            float b[32];
+                            load32_bf16(g.out + (size_t)row * g.ldo + col, b);
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) v[j] = b[j] + g.scale * v[j];
+                        }
+                        store32_bf16(g.out + (size_t)row * g.ldo + col, v);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tempty[as]);
+            if (++as == 2) { as = 0; aphase ^= 1; }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+}
+
+// ---------------------------------------------------------------- SIMT path
+// One warp per output element; used for M < 16 (timestep MLP, M = 1) and
+// for shapes the tensor-core tiles do not cover (N % 128 or K % 64 != 0).
+__global__ void gemm_simt_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ w,
+                                 const uint16_t* __restrict__ bias, uint16_t* __restrict__ y, int M,
+                                 int N, int K, int ldx, int ldy) {
+    const int warps_per_block = blockDim.x >> 5;
+    const int n = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+    const int m = blockIdx.y;
+    const int lane = threadIdx.x & 31;
+    if (n >= N) return;
+    const uint16_t* xr = x + (size_t)m * ldx;
+    const uint16_t* wr = w + (size_t)n * K;
+    float acc = 0.f;
+    if ((K & 7) == 0 && ((((uintptr_t)xr) | ((uintptr_t)wr)) & 15) == 0) {
+        for (int k = lane * 8; k < K; k += 256) {
+            const uint4 a = *reinterpret_cast<const uint4*>(xr + k);
+            const uint4 b = *reinterpret_cast<const uint4*>(wr + k);
+            acc += bf16lo(a.x) * bf16lo(b.x); acc += bf16hi(a.x) * bf16hi(b.x);
+            acc += bf16lo(a.y) * bf16lo(b.y); acc += bf16hi(a.y) * bf16hi(b.y);
+            acc += bf16lo(a.z) * bf16lo(b.z); acc += bf16hi(a.z) * bf16hi(b.z);
+            acc += bf16lo(a.w) * bf16lo(b.w); acc += bf16hi(a.w) * bf16hi(b.w);
+        }
+    } else {
+        for (int k = lane; k < K; k += 32) acc += bf16_to_f32(xr[k]) * bf16_to_f32(wr[k]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) {
+        float v = acc;
+        if (bias) v = bf16_round(v) + bf16_to_f32(bias[n]);
+        y[(size_t)m * ldy + n] = f32_to_bf16(v);
+    }
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres);
+        if (e == cudaSuccess && qres == cudaDriverEntryPointSuccess) fn = (EncodeTiledFn)p;
+    });
+    return fn;
+}
+
+// Row-major bf16 matrix [rows, cols] with row pitch ld (elements); box is
+// 64 columns x box_rows rows, 128-byte swizzle.
+bool make_tmap_bf16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                    uint32_t box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) { set_error("tensor map: cuTensorMapEncodeTiled entry point unavailable"); return false; }
+    if ((((uintptr_t)base) & 15) || ((ld * 2) & 15)) {
+        set_error("tensor map: base/pitch not 16-byte aligned");
+        return false;
+    }
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {ld * 2};
+    cuuint32_t box[2] = {64, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
+                    box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { set_error("tensor map: encode failed (%d)", (int)r); return false; }
+    return true;
+}
+
+struct TmapKey {
+    const void* p; uint64_t rows, cols, ld; uint32_t box;
+    bool operator<(const TmapKey& o) const {
+        return std::tie(p, rows, cols, ld, box) < std::tie(o.p, o.rows, o.cols, o.ld, o.box);
+    }
+};
+// Encoding a tensor map costs a few microseconds on the host; weights and
+// workspace buffers repeat every block and step, so cache by (ptr, shape).
+const CUtensorMap* cached_tmap(const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                               uint32_t box_rows) {
+    static std::map<TmapKey, CUtensorMap> cache;
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lk(mu);
+    TmapKey k{base, rows, cols, ld, box_rows};
+    auto it = cache.find(k);
+    if (it != cache.end()) return &it->second;
+    if (cache.size() > 8192) cache.clear();
+    CUtensorMap m;
+    if (!make_tmap_bf16(&m, base, rows, cols, ld, box_rows)) return nullptr;
+    return &cache.emplace(k, m).first->second;
+}
+
+template <int EPI, int BN>
+static bool launch_tc(const CUtensorMap* tA, const CUtensorMap* tB, const CUtensorMap* tB2,
+                      GemmArgs& g, cudaStream_t st) {
+    using Cfg = GemmCfg<BN>;
+    static bool attr_done = false;
+    auto kern = gemm_tc_kernel<EPI, BN>;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             Cfg::SMEM_BYTES);
+        if (e != cudaSuccess) { set_error("gemm: smem attribute: %s", cudaGetErrorString(e)); return false; }
+        attr_done = true;
+    }
+    const int tiles = g.num_m * g.num_n;
+    int grid = sm_count();
+    if (grid > tiles) grid = tiles;
+    kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, st>>>(*tA, *tB, *tB2, g);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { set_error("gemm: launch: %s", cudaGetErrorString(e)); return false; }
+    return true;
+}
+
+bool gemm_tc_supported(int M, int N, int K, int epi) {
+    if (M < 16 || (K % BK) != 0) return false;
+    if (epi == EPI_SWIGLU) return (N % 128) == 0;  // N = ff columns of each of gate/up
+    return (N % 128) == 0;
+}
+
+// epi: see Epi.  For EPI_SWIGLU, w = gate weight, w2 = up weight, N = ff.
+bool gemm_bf16(const void* x, const void* w, const void* w2, void* y, int M, int N, int K, int epi,
+               const void* bias, const void* resid, float scale, int force_bn, cudaStream_t st) {
+    return gemm_bf16_ld(x, K, w, w2, y, N, M, N, K, epi, bias, resid, N, scale, force_bn, st);
+}
+
+bool gemm_bf16_ld(const void* x, int ldx, const void* w, const void* w2, void* y, int ldy, int M,
+                  int N, int K, int epi, const void* bias, const void* resid, int ldr, float scale,
+                  int force_bn, cudaStream_t st) {
+    if (!x || !w || !y || M <= 0 || N <= 0 || K <= 0) { set_error("gemm: bad args"); return false; }
+    if (!gemm_tc_supported(M, N, K, epi)) {
+        if (epi != EPI_STORE && epi != EPI_BIAS) { set_error("gemm: shape unsupported for fused epilogue"); return false; }
+        dim3 block(128);
+        dim3 grid((N + 3) / 4, M);
+        gemm_simt_kernel<<<grid, block, 0, st>>>((const uint16_t*)x, (const uint16_t*)w,
+                                                 (const uint16_t*)bias, (uint16_t*)y, M, N, K, ldx, ldy);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) { set_error("gemm(simt): launch: %s", cudaGetErrorString(e)); return false; }
+        return true;
+    }
+    GemmArgs g;
+    g.M = M; g.N = N; g.K = K;
+    g.out = (uint16_t*)y; g.ldo = ldy;
+    g.bias = (const uint16_t*)bias;
+    g.resid = (const uint16_t*)resid; g.ldr = ldr;
+    g.scale = scale;
+    g.err = device_error_word();
+    g.num_m = (M + BM - 1) / BM;
+    g.group_m = 32;
+
+    const CUtensorMap* tA = cached_tmap(x, M, K, ldx, 128);
+    const CUtensorMap* tB = cached_tmap(w, N, K, K, 128);
+    const CUtensorMap* tB2 = (epi == EPI_SWIGLU) ? cached_tmap(w2, N, K, K, 128) : tB;
+    if (!tA || !tB || !tB2) return false;
+
+    if (epi == EPI_SWIGLU) {
+        g.num_n = N / 128;
+        return launch_tc<EPI_SWIGLU, 256>(tA, tB, tB2, g, st);
+    }
+    int bn = 256;
+    if ((N % 256) != 0) bn = 128;
+    else {
+        // small problems: halve the tile to fill the SMs
+        const int tiles256 = g.num_m * (N / 256);
+        if (tiles256 < 2 * sm_count()) bn = 128;
+    }
+    if (force_bn == 128 || force_bn == 256) {
+        if (force_bn == 256 && (N % 256) != 0) { set_error("gemm: BN=256 needs N %% 256 == 0"); return false; }
+        bn = force_bn;
+    }
+    g.num_n = N / bn;
+    if (bn == 256) {
+        switch (epi) {
+            case EPI_STORE: return launch_tc<EPI_STORE, 256>(tA, tB, tB2, g, st);
+            case EPI_BIAS:  return launch_tc<EPI_BIAS, 256>(tA, tB, tB2, g, st);
+            case EPI_RESID: return launch_tc<EPI_RESID, 256>(tA, tB, tB2, g, st);
+            case EPI_LORA:  return launch_tc<EPI_LORA, 256>(tA, tB, tB2, g, st);
+        }
+    } else {
+        switch (epi) {
+            case EPI_STORE: return launch_tc<EPI_STORE, 128>(tA, tB, tB2, g, st);
+            case EPI_BIAS:  return launch_tc<EPI_BIAS, 128>(tA, tB, tB2, g, st);
+            case EPI_RESID: return launch_tc<EPI_RESID, 128>(tA, tB, tB2, g, st);
+            case EPI_LORA:  return launch_tc<EPI_LORA, 128>(tA, tB, tB2, g, st);
+        }
+    }
+    set_error("gemm: unknown epilogue %d", epi);
+    return false;
+}
+
+}  // namespace o1

@@ -1,0 +1,92 @@
+// Internal (C++) interface between the kernel files and the host engine.
+// Everything here launches on the stream passed in and allocates nothing.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace o1 {
+
+enum Epi { EPI_STORE = 0, EPI_BIAS = 1, EPI_RESID = 2, EPI_SWIGLU = 3, EPI_LORA = 4 };
+
+// ---- gemm_tc.cu
+bool gemm_bf16(const void* x, const void* w, const void* w2, void* y, int M, int N, int K, int epi,
+               const void* bias, const void* resid, float scale, int force_bn, cudaStream_t st);
+// Same, with explicit row pitches (elements) for x and y so that a GEMM can
+// read / write a column slice of a wider buffer.
+bool gemm_bf16_ld(const void* x, int ldx, const void* w, const void* w2, void* y, int ldy, int M,
+                  int N, int K, int epi, const void* bias, const void* resid, int ldr, float scale,
+                  int force_bn, cudaStream_t st);
+bool gemm_tc_supported(int M, int N, int K, int epi);
+const CUtensorMap* cached_tmap(const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                               uint32_t box_rows);
+
+// ---- attn_tc.cu
+// q [S, ldq] (heads*128 columns used), k/v [S, ldk]/[S, ldv] (kv_heads*128),
+// out [S, ldo] seq-major; rows < ar_len are causal, rows >= ar_len see all keys.
+bool flash_attention(const void* q, int ldq, const void* k, int ldk, const void* v, int ldv,
+                     void* out, int ldo, int S, int heads, int kv_heads, int ar_len, float scale,
+                     cudaStream_t st);
+
+bool flash_attention_hm(const void* q, const void* k, const void* v, void* out, int S, int heads,
+                        int kv_heads, int ar_len, float scale, bool out_head_major, cudaStream_t st);
+
+// ---- elementwise.cu
+bool rmsnorm(const void* x, const void* w, void* y, int rows, int cols, float eps, cudaStream_t st);
+bool silu(const void* x, void* y, size_t n, cudaStream_t st);
+bool swiglu(const void* gate, const void* up, void* y, size_t n, cudaStream_t st);
+bool residual_add(const void* x, const void* a, void* y, size_t n, cudaStream_t st);
+bool mrope_cos_sin(const float* pos, int bs, int seq, const int64_t* section, int n_section,
+                   int head_dim, float theta, float scaling, int interleaved, float* cosd,
+                   float* sind, cudaStream_t st);
+// compact table: cs[s][0..63] = cos, cs[s][64..127] = sin of the 64 distinct angles
+bool mrope_table64(const float* pos, int seq, float theta, float* cs, cudaStream_t st);
+bool apply_rotary(const void* x, const float* cosd, const float* sind, void* y, int heads, int seq,
+                  int dim, int f32_mode, cudaStream_t st);
+// fused per-head RMSNorm + rotary, in place on a seq-major [S, ld] buffer
+// holding `heads` heads of 128 starting at column 0 (weights w[128]).
+bool qk_norm_rope(void* x, int ld, int S, int heads, const void* w, const float* cs_table,
+                  float eps, cudaStream_t st);
+bool head_split(const void* in, void* out, int seq, int heads, int dim, cudaStream_t st);
+bool head_merge(const void* in, void* out, int seq, int heads, int dim, cudaStream_t st);
+bool gather_rows(const void* table, const void* idx, void* out, int M, int cols, int64_t nrows,
+                 cudaStream_t st);
+bool tms_condition(const void* idx, const void* emb, const void* t_emb, void* out, int M, int H,
+                   int64_t tms_id, cudaStream_t st);
+// gather + tms substitution in one pass: out[row] = (id==tms) ? t_emb : table[id]
+bool embed_text(const void* table, const void* idx, const void* t_emb, void* out, int M, int H,
+                int64_t nrows, int64_t tms_id, cudaStream_t st);
+bool scale_f32(const float* in, float* out, float s, int n, cudaStream_t st);
+bool f32_to_bf16_buf(const float* in, void* out, int n, cudaStream_t st);
+bool timestep_embed(const float* t, float* y, int N, int dim, cudaStream_t st);
+bool masked_scatter(const void* h_text, const uint8_t* mask, const void* embeds, void* out, int T,
+                    int H, cudaStream_t st);
+bool deepstack_inject(const void* in, const uint8_t* mask, const void* ds, void* out, int S, int H,
+                      cudaStream_t st);
+bool fill_normal_bf16(void* dst, size_t n, uint64_t seed, float mean, float std, cudaStream_t st);
+bool fill_normal_f32(float* dst, size_t n, uint64_t seed, float mean, float std, cudaStream_t st);
+bool transpose_bf16(const void* in, void* out, int rows, int cols, cudaStream_t st);
+
+// ---- sched.cu
+bool sched_bf16_upcast(const void* in, float* out, int n, cudaStream_t st);
+bool sched_denoised(const float* z, const float* mo, float sigma, float* den, int n, cudaStream_t st);
+bool sched_z_next(const float* noise, const float* den, float sigma_next, float s_noise,
+                  float* z_next, int n, cudaStream_t st);
+bool sched_vcond(const void* z, const void* xp, float sigma, float* mo, int n, cudaStream_t st);
+bool sched_flow_match_step(const void* z, const float* mo, float sigma, float sigma_next,
+                           void* z_next, int n, cudaStream_t st);
+bool sched_cfg_guided(const float* mo_c, const float* mo_u, float g, float* mo, int n, cudaStream_t st);
+// fused vcond x2 + cfg + flow-match step (8 bytes / element instead of 40)
+bool sched_cfg_flow_step(const void* z, const void* xp_cond, const void* xp_uncond, float sigma,
+                         float sigma_next, float g, void* z_next, size_t n, cudaStream_t st);
+bool unipc_convert(const float* sample, const float* mo, float sigma_cur, float* conv, int n,
+                   cudaStream_t st);
+bool unipc_correct(const float* last, const float* mo0, const float* mo_old, const float* conv,
+                   float sig_t, float sig_s0, float alpha_t, float h_phi_1, float B_h, float rhos_c0,
+                   float rhos_c1, float inv_rks0, int order_c, float* out, int n, cudaStream_t st);
+bool unipc_predict(const float* sample, const float* mo0, const float* mo_old, float sig_t,
+                   float sig_s0, float alpha_t, float h_phi_1, float B_h, float rhos_p,
+                   float inv_rks0, int order_p, float* out, int n, cudaStream_t st);
+
+}  // namespace o1
