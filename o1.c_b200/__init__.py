@@ -1,0 +1,207 @@
+"""Host-side Python mirror of the o1.c model interface over libo1b200.so.
+
+The product is the shared library (CUDA kernels + C ABI, see include/o1_b200.h);
+this module only binds it with ctypes and supplies device memory, streams and
+process-group plumbing through PyTorch.  There is no CPU or PyTorch fallback:
+importing this module without the built library raises.
+"""
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libo1b200.so")
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError(
+        f"{LIB_PATH} is missing: build it with `python o1.c_b200/build.py` "
+        "(nvcc, sm_100a). There is no fallback path."
+    )
+
+lib = C.CDLL(LIB_PATH, mode=os.RTLD_LOCAL | os.RTLD_NOW)
+
+c_void_p, c_int, c_int64, c_float, c_size_t, c_uint64 = (
+    C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_size_t, C.c_uint64)
+
+HD_OK = 0
+
+# ----------------------------------------------------------------- dims
+HIDDEN, HEADS, KV_HEADS, HEAD_DIM, FF = 4096, 32, 8, 128, 12288
+PATCH_DIM, XE_MID, VOCAB, TMS_ID, N_LAYERS = 3072, 1024, 151936, 151673, 36
+ROPE_THETA, EPS = 5000000.0, 1e-6
+
+
+# ----------------------------------------------------------------- structs
+class BlockBinding(C.Structure):
+    """hd_block_binding (o1.c src/model/block.h:48-62)."""
+    _fields_ = [("layer_idx", c_int)] + [(n, c_void_p) for n in (
+        "q_proj", "k_proj", "v_proj", "o_proj", "input_ln", "post_ln",
+        "gate_proj", "up_proj", "down_proj", "q_norm", "k_norm")]
+
+
+class BlockInternals(C.Structure):
+    """hd_block_internals (src/model/block.h:34-40)."""
+    _fields_ = [(n, c_void_p) for n in ("ln0", "attn_hidden", "attn_resid", "post_ln", "mlp_out")]
+
+
+class ForwardBinding(C.Structure):
+    """hd_forward_binding (src/model/forward.h:40-59)."""
+    _fields_ = [(n, c_void_p) for n in (
+        "embed_tokens", "te0_w", "te0_b", "te2_w", "te2_b", "xe1_w", "xe2_w", "xe2_b",
+        "fl_w", "fl_b", "fnorm_w")] + [("n_layers", c_int), ("blocks", C.POINTER(BlockBinding))]
+
+
+class ForwardWorkspace(C.Structure):
+    """hd_forward_workspace (src/model/forward.h:66-93)."""
+    _fields_ = [(n, c_void_p) for n in (
+        "hidden_a", "hidden_b", "h_text", "norm_out", "head_out", "t_emb", "te_hidden", "freq",
+        "freq_bf16", "t_scaled", "xe_stage", "xe_out", "xe_ref")] + [
+        ("n_ref", c_int), ("block_scratch", c_void_p), ("block_scratch_bytes", c_int64),
+        ("sdpa", c_void_p)]
+
+
+class ForwardDiagnostics(C.Structure):
+    """hd_forward_diagnostics (src/model/forward.h:96-107)."""
+    _fields_ = [(n, c_void_p) for n in (
+        "after_embedding", "after_timestep_conditioning", "after_target_embedding",
+        "after_block_0_input", "after_block_0", "after_block_mid", "after_block_last",
+        "before_final_norm", "after_final_norm", "after_final_head")]
+
+
+class VisualCond(C.Structure):
+    """hd_visual_cond (src/model/forward.h:129-134)."""
+    _fields_ = [("image_embeds", c_void_p), ("deepstack", c_void_p * 3),
+                ("visual_mask", c_void_p), ("v_tokens", c_int)]
+
+
+class LoraEntry(C.Structure):
+    """hd_lora_entry (include/hd_lora.h:32-45)."""
+    _fields_ = [("lora_prefix", C.c_char * 256), ("base_tensor", C.c_char * 256),
+                ("rank", C.c_uint32), ("in_dim", C.c_uint32), ("out_dim", C.c_uint32),
+                ("alpha", c_float), ("multiplier", c_float),
+                ("down_dev", c_void_p), ("up_dev", c_void_p), ("base_dev", c_void_p)]
+
+
+# ----------------------------------------------------------------- signatures
+def _sig(name, restype, *argtypes):
+    fn = getattr(lib, name)
+    fn.restype = restype
+    fn.argtypes = list(argtypes)
+    return fn
+
+
+_P = c_void_p
+_sig("hd_last_error", C.c_char_p)
+_sig("hd_cuda_last_error", C.c_char_p)
+_sig("hd_cuda_clear_error", None)
+_sig("hd_lora_last_error", C.c_char_p)
+_sig("hd_bf16_to_f32", c_float, C.c_uint16)
+_sig("hd_f32_to_bf16", C.c_uint16, c_float)
+_sig("hd_rmsnorm", None, _P, _P, _P, c_int, c_int, c_float)
+_sig("hd_silu", None, _P, _P, c_size_t)
+_sig("hd_swiglu", None, _P, _P, _P, c_size_t)
+_sig("hd_residual_add", None, _P, _P, _P, c_size_t)
+_sig("hd_linear", None, _P, _P, _P, _P, c_int, c_int, c_int, c_int)
+_sig("hd_linear_reference", None, _P, _P, _P, _P, c_int, c_int, c_int, c_int)
+_sig("hd_timestep_embed", None, _P, _P, c_int, c_int)
+_sig("hd_mrope_cos_sin", None, _P, c_int, c_int, _P, c_int, c_int, c_float, c_float, c_int, _P, _P)
+_sig("hd_apply_rotary", None, _P, _P, _P, _P, c_int, c_int, c_int)
+_sig("hd_apply_rotary_f32", None, _P, _P, _P, _P, c_int, c_int, c_int)
+_sig("hd_attention_eager", None, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_float)
+_sig("hd_head_split", None, _P, _P, c_int, c_int, c_int)
+_sig("hd_head_merge", None, _P, _P, c_int, c_int, c_int)
+_sig("hd_gather_rows", None, _P, _P, _P, c_int, c_int, c_int64)
+_sig("hd_apply_tms_condition", None, _P, _P, _P, _P, c_int, c_int, c_int64)
+_sig("hd_scale_f32", None, _P, _P, c_float, c_int)
+_sig("hd_f32_convert_bf16", None, _P, _P, c_int)
+_sig("hd_sched_bf16_upcast", None, _P, _P, c_int)
+_sig("hd_sched_denoised", None, _P, _P, c_float, _P, c_int)
+_sig("hd_sched_z_next", None, _P, _P, c_float, c_float, _P, c_int)
+_sig("hd_sched_vcond", None, _P, _P, c_float, _P, c_int)
+_sig("hd_sched_flow_match_step", None, _P, _P, c_float, c_float, _P, c_int)
+_sig("hd_sched_cfg_guided", None, _P, _P, c_float, _P, c_int)
+_sig("hd_unipc_convert", None, _P, _P, c_float, _P, c_int)
+_sig("hd_unipc_correct", None, _P, _P, _P, _P, c_float, c_float, c_float, c_float, c_float, c_float,
+     c_float, c_float, c_int, _P, c_int)
+_sig("hd_unipc_predict", None, _P, _P, _P, c_float, c_float, c_float, c_float, c_float, c_float,
+     c_float, c_int, _P, c_int)
+_sig("hd_vision_masked_scatter", None, _P, _P, _P, _P, c_int, c_int)
+_sig("hd_vision_deepstack_inject", None, _P, _P, _P, _P, c_int, c_int)
+_sig("hd_sdpa_create", c_int, C.POINTER(_P), c_int, c_int, c_int, c_int, c_int, c_int, c_float)
+_sig("hd_sdpa_create_split", c_int, C.POINTER(_P), c_int, c_int, c_int, c_int, c_int, c_int, c_float)
+_sig("hd_sdpa_create_prod", c_int, C.POINTER(_P), c_int, c_int, c_int, c_int, c_int, c_int, c_float)
+_sig("hd_sdpa_execute", c_int, _P, _P, _P, _P, _P, _P, _P)
+_sig("hd_sdpa_execute_split", c_int, _P, _P, _P, _P, _P, _P)
+_sig("hd_sdpa_destroy", None, _P)
+_sig("hd_decoder_block_scratch_bytes", c_int64, c_int64, c_int, c_int, c_int, c_int, c_int)
+_sig("hd_decoder_block", c_int, _P, _P, _P, C.POINTER(BlockBinding), _P, _P, c_int64,
+     C.POINTER(BlockInternals), _P, c_int64, c_int, c_int, c_int, c_int, c_int, _P)
+_sig("hd_forward_workspace_bytes", c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, c_int,
+     C.POINTER(c_int64))
+_sig("hd_forward_ws_offset", c_int64, C.c_char_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_int,
+     c_int, C.POINTER(c_int64))
+_sig("hd_forward", c_int, C.POINTER(ForwardBinding), C.POINTER(ForwardWorkspace), _P, c_int, _P, _P,
+     _P, c_int, C.POINTER(VisualCond), _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+     C.POINTER(ForwardDiagnostics), _P, _P)
+_sig("hd_lora_merge_gpu", c_int, C.POINTER(LoraEntry), c_size_t, _P)
+_sig("o1_set_stream", None, _P)
+_sig("o1_get_stream", _P)
+_sig("o1_device_error", c_int)
+_sig("o1_sm_count", c_int)
+_sig("o1_launch_count", c_int64, c_int)
+_sig("o1_gemm", c_int, _P, c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P, _P, c_int,
+     c_float, c_int)
+_sig("o1_flash_attention", c_int, _P, c_int, _P, c_int, _P, c_int, _P, c_int, c_int, c_int, c_int,
+     c_int, c_float)
+_sig("o1_mrope_table", c_int, _P, c_int, c_float, _P)
+_sig("o1_qk_norm_rope", c_int, _P, c_int, c_int, c_int, _P, _P, c_float)
+_sig("o1_sched_cfg_flow_step", c_int, _P, _P, _P, c_float, c_float, c_float, _P, c_size_t)
+_sig("o1_fill_normal_bf16", c_int, _P, c_size_t, c_uint64, c_float, c_float)
+_sig("o1_fill_normal_f32", c_int, _P, c_size_t, c_uint64, c_float, c_float)
+_sig("o1_hash_normal_host", c_float, c_uint64, c_uint64)
+_sig("o1_denoise_step_cfg", c_int, C.POINTER(ForwardBinding), C.POINTER(ForwardWorkspace), _P, _P,
+     c_int, _P, c_int, _P, c_int, _P, c_float, c_float, c_float, _P, _P, c_int, c_int, c_int, c_int,
+     c_int, c_int)
+_sig("o1_denoise_step_cfg_host", c_int, C.POINTER(ForwardBinding), C.POINTER(ForwardWorkspace), _P,
+     _P, c_int, _P, c_int, _P, _P, c_int, c_float, c_float, c_float, _P, _P, _P, _P, c_int, c_int,
+     c_int, c_int, c_int, c_int)
+
+EPI_STORE, EPI_BIAS, EPI_RESID, EPI_SWIGLU, EPI_LORA = 0, 1, 2, 3, 4
+
+
+class O1Error(RuntimeError):
+    pass
+
+
+def last_error():
+    a = lib.hd_last_error() or b""
+    b = lib.hd_cuda_last_error() or b""
+    return (a.decode(errors="replace") + " | " + b.decode(errors="replace")).strip(" |")
+
+
+def check(status, what=""):
+    if status != HD_OK:
+        raise O1Error(f"{what} failed with hd_status {status}: {last_error()}")
+
+
+def check_cuda_errbuf(what=""):
+    msg = lib.hd_cuda_last_error()
+    if msg:
+        text = msg.decode(errors="replace")
+        lib.hd_cuda_clear_error()
+        raise O1Error(f"{what}: {text}")
+
+
+def ptr(t):
+    """Device (or pinned host) address of a torch tensor, None -> NULL."""
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def use_torch_stream():
+    """Make the library enqueue on torch's current CUDA stream."""
+    import torch
+    lib.o1_set_stream(C.c_void_p(torch.cuda.current_stream().cuda_stream))
+
+
+from .model import (  # noqa: E402
+    Weights, Engine, seq_t2i, dev_sigmas, weight_seed, SLOT_NAMES, GLOBAL_NAMES, tensor_shape,
+)

@@ -89,6 +89,12 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     if (kv_end > a.S) kv_end = a.S;
     const int n_tiles = (kv_end + AKV - 1) / AKV;
 
+    // a kernel that already failed on this device leaves its code in *err: do nothing then
+    __shared__ int s_abort;
+    if (threadIdx.x == 0) s_abort = *reinterpret_cast<volatile int*>(a.err);
+    __syncthreads();
+    if (s_abort != 0) return;
+
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
         for (int s = 0; s < KV_STAGES; ++s) {

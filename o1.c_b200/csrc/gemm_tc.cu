@@ -103,6 +103,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
 
+    // a kernel that already failed on this device leaves its code in *err: do nothing then
+    __shared__ int s_abort;
+    if (threadIdx.x == 0) s_abort = *reinterpret_cast<volatile int*>(g.err);
+    __syncthreads();
+    if (s_abort != 0) return;
+
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&full[s], 1);
@@ -403,7 +409,8 @@ bool gemm_bf16_ld(const void* x, int ldx, const void* w, const void* w2, void* y
         dim3 block(128);
         dim3 grid((N + 3) / 4, M);
         gemm_simt_kernel<<<grid, block, 0, st>>>((const uint16_t*)x, (const uint16_t*)w,
-                                                 (const uint16_t*)bias, (uint16_t*)y, M, N, K, ldx, ldy);
+                                                 (const uint16_t*)(epi == EPI_BIAS ? bias : nullptr), (uint16_t*)y, M, N, K,
+                                                 ldx, ldy);
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) { set_error("gemm(simt): launch: %s", cudaGetErrorString(e)); return false; }
         return true;

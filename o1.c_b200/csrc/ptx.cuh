@@ -55,16 +55,21 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint64_t* bar, uint32_t parity
         : "memory");
     return ok;
 }
-// Bounded wait. The limit is generous (seconds) and only exists so that a
-// protocol bug ends as an error code instead of a hung GPU.
-#ifndef O1_WAIT_LIMIT
-#define O1_WAIT_LIMIT (1u << 24)
+// Bounded wait: gives up after about two seconds of SM clock.  Legitimate waits
+// in these kernels last microseconds; the limit only exists so that a protocol
+// bug ends as an error code instead of a hung GPU.
+#ifndef O1_WAIT_CYCLES
+#define O1_WAIT_CYCLES 4000000000ll
 #endif
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    for (uint32_t it = 0; it < O1_WAIT_LIMIT; ++it) {
-        if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (;;) {
+#pragma unroll 1
+        for (int it = 0; it < 64; ++it)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (clock64() - t0 > O1_WAIT_CYCLES) return false;
     }
-    return false;
 }
 
 // ---------------------------------------------------------------- fences

@@ -1,0 +1,230 @@
+"""Seeded random-init weights, sequence geometry and an Engine object that
+drives hd_forward / hd_decoder_block / the CFG denoise step of libo1b200.so.
+
+Mirrors, on the Python side, what o1.c's runtime does around the hot path:
+weight arena + bindings (src/model/weights.c, forward.c:61-105), position ids
+(src/runtime/sequence.c:67-160), sigma list (src/model/scheduler.c:26-64) and
+the step loop (src/runtime/generate.c:1314-1455).
+"""
+import ctypes as C
+
+import torch
+
+from . import (  # noqa: F401  (re-exported names)
+    lib, ptr, check, check_cuda_errbuf, BlockBinding, BlockInternals, ForwardBinding,
+    ForwardWorkspace, ForwardDiagnostics, LoraEntry, HIDDEN, HEADS, KV_HEADS, HEAD_DIM, FF, PATCH_DIM,
+    XE_MID, VOCAB, TMS_ID, N_LAYERS,
+)
+
+SLOT_NAMES = ["q_proj", "k_proj", "v_proj", "o_proj", "input_ln", "post_ln", "gate_proj", "up_proj",
+              "down_proj", "q_norm", "k_norm"]
+GLOBAL_NAMES = ["embed_tokens", "te0_w", "te0_b", "te2_w", "te2_b", "xe1_w", "xe2_w", "xe2_b", "fl_w",
+                "fl_b", "fnorm_w"]
+NORM_NAMES = {"input_ln", "post_ln", "q_norm", "k_norm", "fnorm_w"}
+DEV_TIMESTEPS = [999, 987, 974, 960, 945, 929, 913, 895, 877, 857, 836, 814, 790, 764, 737, 707, 675,
+                 640, 602, 560, 515, 464, 409, 347, 278, 199, 110, 8]
+
+
+def tensor_shape(name, hidden=HIDDEN, heads=HEADS, kv_heads=KV_HEADS, head_dim=HEAD_DIM, ff=FF,
+                 vocab=VOCAB):
+    """[out, in] shapes of the bound tensors (o1.c src/model/block.h:48-62, forward.h:40-59)."""
+    return {
+        "q_proj": (heads * head_dim, hidden), "k_proj": (kv_heads * head_dim, hidden),
+        "v_proj": (kv_heads * head_dim, hidden), "o_proj": (hidden, heads * head_dim),
+        "input_ln": (hidden,), "post_ln": (hidden,), "gate_proj": (ff, hidden), "up_proj": (ff, hidden),
+        "down_proj": (hidden, ff), "q_norm": (head_dim,), "k_norm": (head_dim,),
+        "embed_tokens": (vocab, hidden), "te0_w": (hidden, 256), "te0_b": (hidden,),
+        "te2_w": (hidden, hidden), "te2_b": (hidden,), "xe1_w": (XE_MID, PATCH_DIM),
+        "xe2_w": (hidden, XE_MID), "xe2_b": (hidden,), "fl_w": (PATCH_DIM, hidden), "fl_b": (PATCH_DIM,),
+        "fnorm_w": (hidden,),
+    }[name]
+
+
+def weight_seed(seed, layer, name):
+    """Seed of one tensor's counter-based stream. layer = -1 for the global tensors."""
+    idx = (SLOT_NAMES.index(name) if layer >= 0 else GLOBAL_NAMES.index(name))
+    return (int(seed) * 1000003 + (layer + 1) * 64 + idx) & 0xFFFFFFFFFFFFFFFF
+
+
+def dev_sigmas():
+    """28 Dev sigmas + trailing 0.0, fp32 (scheduler.c:26-64)."""
+    return [float(torch.tensor(t, dtype=torch.float32) / 1000.0) for t in DEV_TIMESTEPS] + [0.0]
+
+
+def seq_t2i(text_len, grid_h, grid_w, fix_point=4096):
+    """Position ids fp32 [3, S] and ar_len for a T2I sequence (sequence.c:88-118, 120-142)."""
+    S = text_len + grid_h * grid_w
+    pos = torch.empty(3, S, dtype=torch.float32)
+    t = torch.arange(text_len, dtype=torch.float32)
+    pos[:, :text_len] = t
+    hh = torch.arange(grid_h, dtype=torch.float32).repeat_interleave(grid_w)
+    ww = torch.arange(grid_w, dtype=torch.float32).repeat(grid_h)
+    pos[0, text_len:] = float(fix_point)
+    pos[1, text_len:] = fix_point + hh
+    pos[2, text_len:] = fix_point + ww
+    return pos, text_len - 1
+
+
+class Weights:
+    """One 256-byte-aligned device arena of bf16 tensors, filled by the library's
+    counter-based generator so that the CPU oracle can regenerate any tensor.
+
+    weight_set "A": every tensor ~ N(0, std).  "B": RMSNorm weights are
+    1 + N(0, std) instead, which keeps attention logits away from zero.
+    """
+
+    def __init__(self, n_layers=N_LAYERS, seed=1234, weight_set="A", std=0.02, device="cuda",
+                 hidden=HIDDEN, heads=HEADS, kv_heads=KV_HEADS, head_dim=HEAD_DIM, ff=FF, vocab=VOCAB):
+        self.n_layers, self.seed, self.weight_set, self.std = n_layers, seed, weight_set, std
+        self.dims = dict(hidden=hidden, heads=heads, kv_heads=kv_heads, head_dim=head_dim, ff=ff,
+                         vocab=vocab)
+        self.device = torch.device(device)
+        entries = [(-1, n) for n in GLOBAL_NAMES] + [(l, n) for l in range(n_layers) for n in SLOT_NAMES]
+        self.offsets, off = {}, 0
+        for layer, name in entries:
+            shape = tensor_shape(name, **self.dims)
+            n = 1
+            for d in shape:
+                n *= d
+            self.offsets[(layer, name)] = (off, shape, n)
+            off += (n * 2 + 255) & ~255
+        self.arena = torch.empty(off, dtype=torch.uint8, device=self.device)
+        assert self.arena.data_ptr() % 256 == 0
+        with torch.cuda.device(self.device):
+            from . import use_torch_stream
+            use_torch_stream()
+            for (layer, name), (o, shape, n) in self.offsets.items():
+                mean = 1.0 if (weight_set == "B" and name in NORM_NAMES) else 0.0
+                rc = lib.o1_fill_normal_bf16(C.c_void_p(self.arena.data_ptr() + o), n,
+                                             weight_seed(seed, layer, name), mean, std)
+                if rc != 0:
+                    check_cuda_errbuf("fill_normal")
+        self._blocks = (BlockBinding * n_layers)()
+        for l in range(n_layers):
+            self._blocks[l].layer_idx = l
+            for name in SLOT_NAMES:
+                setattr(self._blocks[l], name, self.addr(l, name))
+        self.binding = ForwardBinding()
+        for name in GLOBAL_NAMES:
+            setattr(self.binding, name, self.addr(-1, name))
+        self.binding.n_layers = n_layers
+        self.binding.blocks = C.cast(self._blocks, C.POINTER(BlockBinding))
+
+    def addr(self, layer, name):
+        return self.arena.data_ptr() + self.offsets[(layer, name)][0]
+
+    def tensor(self, layer, name):
+        """bf16 torch view of one tensor inside the arena."""
+        o, shape, n = self.offsets[(layer, name)]
+        return self.arena[o:o + n * 2].view(torch.bfloat16).view(*shape)
+
+    def block_binding(self, layer):
+        return self._blocks[layer]
+
+    def nbytes(self):
+        return self.arena.numel()
+
+
+class Engine:
+    """Workspace + call wrappers for one sequence geometry on one GPU."""
+
+    def __init__(self, weights, text_len, img_tokens, ar_len=None):
+        self.w = weights
+        self.T, self.I, self.S = text_len, img_tokens, text_len + img_tokens
+        self.ar_len = text_len - 1 if ar_len is None else ar_len
+        d = weights.dims
+        self.dimargs = (d["heads"], d["kv_heads"], d["hidden"], d["ff"], d["head_dim"])
+        self.device = weights.device
+        bs = C.c_int64(0)
+        nbytes = lib.hd_forward_workspace_bytes(self.S, self.I, *self.dimargs, C.byref(bs))
+        self.block_scratch_bytes = bs.value
+        self.ws_buf = torch.empty(nbytes + 256, dtype=torch.uint8, device=self.device)
+        self.ws = ForwardWorkspace()
+        self.ws.hidden_a = self.ws_buf.data_ptr()
+        self.ws.block_scratch_bytes = bs.value
+        plan = C.c_void_p()
+        rc = lib.hd_sdpa_create_split(C.byref(plan), 1, d["heads"], d["kv_heads"], self.S, self.ar_len,
+                                      d["head_dim"], float(d["head_dim"]) ** -0.5)
+        if rc != 0:
+            check_cuda_errbuf("sdpa_create")
+        self.plan = plan
+        self.ws.sdpa = plan
+        self.xp = torch.empty(2 * self.S * PATCH_DIM, dtype=torch.bfloat16, device=self.device)
+        self.timestep = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self.sec = torch.tensor([24, 20, 20], dtype=torch.int64, device=self.device)
+
+    def __del__(self):
+        try:
+            if getattr(self, "plan", None):
+                lib.hd_sdpa_destroy(self.plan)
+        except Exception:
+            pass
+
+    def ws_region(self, name, nbytes):
+        bs = C.c_int64(0)
+        off = lib.hd_forward_ws_offset(name.encode(), self.S, self.T, self.I, *self.dimargs, C.byref(bs))
+        if off < 0:
+            raise KeyError(name)
+        return self.ws_buf[off:off + nbytes]
+
+    def block(self, x, pos, layer, internals=False):
+        """hd_decoder_block on x [S, hidden] bf16; returns out (and the five internals)."""
+        out = torch.empty_like(x)
+        scratch = self.ws_region("block_scratch", self.block_scratch_bytes)
+        ints, bufs = None, {}
+        if internals:
+            ints = BlockInternals()
+            for n in ("ln0", "attn_hidden", "attn_resid", "post_ln", "mlp_out"):
+                bufs[n] = torch.empty_like(x)
+                setattr(ints, n, bufs[n].data_ptr())
+        bb = self.w.block_binding(layer)
+        rc = lib.hd_decoder_block(ptr(x), ptr(pos), None, C.byref(bb), ptr(self.sec), ptr(scratch),
+                                  self.block_scratch_bytes, C.byref(ints) if ints else None, ptr(out),
+                                  self.S, *self.dimargs, self.plan)
+        check(rc, "hd_decoder_block")
+        return (out, bufs) if internals else out
+
+    def forward(self, ids, pos, vinputs, t, out=None, diag_names=()):
+        """hd_forward; t is the model timestep (1 - sigma). Returns x_pred [S, 3072] bf16."""
+        if out is None:
+            out = torch.empty(self.S, PATCH_DIM, dtype=torch.bfloat16, device=self.device)
+        self.timestep.fill_(float(t))
+        diag, bufs = None, {}
+        if diag_names:
+            diag = ForwardDiagnostics()
+            d = self.w.dims
+            for n in diag_names:
+                rows = {"after_embedding": self.T, "after_timestep_conditioning": self.T,
+                        "after_target_embedding": self.I}.get(n, self.S)
+                cols = PATCH_DIM if n == "after_final_head" else d["hidden"]
+                bufs[n] = torch.empty(rows, cols, dtype=torch.bfloat16, device=self.device)
+                setattr(diag, n, bufs[n].data_ptr())
+        d = self.w.dims
+        rc = lib.hd_forward(C.byref(self.w.binding), C.byref(self.ws), ptr(ids), self.T, ptr(pos), None,
+                            ptr(vinputs), self.I, None, ptr(self.timestep), ptr(self.sec), self.S,
+                            *self.dimargs, TMS_ID, C.byref(diag) if diag else None, ptr(out), None)
+        check(rc, "hd_forward")
+        return (out, bufs) if diag_names else out
+
+    def denoise_step_cfg(self, ids_c, ids_u, pos, z, sigma, sigma_next, guidance, z_next=None):
+        """One CFG flow-match step on device-resident latents z [I, 3072] bf16."""
+        if z_next is None:
+            z_next = torch.empty_like(z)
+        self.timestep.fill_(1.0 - float(sigma))
+        rc = lib.o1_denoise_step_cfg(C.byref(self.w.binding), C.byref(self.ws), ptr(ids_c), ptr(ids_u),
+                                     self.T, ptr(pos), self.ar_len, ptr(z), self.I, ptr(self.timestep),
+                                     float(sigma), float(sigma_next), float(guidance), ptr(self.xp),
+                                     ptr(z_next), *self.dimargs, TMS_ID)
+        check(rc, "o1_denoise_step_cfg")
+        return z_next
+
+    def denoise_step_cfg_host(self, ids_c, ids_u, pos, z_host, z_dev, sigma, sigma_next, guidance,
+                              z_next_dev, z_next_host):
+        """Same step through host (pinned) latents: H2D, step, D2H, synchronise."""
+        rc = lib.o1_denoise_step_cfg_host(C.byref(self.w.binding), C.byref(self.ws), ptr(ids_c),
+                                          ptr(ids_u), self.T, ptr(pos), self.ar_len, ptr(z_host),
+                                          ptr(z_dev), self.I, float(sigma), float(sigma_next),
+                                          float(guidance), ptr(self.timestep), ptr(self.xp),
+                                          ptr(z_next_dev), ptr(z_next_host), *self.dimargs, TMS_ID)
+        check(rc, "o1_denoise_step_cfg_host")
+        return z_next_host

@@ -1,0 +1,117 @@
+"""No-GPU checks of the C ABI and of the host logic: the library loads, exports every
+function include/o1_b200.h declares, sizes/offsets are consistent, argument checks fail
+the way o1.c's do (status code + message, src/model/block.c:146-157, forward.c:208-224),
+and the Python mirror's structs match the C layout."""
+import ctypes as C
+import os
+import re
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_functions():
+    text = open(os.path.join(ROOT, "include", "o1_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    names = set(re.findall(r"\b((?:hd|o1)_[a-z0-9_]+)\s*\(", text))
+    return sorted(names)
+
+
+def test_library_exports_every_declared_symbol(pkg):
+    names = declared_functions()
+    assert len(names) > 70
+    missing = [n for n in names if not hasattr(pkg.lib, n)]
+    assert not missing, f"declared in include/o1_b200.h but not exported: {missing}"
+
+
+def test_no_torch_or_oracle_linked_into_product(pkg):
+    import subprocess
+    out = subprocess.run(["ldd", pkg.LIB_PATH], capture_output=True, text=True).stdout
+    assert "torch" not in out and "o1oracle" not in out and "o1ref" not in out
+    assert "cublas" not in out and "cudnn" not in out       # no library GEMM/attention on the hot path
+
+
+def test_struct_sizes_match_c_layout(pkg):
+    p = C.sizeof(C.c_void_p)
+    assert C.sizeof(pkg.BlockBinding) == 8 + 11 * p
+    assert C.sizeof(pkg.BlockInternals) == 5 * p
+    assert C.sizeof(pkg.ForwardBinding) == 11 * p + 8 + p
+    assert C.sizeof(pkg.ForwardWorkspace) == 13 * p + 8 + p + 8 + p
+    assert C.sizeof(pkg.ForwardDiagnostics) == 10 * p
+    assert C.sizeof(pkg.LoraEntry) == 512 + 3 * 4 + 2 * 4 + 4 + 3 * p   # 4 bytes padding before pointers
+
+
+def test_workspace_layout(pkg):
+    lib = pkg.lib
+    S, I = 1280, 1024
+    bs = C.c_int64(0)
+    total = lib.hd_forward_workspace_bytes(S, I, 32, 8, 4096, 12288, 128, C.byref(bs))
+    assert bs.value == lib.hd_decoder_block_scratch_bytes(S, 32, 8, 4096, 12288, 128)
+    # O(S) scratch: far below the reference's 2*heads*S*S bf16 score buffers (block.c:106-131)
+    assert bs.value < 2 * 32 * S * S * 2
+    offs = {}
+    for name in ("hidden_a", "hidden_b", "h_text", "norm_out", "head_out", "t_emb", "te_hidden", "freq",
+                 "freq_bf16", "t_scaled", "xe_stage", "xe_out", "block_scratch", "rope_table"):
+        o = lib.hd_forward_ws_offset(name.encode(), S, S - I, I, 32, 8, 4096, 12288, 128, None)
+        assert o >= 0 and o % 256 == 0 and o < total, name
+        offs[name] = o
+    assert len(set(offs.values())) == len(offs)
+    assert offs["hidden_a"] == 0 and offs["hidden_b"] == S * 4096 * 2
+    assert lib.hd_forward_ws_offset(b"nope", S, S - I, I, 32, 8, 4096, 12288, 128, None) == -1
+    # scratch grows linearly in S
+    b2 = lib.hd_decoder_block_scratch_bytes(2 * S, 32, 8, 4096, 12288, 128)
+    assert abs(b2 - 2 * bs.value) < 8192
+
+
+def test_argument_checks_fail_closed_without_touching_the_gpu(pkg):
+    lib = pkg.lib
+    bb = pkg.BlockBinding()
+    rc = lib.hd_decoder_block(None, None, None, C.byref(bb), None, None, 0, None, None, 16, 32, 8, 4096,
+                              12288, 128, None)
+    assert rc == 6 and b"null argument" in lib.hd_last_error()          # HD_ERR_MISSING
+    fb, ws = pkg.ForwardBinding(), pkg.ForwardWorkspace()
+    rc = lib.hd_forward(C.byref(fb), C.byref(ws), None, 4, None, None, None, 4, None, None, None, 8, 32, 8,
+                        4096, 12288, 128, pkg.TMS_ID, None, None, None)
+    assert rc == 6
+    plan = C.c_void_p()
+    assert lib.hd_sdpa_create(C.byref(plan), 2, 32, 8, 64, 64, 128, 0.088) != 0     # batch != 1
+    assert lib.hd_sdpa_create(C.byref(plan), 1, 32, 8, 64, 64, 64, 0.125) != 0      # head_dim != 128
+    assert lib.hd_sdpa_create_split(C.byref(plan), 1, 32, 8, 64, 65, 128, 0.088) != 0
+    assert lib.hd_sdpa_create_prod(C.byref(plan), 1, 32, 8, 64, 18, 128, 0.088) == 0
+    lib.hd_sdpa_destroy(plan)
+    lib.hd_cuda_clear_error()
+    lib.hd_linear(None, None, None, None, 4, 4, 4, 1)
+    assert b"bad args" in lib.hd_cuda_last_error()
+    lib.hd_cuda_clear_error()
+    assert lib.hd_cuda_last_error() == b""
+    assert lib.hd_lora_merge_gpu(None, 0, None) == 0
+
+
+def test_host_bf16_helpers(pkg):
+    lib = pkg.lib
+    assert lib.hd_f32_to_bf16(1.0) == 0x3F80 and lib.hd_f32_to_bf16(1.01171875) == 0x3F82
+    assert lib.hd_bf16_to_f32(0xC020) == -2.5
+
+
+def test_dev_sigmas_and_seeds(pkg, golden):
+    import json
+    ref = json.load(open(os.path.join(golden, "sigmas_ref.json")))["dev"]
+    assert pkg.dev_sigmas() == ref
+    seeds = {pkg.weight_seed(1234, l, n) for l in range(36) for n in pkg.SLOT_NAMES}
+    seeds |= {pkg.weight_seed(1234, -1, n) for n in pkg.GLOBAL_NAMES}
+    assert len(seeds) == 36 * 11 + 11
+    assert pkg.tensor_shape("gate_proj") == (12288, 4096) and pkg.tensor_shape("k_proj") == (1024, 4096)
+
+
+def test_importing_without_the_library_fails_loudly(pkg, tmp_path):
+    import importlib.util
+    import shutil
+    dst = tmp_path / "o1.c_b200"
+    shutil.copytree(os.path.join(ROOT, "o1.c_b200"), dst, ignore=shutil.ignore_patterns("*.so", "*.o", "csrc"))
+    spec = importlib.util.spec_from_file_location("o1c_nolib", dst / "__init__.py",
+                                                  submodule_search_locations=[str(dst)])
+    mod = importlib.util.module_from_spec(spec)
+    with pytest.raises(ImportError, match="no fallback"):
+        spec.loader.exec_module(mod)

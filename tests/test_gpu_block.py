@@ -1,0 +1,138 @@
+"""One decoder block through the C ABI (hd_decoder_block) against the CPU oracle and, when present,
+the reference's own CUDA build, on identical seeded inputs and random-init weights.
+
+With random-init weights the residual stream dominates the block output, so the branch tensors
+(attn_hidden, mlp_out) and the other internals are gated separately, as o1.c's
+tests/unit/test_block.c:281-302 does, and weight set "B" (norm weights around 1) is used besides the
+N(0,0.02) set so that attention logits are not all ~0."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+import parity
+from parity import seeded_bf16, torch_to_u16, u16_to_torch, assert_close
+
+pytestmark = pytest.mark.gpu
+INTS = ("ln0", "attn_hidden", "attn_resid", "post_ln", "mlp_out")
+
+
+def run_block(pkg, dev, wset, T, gh, gw, seed=1234, xseed=42):
+    w = pkg.Weights(n_layers=1, seed=seed, weight_set=wset, device=dev)
+    eng = pkg.Engine(w, T, gh * gw)
+    pos, ar = pkg.seq_t2i(T, gh, gw)
+    x = seeded_bf16((eng.S, pkg.HIDDEN), xseed)
+    out, ints = eng.block(u16_to_torch(x, dev), pos.to(dev), 0, internals=True)
+    out_fused = eng.block(u16_to_torch(x, dev), pos.to(dev), 0)
+    torch.cuda.synchronize()
+    return w, eng, pos, ar, x, out, ints, out_fused
+
+
+@pytest.mark.parametrize("wset,T,gh,gw", [("B", 24, 8, 12), ("A", 24, 8, 12), ("B", 19, 2, 2), ("B", 7, 15, 11)])
+def test_block_vs_oracle(pkg, dev, wset, T, gh, gw):
+    w, eng, pos, ar, x, out, ints, out_fused = run_block(pkg, dev, wset, T, gh, gw)
+    hw = parity.HostWeights(pkg, 1, 1234, wset)
+    ref_out, ref_ints = parity.oracle_block(hw, 0, x, pos.numpy(), ar)
+    assert_close(torch_to_u16(ints["ln0"]), ref_ints["ln0"], "B", "ln0")
+    assert_close(torch_to_u16(ints["attn_hidden"]), ref_ints["attn_hidden"], "D", "attn_hidden")
+    assert_close(torch_to_u16(ints["attn_resid"]), ref_ints["attn_resid"], "D", "attn_resid")
+    assert_close(torch_to_u16(ints["post_ln"]), ref_ints["post_ln"], "D", "post_ln")
+    assert_close(torch_to_u16(ints["mlp_out"]), ref_ints["mlp_out"], "D", "mlp_out")
+    assert_close(torch_to_u16(out), ref_out, "D", "block output")
+    # fused-epilogue path (no internals) keeps the same rounding points as the exporting path
+    assert_close(out_fused, out, "B", "fused vs unfused block")
+    assert np.abs(torch_to_u16(out_fused).astype(np.int32) - torch_to_u16(out).astype(np.int32)).max() <= 1
+
+
+def _ref_block(pkg, r, dev, w, x, pos, ar, S, production):
+    """The reference's hd_decoder_block (src/model/block.c:137) on the same device weights."""
+    sec = torch.tensor([24, 20, 20], dtype=torch.int64, device=dev)
+    mask = np.empty((S, S), dtype=np.uint16)
+    parity.oracle().orc_prefix_causal_mask(S, ar, parity.np_ptr(mask))
+    md = u16_to_torch(mask, dev)
+    nbytes = r.hd_decoder_block_scratch_bytes(S, 32, 8, 4096, 12288, 128)
+    scratch = torch.empty(nbytes + 256, dtype=torch.uint8, device=dev)
+    out = torch.empty(S, 4096, dtype=torch.bfloat16, device=dev)
+    bufs = {n: torch.empty(S, 4096, dtype=torch.bfloat16, device=dev) for n in INTS}
+    ints = pkg.BlockInternals(**{n: bufs[n].data_ptr() for n in INTS})
+    bb = w.block_binding(0)
+    plan = C.c_void_p()
+    rt = None
+    if production:
+        rt = r.hd_gemm_runtime_init(0, 64 << 20)
+        assert rt, r.hd_cuda_last_error()
+        r.hd_gemm_set_backend(1)
+        assert r.hd_sdpa_create_prod(C.byref(plan), 1, 32, 8, S, ar, 128, 128 ** -0.5) == 0, r.hd_cuda_last_error()
+    else:
+        r.hd_gemm_set_backend(0)
+    rc = r.hd_decoder_block(pkg.ptr(x), pkg.ptr(pos), pkg.ptr(md), C.byref(bb), pkg.ptr(sec), pkg.ptr(scratch),
+                            nbytes, C.byref(ints), pkg.ptr(out), S, 32, 8, 4096, 12288, 128,
+                            plan if production else None)
+    torch.cuda.synchronize()
+    assert rc == 0, r.hd_last_error()
+    if production:
+        r.hd_sdpa_destroy(plan)
+        r.hd_gemm_runtime_destroy(rt)
+    return out, bufs
+
+
+@pytest.mark.parametrize("production", [False, True])
+def test_block_vs_reference_cuda_build(pkg, dev, production):
+    """Pure-source reference path (16x16 GEMM kernel + eager attention) and production path
+    (cuBLASLt + cuDNN SDPA) of the reference itself, same inputs, class D on every exported tensor."""
+    r = parity.reflib()
+    if r is None:
+        pytest.skip("oracle/_ref/libo1ref.so not built")
+    T, gh, gw = 24, 8, 12
+    w, eng, pos, ar, x, out, ints, out_fused = run_block(pkg, dev, "B", T, gh, gw)
+    ref_out, ref_ints = _ref_block(pkg, r, dev, w, u16_to_torch(x, dev), pos.to(dev), ar, eng.S, production)
+    assert_close(ints["ln0"], ref_ints["ln0"], "B", "ln0")
+    for n in ("attn_hidden", "attn_resid", "post_ln", "mlp_out"):
+        assert_close(ints[n], ref_ints[n], "D", n)
+    assert_close(out, ref_out, "D", "block output")
+    assert_close(out_fused, ref_out, "D", "fused block output")
+    # and the CPU oracle agrees with the reference's own CUDA code on the same inputs
+    hw = parity.HostWeights(pkg, 1, 1234, "B")
+    o_out, o_ints = parity.oracle_block(hw, 0, x, pos.numpy(), ar)
+    for n in ("attn_hidden", "mlp_out"):
+        assert_close(o_ints[n], torch_to_u16(ref_ints[n]), "D", f"oracle vs reference {n}")
+    assert_close(o_out, torch_to_u16(ref_out), "D", "oracle vs reference block output")
+
+
+def test_block_c0_shape_vs_reference_production(pkg, dev):
+    """BASELINE config 0: 256 text + 32x32 image tokens, both weight sets, vs the reference's production
+    path (cuBLASLt + cuDNN two-pass SDPA) when available, else vs the CPU oracle on weight set B."""
+    T, gh, gw = 256, 32, 32
+    r = parity.reflib()
+    for wset in ("B", "A"):
+        w, eng, pos, ar, x, out, ints, out_fused = run_block(pkg, dev, wset, T, gh, gw)
+        assert ar == 255 and eng.S == 1280
+        if r is not None:
+            ref_out, ref_ints = _ref_block(pkg, r, dev, w, u16_to_torch(x, dev), pos.to(dev), ar, eng.S, True)
+            for n in ("attn_hidden", "attn_resid", "post_ln", "mlp_out"):
+                assert_close(ints[n], ref_ints[n], "D", f"{wset}:{n}")
+            assert_close(out_fused, ref_out, "D", f"{wset}: block output")
+        elif wset == "B":
+            hw = parity.HostWeights(pkg, 1, 1234, wset)
+            o_out, o_ints = parity.oracle_block(hw, 0, x, pos.numpy(), ar)
+            for n in ("attn_hidden", "mlp_out"):
+                assert_close(torch_to_u16(ints[n]), o_ints[n], "D", n)
+            assert_close(torch_to_u16(out_fused), o_out, "D", "block output")
+        del w, eng
+        torch.cuda.empty_cache()
+
+
+def test_block_argument_errors(pkg, dev):
+    w = pkg.Weights(n_layers=1, device=dev)
+    eng = pkg.Engine(w, 8, 8)
+    x = torch.zeros(16, 4096, dtype=torch.bfloat16, device=dev)
+    pos, _ = pkg.seq_t2i(8, 2, 4)
+    bb = w.block_binding(0)
+    small = torch.empty(1024, dtype=torch.uint8, device=dev)
+    rc = pkg.lib.hd_decoder_block(pkg.ptr(x), pkg.ptr(pos.to(dev)), None, C.byref(bb), None, pkg.ptr(small), 1024,
+                                  None, pkg.ptr(x), 16, 32, 8, 4096, 12288, 128, eng.plan)
+    assert rc == 7 and b"scratch too small" in pkg.lib.hd_last_error()      # HD_ERR_OOM, block.c:153-156
+    rc = pkg.lib.hd_decoder_block(pkg.ptr(x), pkg.ptr(pos.to(dev)), None, C.byref(bb), None, pkg.ptr(small), 1 << 40,
+                                  None, pkg.ptr(x), 16, 32, 8, 4096, 12288, 64, eng.plan)
+    assert rc == 9                                                           # HD_ERR_UNSUPPORTED
