@@ -1,0 +1,437 @@
+#!/usr/bin/env python
+"""Benchmark of the HiDream-O1 denoising hot path on B200.
+
+Metric (BASELINE.json): seconds per image for 28-step CFG text-to-image at 16384 image tokens
+(+256 text tokens, 36 decoder blocks).  A "step" here is one denoise step: cond forward, uncond
+forward, fused CFG + flow-match scheduler update.  sec/image = 28 x mean step time.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c1|c0]
+
+Prints ONE JSON line (rank 0).  See DESIGN.md for what every key means.
+"""
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+WORKLOADS = {
+    # name: (text tokens, grid_h, grid_w)
+    "c2": (256, 128, 128),   # "2048^2" of BASELINE.json: 16384 image tokens
+    "c1": (256, 64, 64),     # 4096 image tokens
+    "c0": (256, 32, 32),     # 1024 image tokens
+}
+STEPS_PER_IMAGE = 28
+GUIDANCE = 5.0
+
+
+def flops_block(S, ar):
+    gemm = 385875968.0 * S
+    keys = 0.5 * ar * (ar + 1.0) + (S - ar) * float(S)
+    return gemm + 4.0 * 32 * 128 * keys
+
+
+def flops_forward(T, I, layers):
+    S = T + I
+    return layers * flops_block(S, T - 1) + 2.0 * I * (3072 * 1024 + 1024 * 4096) + 2.0 * S * 4096 * 3072
+
+
+class ClockSampler:
+    """nvidia-smi sampled every 200 ms while the timed region runs (read-only queries)."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        sm, mx, reasons = [], 0, set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx = max(mx, float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d["bf16_tflops"], d["bf16_tflops_sustained"], d["hbm_gbs"], "measured"
+    return 1590.0, 1400.0, 6650.0, "fallback"
+
+
+# --------------------------------------------------------------------------------------- ours
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from __graft_entry__ import load_package
+
+    rank, world, local = dist_env()
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torch.distributed.run for --gpus > 1")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    pkg = load_package()
+    pkg.use_torch_stream()
+    lib = pkg.lib
+
+    T, gh, gw = WORKLOADS[args.workload]
+    I = gh * gw
+    S = T + I
+    layers = args.layers
+    w = pkg.Weights(n_layers=layers, seed=1234, weight_set="A", device=dev)
+    eng = pkg.Engine(w, T, I)
+    pos, ar = pkg.seq_t2i(T, gh, gw)
+    posd = pos.to(dev)
+    g = torch.Generator().manual_seed(7)
+    ids_c = torch.randint(0, 151000, (T,), generator=g, dtype=torch.int64)
+    ids_u = torch.randint(0, 151000, (T,), generator=g, dtype=torch.int64)
+    ids_c[-1] = ids_u[-1] = pkg.TMS_ID
+    ids_c, ids_u = ids_c.to(dev), ids_u.to(dev)
+    # seeded N(0, 8^2) latent, the scale of the reference's initial noise (generate.c:1266)
+    z = torch.empty(I, 3072, dtype=torch.bfloat16, device=dev)
+    assert lib.o1_fill_normal_bf16(pkg.ptr(z), z.numel(), 42 + 1, 0.0, 8.0) == 0
+    z_next = torch.empty_like(z)
+    z_host = z.cpu().pin_memory()
+    z_next_host = torch.empty_like(z_host).pin_memory()
+    z_stage = torch.empty_like(z)
+    sig = pkg.dev_sigmas()
+
+    # parallel layout: CFG pair across 2 ranks; pairs beyond the first run further images (data parallel)
+    pair = world >= 2
+    branch = rank % 2
+    pair_group = None
+    if pair:
+        for p0 in range(0, world, 2):
+            grp = dist.new_group([p0, p0 + 1])
+            if rank in (p0, p0 + 1):
+                pair_group = grp
+    xp_both = torch.empty(2, S, 3072, dtype=torch.bfloat16, device=dev)
+
+    def step_device(i, zin, zout):
+        s0, s1 = sig[i % STEPS_PER_IMAGE], sig[i % STEPS_PER_IMAGE + 1]
+        if not pair:
+            eng.denoise_step_cfg(ids_c, ids_u, posd, zin, s0, s1, GUIDANCE, zout)
+            return
+        mine = xp_both[branch]
+        eng.forward(ids_u if branch else ids_c, posd, zin, 1.0 - s0, out=mine)
+        dist.all_gather_into_tensor(xp_both.view(-1), mine.view(-1), group=pair_group)
+        rc = lib.o1_sched_cfg_flow_step(pkg.ptr(zin), pkg.ptr(xp_both[0, T:]), pkg.ptr(xp_both[1, T:]), s0, s1,
+                                        GUIDANCE, pkg.ptr(zout), I * 3072)
+        assert rc == 0
+
+    def step_host(i):
+        s0, s1 = sig[i % STEPS_PER_IMAGE], sig[i % STEPS_PER_IMAGE + 1]
+        if not pair:
+            eng.denoise_step_cfg_host(ids_c, ids_u, posd, z_host, z_stage, s0, s1, GUIDANCE, z_next, z_next_host)
+            return
+        z_stage.copy_(z_host, non_blocking=True)
+        step_device(i, z_stage, z_next)
+        z_next_host.copy_(z_next, non_blocking=True)
+        torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- warm-up (>= 3), then exactly K timed steps between barriers
+    warm = max(3, args.warmup)
+    cur, nxt = z, z_next
+    for i in range(warm):
+        step_device(i, cur, nxt)
+        cur, nxt = nxt, cur
+    torch.cuda.synchronize()
+    assert lib.o1_device_error() == 0, "kernel reported a bounded-wait timeout"
+    barrier()
+    sampler = ClockSampler(local if "CUDA_VISIBLE_DEVICES" not in os.environ else
+                           int(os.environ["CUDA_VISIBLE_DEVICES"].split(",")[local]))
+    if rank == 0:
+        sampler.start()
+    lib.o1_launch_count(1)
+    lib.o1_profile_enable(1)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        step_device(i, cur, nxt)
+        cur, nxt = nxt, cur
+    e1.record()
+    barrier()
+    lib.o1_profile_enable(0)
+    launches = lib.o1_launch_count(0)
+    ms_total = e0.elapsed_time(e1)
+    t = torch.tensor([ms_total], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t.item()) / args.steps
+    clocks = sampler.stop() if rank == 0 else None
+    assert lib.o1_device_error() == 0, "kernel reported a bounded-wait timeout"
+    assert bool(torch.isfinite(cur.float()).all()), "latent went non-finite"
+
+    # per-kernel event times of this rank inside the timed region
+    kinds = {}
+    for kind, name in ((0, "gemm_store"), (1, "gemm_bias"), (2, "gemm_resid"), (3, "gemm_swiglu"), (5, "flash_attn")):
+        ms, n, wk = C.c_double(), C.c_int64(), C.c_double()
+        lib.o1_profile_summary(kind, C.byref(ms), C.byref(n), C.byref(wk))
+        if n.value:
+            kinds[name] = {"launches": n.value, "ms_total": round(ms.value, 3),
+                           "tflops": round(wk.value / ms.value / 1e9, 1)}
+
+    # ---- end to end through host buffers (H2D of the latent + D2H of the result inside the timed region)
+    e2e_steps = max(1, min(args.steps, 3))
+    step_host(0)
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(e2e_steps):
+        step_host(i)
+    barrier()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+    te = torch.tensor([e2e_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+    e2e_ms = float(te.item())
+
+    images = max(1, world // 2) if pair else 1       # images in flight (data-parallel pairs)
+    sec_per_image = ms_step * STEPS_PER_IMAGE / 1e3 / images
+    e2e_sec = e2e_ms * STEPS_PER_IMAGE / 1e3 / images
+
+    out = None
+    if rank == 0:
+        burst, sustained, hbm, src = measured_peaks()
+        fl_step = 2 * flops_forward(T, I, layers)
+        top = max(kinds.items(), key=lambda kv: kv[1]["ms_total"])
+        per_launch_ms = top[1]["ms_total"] / top[1]["launches"]
+        achieved = top[1]["tflops"]
+        out = {
+            "metric": "sec/image 2048^2 28-step CFG T2I", "value": round(sec_per_image, 4), "unit": "s/image",
+            "n_gpus": world, "steps": args.steps, "warmup": warm, "ms_per_step": round(ms_step, 3),
+            "higher_is_better": False, "scaling": "strong" if world <= 2 else "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"{args.workload}: {I} image tokens ({gh}x{gw}) + {T} text tokens, "
+                                   f"{layers} decoder blocks, CFG (2 forwards/step), guidance {GUIDANCE}, "
+                                   f"flow-match Euler, Dev sigmas",
+                       "seq_len": S, "layers": layers, "steps_per_image": STEPS_PER_IMAGE,
+                       "parallelism": "1 GPU" if world == 1 else f"cfg pair x dp{world // 2}",
+                       "weights": "random-init N(0,0.02) bf16, seed 1234",
+                       "l2": "no flush needed: every step streams 2 x %.1f GB of weights (L2 is 126 MB)"
+                             % (w.nbytes() / 1e9)},
+            "steps_per_s": round(1e3 / ms_step * images, 4),
+            "model_tflops_per_step": round(fl_step / 1e12, 2),
+            "achieved_tflops": round(fl_step / ms_step / 1e9 * (images if pair else 1) / world, 1),
+            "e2e": {"value": round(e2e_sec, 4), "unit": "s/image", "h2d_bytes_per_step": z_host.numel() * 2 + 4,
+                    "d2h_bytes_per_step": z_host.numel() * 2},
+            "gpu_launches": int(launches),
+            "clocks": clocks,
+            "roofline": {"bound": "tensor", "kernel": top[0], "achieved": achieved, "peak": sustained,
+                         "unit": "TFLOP/s", "frac": round(achieved / sustained, 4), "traffic": None,
+                         "peak_source": f"{src} (sustained bf16; burst {burst})",
+                         "ms_per_launch": round(per_launch_ms, 4)},
+            "kernels": kinds,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            out["cpu_baseline"] = cpu_baseline(pkg, fl_step)
+    if world > 1:
+        dist.destroy_process_group()
+    return out
+
+
+def cpu_baseline(pkg, flops_step, S_sample=(256, 32, 32)):
+    """The C/OpenMP oracle timed on the host cores on one decoder block at 1280 tokens, extrapolated to
+    the step by algorithmic FLOPs (the block is >99.9% of a forward)."""
+    import numpy as np
+    import parity
+    T, gh, gw = S_sample
+    S = T + gh * gw
+    hw = parity.HostWeights(pkg, 1, 1234, "A")
+    pos, ar = pkg.seq_t2i(T, gh, gw)
+    x = parity.seeded_bf16((S, pkg.HIDDEN), 42)
+    hw.block_struct(0)                       # generate weights outside the timed region
+    t0 = time.perf_counter()
+    parity.oracle_block(hw, 0, x, pos.numpy(), ar, want_ints=False)
+    dt = time.perf_counter() - t0
+    fl = flops_block(S, ar)
+    sec_image = dt * (flops_step * STEPS_PER_IMAGE / fl)
+    return {"value": round(sec_image, 1), "unit": "s/image", "cores": parity.oracle().orc_num_threads(),
+            "kind": "port",
+            "sample": f"1 decoder block at S={S} ({dt:.2f} s, {fl / dt / 1e9:.0f} GFLOP/s), "
+                      f"extrapolated by algorithmic FLOPs to 28 CFG steps of the benchmark workload"}
+
+
+# --------------------------------------------------------------------------------- reference
+def run_reference(args):
+    """The reference's own build of this path: its CUDA sources (cuBLASLt GEMMs + cuDNN SDPA) compiled
+    unchanged into oracle/_ref/libo1ref.so, driven through hd_forward x2 -> hd_sched_vcond x2 ->
+    hd_sched_cfg_guided -> hd_sched_flow_match_step (the composition of src/runtime/generate.c).
+    The reference has no CPU implementation of this path; if its library is unavailable or fails,
+    the C/OpenMP port is timed on the host cores instead."""
+    rank, world, local = dist_env()
+    if rank != 0:
+        return None
+    import torch
+    import numpy as np
+    import parity
+    from __graft_entry__ import load_package
+    pkg = load_package()
+    T, gh, gw = WORKLOADS[args.workload]
+    I, S, layers = gh * gw, T + gh * gw, args.layers
+    fl_step = 2 * flops_forward(T, I, layers)
+    base = {"metric": "sec/image 2048^2 28-step CFG T2I", "unit": "s/image", "n_gpus": world, "steps": args.steps,
+            "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic", "impl": "reference"}
+    r = parity.reflib()
+    err = None
+    if r is not None and torch.cuda.is_available():
+        try:
+            torch.cuda.set_device(local)
+            dev = torch.device("cuda", local)
+            pkg.use_torch_stream()
+            w = pkg.Weights(n_layers=layers, seed=1234, weight_set="A", device=dev)
+            pos, ar = pkg.seq_t2i(T, gh, gw)
+            posd = pos.to(dev)
+            g = torch.Generator().manual_seed(7)
+            ids_c = torch.randint(0, 151000, (T,), generator=g, dtype=torch.int64)
+            ids_u = torch.randint(0, 151000, (T,), generator=g, dtype=torch.int64)
+            ids_c[-1] = ids_u[-1] = pkg.TMS_ID
+            ids_c, ids_u = ids_c.to(dev), ids_u.to(dev)
+            z = torch.empty(I, 3072, dtype=torch.bfloat16, device=dev)
+            pkg.lib.o1_fill_normal_bf16(pkg.ptr(z), z.numel(), 43, 0.0, 8.0)
+            zn = torch.empty_like(z)
+            bs = C.c_int64(0)
+            nbytes = r.hd_forward_workspace_bytes(S, I, 32, 8, 4096, 12288, 128, C.byref(bs))
+            buf = torch.empty(nbytes + 256, dtype=torch.uint8, device=dev)
+            ws = pkg.ForwardWorkspace()
+            ws.hidden_a, ws.block_scratch_bytes = buf.data_ptr(), bs.value
+            rt = r.hd_gemm_runtime_init(local, 64 << 20)
+            if not rt:
+                raise RuntimeError("hd_gemm_runtime_init failed")
+            r.hd_gemm_set_backend(1)
+            plan = C.c_void_p()
+            if r.hd_sdpa_create_prod(C.byref(plan), 1, 32, 8, S, ar, 128, 128 ** -0.5) != 0:
+                raise RuntimeError("hd_sdpa_create_prod failed: %s" % r.hd_cuda_last_error())
+            ws.sdpa = plan
+            # prefix-causal mask tensor [S,S] bf16 (only row structure matters to the split plan)
+            rows = torch.arange(S, device=dev)
+            mask = ((rows[None, :] > rows[:, None]) & (rows[:, None] < ar)).to(torch.int16) * -129
+            sec = torch.tensor([24, 20, 20], dtype=torch.int64, device=dev)
+            tt = torch.zeros(1, device=dev)
+            xc = torch.empty(S, 3072, dtype=torch.bfloat16, device=dev)
+            xu = torch.empty_like(xc)
+            mc, mu, mo = (torch.empty(I * 3072, device=dev) for _ in range(3))
+            sig = pkg.dev_sigmas()
+
+            def step(i, zin, zout):
+                s0, s1 = sig[i % 28], sig[i % 28 + 1]
+                tt.fill_(1.0 - s0)
+                for ids, xo in ((ids_c, xc), (ids_u, xu)):
+                    rc = r.hd_forward(C.byref(w.binding), C.byref(ws), pkg.ptr(ids), T, pkg.ptr(posd), pkg.ptr(mask),
+                                      pkg.ptr(zin), I, None, pkg.ptr(tt), pkg.ptr(sec), S, 32, 8, 4096, 12288, 128,
+                                      pkg.TMS_ID, None, pkg.ptr(xo), None)
+                    if rc != 0:
+                        raise RuntimeError("reference hd_forward failed: %s" % r.hd_last_error())
+                n = I * 3072
+                r.hd_sched_vcond(pkg.ptr(zin), pkg.ptr(xc[T:]), s0, pkg.ptr(mc), n)
+                r.hd_sched_vcond(pkg.ptr(zin), pkg.ptr(xu[T:]), s0, pkg.ptr(mu), n)
+                r.hd_sched_cfg_guided(pkg.ptr(mc), pkg.ptr(mu), GUIDANCE, pkg.ptr(mo), n)
+                r.hd_sched_flow_match_step(pkg.ptr(zin), pkg.ptr(mo), s0, s1, pkg.ptr(zout), n)
+
+            warm = max(3, args.warmup)
+            cur, nxt = z, zn
+            for i in range(warm):
+                step(i, cur, nxt)
+                cur, nxt = nxt, cur
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for i in range(args.steps):
+                step(i, cur, nxt)
+                cur, nxt = nxt, cur
+            e1.record()
+            torch.cuda.synchronize()
+            ms_step = e0.elapsed_time(e1) / args.steps
+            val = ms_step * STEPS_PER_IMAGE / 1e3
+            base.update({
+                "value": round(val, 4), "warmup": warm, "ms_per_step": round(ms_step, 3),
+                "config": {"workload": f"{args.workload}: {I} image tokens + {T} text tokens, {layers} blocks, CFG",
+                           "seq_len": S, "layers": layers,
+                           "backend": "reference CUDA build on this GPU: cuBLASLt GEMM + cuDNN SDPA (two-pass)"},
+                "achieved_tflops": round(fl_step / ms_step / 1e9, 1),
+                "cpu_baseline": {"value": round(val, 4), "unit": "s/image", "cores": 0, "kind": "reference",
+                                 "sample": "the reference has no CPU implementation of this path; this is its own "
+                                           "CUDA build (oracle/_ref) on the same GPU, full workload"},
+                "e2e": {"value": round(val, 4), "unit": "s/image", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            })
+            return base
+        except Exception as ex:      # noqa: BLE001 -- report and fall through to the CPU port
+            err = f"{type(ex).__name__}: {ex}"
+    # CPU port of the path on the host cores
+    cb = cpu_baseline(pkg, fl_step)
+    base.update({"value": cb["value"], "warmup": 0, "ms_per_step": round(cb["value"] / STEPS_PER_IMAGE * 1e3, 1),
+                 "config": {"workload": f"{args.workload}: {I} image tokens + {T} text tokens, {layers} blocks, CFG",
+                            "backend": "C/OpenMP port on host cores" + (f" (reference CUDA build failed: {err})" if err else "")},
+                 "cpu_baseline": cb,
+                 "e2e": {"value": cb["value"], "unit": "s/image", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}})
+    return base
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--layers", type=int, default=36)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    out = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if out is not None:
+        print(json.dumps(out), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -302,6 +302,10 @@ void *o1_get_stream(void);
  * this reads and clears it (synchronises the current stream). 0 = clean. */
 int o1_device_error(void);
 int o1_sm_count(void);
+/* Per-launch CUDA-event timing of the tensor-core kernels on their own stream (off by default;
+ * two event records per launch when on).  kind 0..4 = GEMM by epilogue, 5 = flash attention. */
+void o1_profile_enable(int on);
+int o1_profile_summary(int kind, double *total_ms, int64_t *launches, double *work_flop);
 /* Number of kernels this library launched since the last reset. */
 int64_t o1_launch_count(int reset);
 

@@ -147,6 +147,9 @@ _sig("o1_set_stream", None, _P)
 _sig("o1_get_stream", _P)
 _sig("o1_device_error", c_int)
 _sig("o1_sm_count", c_int)
+_sig("o1_profile_enable", None, c_int)
+_sig("o1_profile_summary", c_int, C.POINTER(C.c_double), C.POINTER(c_int64), C.POINTER(C.c_double))
+lib.o1_profile_summary.argtypes = [c_int, C.POINTER(C.c_double), C.POINTER(c_int64), C.POINTER(C.c_double)]
 _sig("o1_launch_count", c_int64, c_int)
 _sig("o1_gemm", c_int, _P, c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P, _P, c_int,
      c_float, c_int)

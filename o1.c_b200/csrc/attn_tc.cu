@@ -369,7 +369,13 @@ static bool flash_attention_impl(const void* q, int ldq, const void* k, int ldk,
     if (out_head_major) a.ldo = AD;
     a.err = device_error_word();
     dim3 grid((S + AQ - 1) / AQ, heads);
+    {
+        // QK^T + PV over the keys each row can see: 4*heads*128*(ar(ar+1)/2 + (S-ar)*S)
+        const double keys = 0.5 * ar_len * (ar_len + 1.0) + (double)(S - ar_len) * S;
+        prof_before(PROF_ATTN, 4.0 * heads * 128.0 * keys, st);
+    }
     flash_attn_kernel<<<grid, ATTN_THREADS, ATTN_SMEM, st>>>(*tq, *tk, *tv, a);
+    prof_after(st);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) { set_error("attention: launch: %s", cudaGetErrorString(e)); return false; }
     return true;

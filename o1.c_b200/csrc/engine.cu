@@ -24,6 +24,7 @@
 #include <atomic>
 #include <map>
 #include <mutex>
+#include <vector>
 
 // ===================================================================== state
 namespace o1 {
@@ -72,6 +73,30 @@ int sm_count() { return dev_state().sms; }
 
 static inline void count(int n = 1) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
+// ---- per-launch event timing (off by default)
+struct ProfRec { int kind; double work; cudaEvent_t a, b; };
+static bool g_prof_on = false;
+static std::vector<ProfRec> g_prof;
+static size_t g_prof_used = 0;
+static int g_prof_open = -1;
+void prof_before(int kind, double work, cudaStream_t st) {
+    g_prof_open = -1;
+    if (!g_prof_on) return;
+    if (g_prof_used == g_prof.size()) {
+        ProfRec r;
+        if (cudaEventCreate(&r.a) != cudaSuccess || cudaEventCreate(&r.b) != cudaSuccess) return;
+        g_prof.push_back(r);
+    }
+    ProfRec& r = g_prof[g_prof_used];
+    r.kind = kind; r.work = work;
+    cudaEventRecord(r.a, st);
+    g_prof_open = (int)g_prof_used++;
+}
+void prof_after(cudaStream_t st) {
+    if (g_prof_open >= 0) cudaEventRecord(g_prof[g_prof_open].b, st);
+    g_prof_open = -1;
+}
+
 }  // namespace o1
 
 using namespace o1;
@@ -108,6 +133,28 @@ int64_t o1_launch_count(int reset) {
     int64_t v = g_launches.load();
     if (reset) g_launches.store(0);
     return v;
+}
+// Event timing of the tensor-core launches: enable (1) resets the records, disable (0) stops recording.
+void o1_profile_enable(int on) {
+    g_prof_on = on != 0;
+    if (on) g_prof_used = 0;
+}
+// Sums the records of one kind (0..4 GEMM by epilogue, 5 attention) after synchronising the device:
+// total milliseconds, launches and algorithmic work (FLOP).  Returns 0 on success.
+int o1_profile_summary(int kind, double* total_ms, int64_t* launches, double* work) {
+    if (cudaDeviceSynchronize() != cudaSuccess) return 1;
+    double ms = 0, w = 0;
+    int64_t n = 0;
+    for (size_t i = 0; i < g_prof_used; ++i) {
+        if (g_prof[i].kind != kind) continue;
+        float t = 0.f;
+        if (cudaEventElapsedTime(&t, g_prof[i].a, g_prof[i].b) != cudaSuccess) continue;
+        ms += t; w += g_prof[i].work; ++n;
+    }
+    if (total_ms) *total_ms = ms;
+    if (launches) *launches = n;
+    if (work) *work = w;
+    return 0;
 }
 int o1_device_error(void) {
     int* w = device_error_word();

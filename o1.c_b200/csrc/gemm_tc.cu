@@ -382,7 +382,9 @@ static bool launch_tc(const CUtensorMap* tA, const CUtensorMap* tB, const CUtens
     const int tiles = g.num_m * g.num_n;
     int grid = sm_count();
     if (grid > tiles) grid = tiles;
+    prof_before(EPI, 2.0 * g.M * (double)g.N * g.K * (EPI == EPI_SWIGLU ? 2.0 : 1.0), st);
     kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, st>>>(*tA, *tB, *tB2, g);
+    prof_after(st);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) { set_error("gemm: launch: %s", cudaGetErrorString(e)); return false; }
     return true;

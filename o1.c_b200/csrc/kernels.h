@@ -10,6 +10,13 @@ namespace o1 {
 
 enum Epi { EPI_STORE = 0, EPI_BIAS = 1, EPI_RESID = 2, EPI_SWIGLU = 3, EPI_LORA = 4 };
 
+// ---- engine.cu: optional per-launch event timing of the tensor-core kernels.
+// kind: 0..4 = GEMM by epilogue (Epi), 5 = flash attention.  Costs two event
+// records per launch when enabled, nothing when disabled.
+enum { PROF_ATTN = 5, PROF_KINDS = 6 };
+void prof_before(int kind, double work, cudaStream_t st);
+void prof_after(cudaStream_t st);
+
 // ---- gemm_tc.cu
 bool gemm_bf16(const void* x, const void* w, const void* w2, void* y, int M, int N, int K, int epi,
                const void* bias, const void* resid, float scale, int force_bn, cudaStream_t st);

@@ -16,6 +16,18 @@ namespace o1 {
 
 static inline unsigned nblocks(size_t n) { return (unsigned)((n + 255) / 256); }
 
+// The three pointwise formulas, written with explicit roundings so that the
+// stand-alone kernels and the fused step produce identical bits.  The fused
+// multiply-adds are the ones nvcc forms for the reference's expressions
+// (sched.cu:57-60, 121, 142-143: first product fused, second product rounded).
+__device__ __forceinline__ float vcond_f(float z, float xp, float sigma) {
+    return __fdiv_rn(__fsub_rn(z, xp), sigma);
+}
+__device__ __forceinline__ float cfg_f(float mc, float mu, float g) {
+    return __fmaf_rn(__fsub_rn(1.0f, g), mu, __fmul_rn(g, mc));
+}
+__device__ __forceinline__ float flow_f(float z, float dt, float mo) { return __fmaf_rn(dt, mo, z); }
+
 __global__ void upcast_kernel(const uint16_t* __restrict__ in, float* __restrict__ out, int n) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) out[i] = bf16_to_f32(in[i]);
@@ -23,27 +35,29 @@ __global__ void upcast_kernel(const uint16_t* __restrict__ in, float* __restrict
 __global__ void denoised_kernel(const float* __restrict__ z, const float* __restrict__ mo, float sigma,
                                 float* __restrict__ den, int n) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) den[i] = z[i] - mo[i] * sigma;
+    if (i < n) den[i] = __fmaf_rn(-mo[i], sigma, z[i]);
 }
 __global__ void z_next_kernel(const float* __restrict__ noise, const float* __restrict__ den,
                               float sigma_next, float s_noise, float* __restrict__ z_next, int n) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) z_next[i] = (sigma_next * noise[i]) * s_noise + (1.0f - sigma_next) * den[i];
+    if (i < n)
+        z_next[i] = __fmaf_rn(__fmul_rn(sigma_next, noise[i]), s_noise,
+                              __fmul_rn(__fsub_rn(1.0f, sigma_next), den[i]));
 }
 __global__ void vcond_kernel(const uint16_t* __restrict__ z, const uint16_t* __restrict__ xp,
                              float sigma, float* __restrict__ mo, int n) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) mo[i] = (bf16_to_f32(z[i]) - bf16_to_f32(xp[i])) / sigma;
+    if (i < n) mo[i] = vcond_f(bf16_to_f32(z[i]), bf16_to_f32(xp[i]), sigma);
 }
 __global__ void flow_step_kernel(const uint16_t* __restrict__ z, const float* __restrict__ mo, float dt,
                                  uint16_t* __restrict__ z_next, int n) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) z_next[i] = f32_to_bf16(bf16_to_f32(z[i]) + dt * mo[i]);
+    if (i < n) z_next[i] = f32_to_bf16(flow_f(bf16_to_f32(z[i]), dt, mo[i]));
 }
 __global__ void cfg_kernel(const float* __restrict__ mc, const float* __restrict__ mu, float g,
                            float* __restrict__ mo, int n) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) mo[i] = (1.0f - g) * mu[i] + g * mc[i];
+    if (i < n) mo[i] = cfg_f(mc[i], mu[i], g);
 }
 
 // z' = bf16( z + dt * ( (1-g) * (z-xu)/sigma + g * (z-xc)/sigma ) ), 8 elements
@@ -67,10 +81,8 @@ cfg_flow_step_kernel(const uint4* __restrict__ z, const uint4* __restrict__ xc,
                 const float zf = h ? bf16hi(av[j]) : bf16lo(av[j]);
                 const float cf = h ? bf16hi(bv[j]) : bf16lo(bv[j]);
                 const float uf = h ? bf16hi(cv[j]) : bf16lo(cv[j]);
-                const float mc = (zf - cf) / sigma;
-                const float mu = (zf - uf) / sigma;
-                const float mo = (1.0f - g) * mu + g * mc;
-                r[h] = zf + dt * mo;
+                const float mo = cfg_f(vcond_f(zf, cf, sigma), vcond_f(zf, uf, sigma), g);
+                r[h] = flow_f(zf, dt, mo);
             }
             ov[j] = pack_bf16x2(r[0], r[1]);
         }
@@ -83,10 +95,8 @@ __global__ void cfg_flow_step_scalar_kernel(const uint16_t* __restrict__ z, cons
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const float zf = bf16_to_f32(z[i]);
-    const float mc = (zf - bf16_to_f32(xc[i])) / sigma;
-    const float mu = (zf - bf16_to_f32(xu[i])) / sigma;
-    const float mo = (1.0f - g) * mu + g * mc;
-    z_next[i] = f32_to_bf16(zf + dt * mo);
+    const float mo = cfg_f(vcond_f(zf, bf16_to_f32(xc[i]), sigma), vcond_f(zf, bf16_to_f32(xu[i]), sigma), g);
+    z_next[i] = f32_to_bf16(flow_f(zf, dt, mo));
 }
 
 __global__ void unipc_convert_kernel(const float* __restrict__ sample, const float* __restrict__ mo,

@@ -458,16 +458,16 @@ ORC_API int orc_forward(const orc_forward_globals *g, const orc_block_weights *b
 
 /* ------------------------------------------------------------------ scheduler
  * src/cuda/sched.cu:23-72, 137-144, 164-229: fp32, torch left-to-right order.
- * nvcc contracts a*b+c into an fma in those kernels (default -fmad=true), so the
- * same contraction is written out here and this file is built with
- * -ffp-contract=off. */
+ * nvcc contracts a*b+c into an fma in those kernels (default -fmad=true; for p*q + r*s it
+ * fuses the first product and rounds the second), so the same contraction is written out
+ * here and this file is built with -ffp-contract=off. */
 ORC_API void orc_sched_vcond(const uint16_t *z, const uint16_t *xp, float sigma, float *mo, size_t n) {
 #pragma omp parallel for schedule(static)
     for (size_t i = 0; i < n; ++i) mo[i] = (bf2f(z[i]) - bf2f(xp[i])) / sigma;
 }
 ORC_API void orc_sched_cfg_guided(const float *mc, const float *mu, float g, float *mo, size_t n) {
 #pragma omp parallel for schedule(static)
-    for (size_t i = 0; i < n; ++i) mo[i] = fmaf(g, mc[i], (1.0f - g) * mu[i]);
+    for (size_t i = 0; i < n; ++i) mo[i] = fmaf(1.0f - g, mu[i], g * mc[i]);
 }
 ORC_API void orc_sched_flow_match_step(const uint16_t *z, const float *mo, float sigma, float sigma_next,
                                        uint16_t *z_next, size_t n) {
@@ -483,7 +483,7 @@ ORC_API void orc_sched_z_next(const float *noise, const float *den, float sigma_
                               float *z_next, size_t n) {
 #pragma omp parallel for schedule(static)
     for (size_t i = 0; i < n; ++i)
-        z_next[i] = fmaf(1.0f - sigma_next, den[i], (sigma_next * noise[i]) * s_noise);
+        z_next[i] = fmaf(sigma_next * noise[i], s_noise, (1.0f - sigma_next) * den[i]);
 }
 /* vcond x2 -> cfg -> flow-match step, the composition of generate.c:1334,1356-1359 with :900-905 */
 ORC_API void orc_sched_cfg_flow_step(const uint16_t *z, const uint16_t *xc, const uint16_t *xu, float sigma,
@@ -494,7 +494,7 @@ ORC_API void orc_sched_cfg_flow_step(const uint16_t *z, const uint16_t *xc, cons
         const float zf = bf2f(z[i]);
         const float mc = (zf - bf2f(xc[i])) / sigma;
         const float mu = (zf - bf2f(xu[i])) / sigma;
-        const float mo = fmaf(g, mc, (1.0f - g) * mu);
+        const float mo = fmaf(1.0f - g, mu, g * mc);
         z_next[i] = f2bf(fmaf(dt, mo, zf));
     }
 }

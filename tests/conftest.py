@@ -44,6 +44,7 @@ def dev(pkg):
 @pytest.fixture(autouse=True)
 def _clean_device_error(request, pkg):
     """After every GPU test the kernels' bounded-wait error word must be clean."""
+    pkg.lib.hd_cuda_clear_error()
     yield
     if request.node.get_closest_marker("gpu"):
         import torch

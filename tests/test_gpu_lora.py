@@ -1,6 +1,11 @@
 """Load-time LoRA merge (hd_lora_merge_gpu, o1.c include/hd_lora.h:71-79) against the FP32 restatement
-of src/model/lora_merge.cu:26-109: the merged bf16 weights must be bit-identical except where
-scale*delta lands on a rounding tie of the FP32 sum (counted, must be a vanishing fraction)."""
+of the documented contract W' = bf16(f32(W) + multiplier*alpha/rank * up@down) (hd_lora.h:10-14,
+lora_merge.cu:26-33): the merged bf16 weights must be bit-identical except where the FP32 sum lands on
+a rounding tie (counted, must be a vanishing fraction).
+
+The reference's own GPU merge is NOT run here: its cublasSgemm call passes the row-major up-chunk
+with leading dimension C instead of rank (lora_merge.cu:86-93), which reads beyond the adapter
+buffer whenever out_dim != rank."""
 import ctypes as C
 
 import numpy as np
@@ -11,6 +16,17 @@ import parity
 from parity import np_ptr, seeded_bf16, torch_to_u16, u16_to_torch
 
 pytestmark = pytest.mark.gpu
+
+
+def check_merged(got, ref, w0, max_frac=2e-4):
+    """Bit-identical except on rounding ties: where the two FP32 sums round to different bf16 values
+    they must be neighbours at the scale of the operands (one bf16 ulp of max(|W|, |W'|)), and such
+    elements must be a vanishing fraction."""
+    g, r_, w = (parity.bf16_to_f32_np(a).astype(np.float64) for a in (got, ref, w0))
+    neq = got != ref
+    assert neq.mean() <= max_frac, f"{neq.mean():.2e} of the merged weights differ"
+    ulp = np.maximum(np.abs(w), np.abs(r_)) * 2.0 ** -7 + 1e-30
+    assert (np.abs(g - r_) <= ulp).all()
 
 
 def entry(pkg, w, up, down, R, K, N, alpha, mult):
@@ -40,17 +56,7 @@ def test_lora_merge(pkg, orc, dev, N, K, R):
     orc.orc_lora_merge(np_ptr(ref), np_ptr(up), np_ptr(down), N, K, R, mult * alpha / R)
     got = torch_to_u16(wd)
     assert (got != w0).mean() > 0.01, "merge changed nothing"
-    diff = got.astype(np.int32) - ref.astype(np.int32)
-    assert np.abs(diff).max() <= 1
-    assert (diff != 0).mean() <= 2e-4, f"{(diff != 0).mean():.2e} of the weights differ by one bf16 ulp"
-    r = parity.reflib()
-    if r is not None:
-        w2 = u16_to_torch(w0, dev)
-        ents2 = (pkg.LoraEntry * 1)(entry(pkg, w2, upd, dnd, R, K, N, alpha, mult))
-        assert r.hd_lora_merge_gpu(ents2, 1, None) == 0
-        torch.cuda.synchronize()
-        d2 = torch_to_u16(w2).astype(np.int32) - got.astype(np.int32)
-        assert np.abs(d2).max() <= 1 and (d2 != 0).mean() <= 2e-4, "vs reference cublasSgemm merge"
+    check_merged(got, ref, w0)
 
 
 def test_lora_sequential_adapters_and_errors(pkg, orc, dev):
@@ -71,7 +77,6 @@ def test_lora_sequential_adapters_and_errors(pkg, orc, dev):
     ref = w0.copy()
     orc.orc_lora_merge(np_ptr(ref), np_ptr(ups[0]), np_ptr(dns[0]), N, K, R, 1.0 * 4.0 / R)
     orc.orc_lora_merge(np_ptr(ref), np_ptr(ups[1]), np_ptr(dns[1]), N, K, R, 0.5 * 8.0 / R)
-    diff = torch_to_u16(wd).astype(np.int32) - ref.astype(np.int32)
-    assert np.abs(diff).max() <= 1 and (diff != 0).mean() <= 5e-4
+    check_merged(torch_to_u16(wd), ref, w0, 5e-4)
     bad = (pkg.LoraEntry * 1)(entry(pkg, wd, keep[0], keep[2], 0, K, N, 4.0, 1.0))
     assert pkg.lib.hd_lora_merge_gpu(bad, 1, None) == 5          # HD_ERR_MISMATCH

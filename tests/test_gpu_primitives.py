@@ -14,8 +14,21 @@ from parity import np_ptr, seeded_bf16, torch_to_u16, u16_to_torch, assert_close
 pytestmark = pytest.mark.gpu
 
 
+_KEEP = []
+
+
+@pytest.fixture(autouse=True)
+def _release_device_temporaries():
+    yield
+    _KEEP.clear()
+
+
 def dv(a, dev):
-    return u16_to_torch(a, dev) if a.dtype == np.uint16 else torch.from_numpy(a).to(dev)
+    """Host array -> device tensor that stays alive until the test ends (its address is handed to
+    asynchronous kernels, so it must not return to the allocator mid-test)."""
+    t = u16_to_torch(a, dev) if a.dtype == np.uint16 else torch.from_numpy(a).to(dev)
+    _KEEP.append(t)
+    return t
 
 
 def empty_bf16(shape, dev):
@@ -37,7 +50,9 @@ def test_rmsnorm(pkg, orc, dev, rows, cols):
     orc.orc_rmsnorm(np_ptr(x), np_ptr(w), np_ptr(ref), rows, cols, 1e-6)
     assert_close(torch_to_u16(y), ref, "B", "rmsnorm")
     r = parity.reflib()
-    if r is not None:
+    # The reference kernel reduces with a halving tree over min(cols,256) threads (norm.cu:31-35), which
+    # only sums every element when that count is a power of two: compare against it for those shapes.
+    if r is not None and (cols >= 256 or (cols & (cols - 1)) == 0):
         y2 = empty_bf16((rows, cols), dev)
         r.hd_rmsnorm(pkg.ptr(dv(x, dev)), pkg.ptr(dv(w, dev)), pkg.ptr(y2), rows, cols, 1e-6)
         torch.cuda.synchronize()
@@ -165,7 +180,9 @@ def test_timestep_and_mrope(pkg, orc, dev):
     done(pkg, "timestep_embed")
     ref = np.empty((2, 256), dtype=np.float32)
     orc.orc_timestep_embed(np_ptr(t), np_ptr(ref), 2, 256)
-    assert np.abs(y.cpu().numpy() - ref).max() <= 2e-6
+    # t*freq reaches 500 rad; one ulp of expf in freq moves the angle by ~3e-5
+    assert np.abs(y.cpu().numpy() - ref).max() <= 1e-4
+    assert_close(y.cpu().numpy(), ref, "B", "timestep_embed")
     S = 23 + 48
     pos, _ = pkg.seq_t2i(23, 6, 8)
     sec = torch.tensor([24, 20, 20], dtype=torch.int64, device=dev)
