@@ -181,7 +181,7 @@ def run_ours(args):
         torch.cuda.synchronize()
 
     # ---- warm-up (>= 3), then exactly K timed steps between barriers
-    warm = max(3, args.warmup)
+    warm = args.warmup if args.short else max(3, args.warmup)
     cur, nxt = z, z_next
     for i in range(warm):
         step_device(i, cur, nxt)
@@ -223,14 +223,16 @@ def run_ours(args):
                            "tflops": round(wk.value / ms.value / 1e9, 1)}
 
     # ---- end to end through host buffers (H2D of the latent + D2H of the result inside the timed region)
-    e2e_steps = max(1, min(args.steps, 3))
-    step_host(0)
-    barrier()
-    t0 = time.perf_counter()
-    for i in range(e2e_steps):
-        step_host(i)
-    barrier()
-    e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+    e2e_steps = 0 if args.short else max(1, min(args.steps, 3))
+    e2e_ms = float("nan")
+    if e2e_steps:
+        step_host(0)
+        barrier()
+        t0 = time.perf_counter()
+        for i in range(e2e_steps):
+            step_host(i)
+        barrier()
+        e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
     te = torch.tensor([e2e_ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(te, op=dist.ReduceOp.MAX)
@@ -273,7 +275,10 @@ def run_ours(args):
                          "ms_per_launch": round(per_launch_ms, 4)},
             "kernels": kinds,
         }
-        if world == 1 and not args.no_cpu_baseline:
+        if args.short:
+            out["short_profiler_run"] = True
+            out.pop("e2e")
+        if world == 1 and not args.no_cpu_baseline and not args.short:
             out["cpu_baseline"] = cpu_baseline(pkg, fl_step)
     if world > 1:
         dist.destroy_process_group()
@@ -427,6 +432,9 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--layers", type=int, default=36)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--short", action="store_true",
+                    help="profiler runs only: take --warmup literally, skip the end-to-end and CPU legs "
+                         "(a number from such a run is not a benchmark value)")
     args = ap.parse_args()
     out = run_reference(args) if args.impl == "reference" else run_ours(args)
     if out is not None:

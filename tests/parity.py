@@ -353,9 +353,9 @@ def smoke_check(pkg, device):
         assert_close(torch_to_u16(ints[n]), ref_ints[n], "D", f"smoke {n}")
     n = 4096
     z, xc, xu = (seeded_bf16(n, 7), seeded_bf16(n, 8), seeded_bf16(n, 9))
+    zd, cd, ud = (u16_to_torch(a, device) for a in (z, xc, xu))     # kept alive across the async launch
     zn = torch.empty(n, dtype=torch.bfloat16, device=device)
-    rc = pkg.lib.o1_sched_cfg_flow_step(pkg.ptr(u16_to_torch(z, device)), pkg.ptr(u16_to_torch(xc, device)),
-                                        pkg.ptr(u16_to_torch(xu, device)), 0.9, 0.8, 5.0, pkg.ptr(zn), n)
+    rc = pkg.lib.o1_sched_cfg_flow_step(pkg.ptr(zd), pkg.ptr(cd), pkg.ptr(ud), 0.9, 0.8, 5.0, pkg.ptr(zn), n)
     assert rc == 0
     torch.cuda.synchronize()
     ref = np.empty(n, dtype=np.uint16)
