@@ -331,6 +331,17 @@ int o1_fill_normal_bf16(void *dst, size_t n, uint64_t seed, float mean, float st
 int o1_fill_normal_f32(float *dst, size_t n, uint64_t seed, float mean, float std);
 float o1_hash_normal_host(uint64_t seed, uint64_t index);
 
+/* No counterpart in the reference.  Merges ONE LoRA target, W = bf16(f32(W) + scale * up@down), without
+ * allocating device memory: its FP32 delta scratch is a fixed 16 MiB array inside the library (held by
+ * every GPU that loads it).  For hosts that cannot call cudaMalloc: all HBM already owned by their own
+ * pool, or other streams busy so that the device-wide stall of cudaMalloc/cudaFree is not acceptable.
+ * base_dev [out_dim,in_dim] bf16 (in place), up_dev [out_dim,rank] fp32, down_dev [rank,in_dim] fp32,
+ * scale = multiplier*alpha/rank.  Limits: in_dim <= 262144, rank <= 4096, else HD_ERR_UNSUPPORTED.
+ * The first call on a device looks up the scratch address (cudaGetSymbolAddress): make that call
+ * before any stream capture.  All calls share the scratch: calls that overlap on the GPU race. */
+hd_status o1_lora_merge_static(void *base_dev, const float *up_dev, const float *down_dev, uint32_t out_dim,
+                               uint32_t in_dim, uint32_t rank, float scale, void *stream);
+
 /* One CFG denoise step on device-resident state: x_c = forward(ids_cond),
  * x_u = forward(ids_uncond), z' = cfg_flow_step(z, x_c, x_u).  Composition of
  * src/runtime/generate.c:1314-1360 with the flow-match update of :900-905.

@@ -143,6 +143,7 @@ _sig("hd_forward", c_int, C.POINTER(ForwardBinding), C.POINTER(ForwardWorkspace)
      _P, c_int, C.POINTER(VisualCond), _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
      C.POINTER(ForwardDiagnostics), _P, _P)
 _sig("hd_lora_merge_gpu", c_int, C.POINTER(LoraEntry), c_size_t, _P)
+_sig("o1_lora_merge_static", c_int, _P, _P, _P, C.c_uint32, C.c_uint32, C.c_uint32, c_float, _P)
 _sig("o1_set_stream", None, _P)
 _sig("o1_get_stream", _P)
 _sig("o1_device_error", c_int)
