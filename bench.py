@@ -142,27 +142,56 @@ def run_ours(args):
     z_stage = torch.empty_like(z)
     sig = pkg.dev_sigmas()
 
-    # parallel layout: CFG pair across 2 ranks; pairs beyond the first run further images (data parallel)
+    # parallel layout (o1c_b200.sp.layout): 2 GPUs = CFG pair; 4 / 8 GPUs = CFG pair x Ulysses SP 2 / 4 on ONE
+    # image.  Rank pairs with equal sp_rank all-gather their predictions and apply the same scheduler kernel.
+    from o1c_b200 import sp as spmod
+    lay, sp_size = spmod.layout(world, cfg=True)
+    image_id, branch, sp_rank = lay[rank]
     pair = world >= 2
-    branch = rank % 2
-    pair_group = None
+    cfg_group = sp_group = None
     if pair:
-        for p0 in range(0, world, 2):
-            grp = dist.new_group([p0, p0 + 1])
-            if rank in (p0, p0 + 1):
-                pair_group = grp
-    xp_both = torch.empty(2, S, 3072, dtype=torch.bfloat16, device=dev)
+        for key in sorted({(v[0], v[2]) for v in lay.values()}):
+            members = sorted(r for r, v in lay.items() if (v[0], v[2]) == key)
+            grp = dist.new_group(members)
+            if rank in members:
+                cfg_group = grp
+        for key in sorted({(v[0], v[1]) for v in lay.values()}):
+            members = sorted(r for r, v in lay.items() if (v[0], v[1]) == key)
+            grp = dist.new_group(members)
+            if rank in members:
+                sp_group = grp
+    n_images = len({v[0] for v in lay.values()})
+    if sp_size > 1:
+        del eng
+        torch.cuda.empty_cache()
+        eng = spmod.EngineSP(w, T, I, sp_size, sp_rank, spmod.nccl_exchange(sp_group))
+        i0, i1, n_text_local = eng.i0, eng.i1, eng.t1 - eng.t0
+        z, z_next = z[i0:i1].contiguous(), z_next[i0:i1].contiguous()
+        z_host = z.cpu().pin_memory()
+        z_next_host = torch.empty_like(z_host).pin_memory()
+        z_stage = torch.empty_like(z)
+        xp_local = torch.empty(eng.rows, 3072, dtype=torch.bfloat16, device=dev)
+        xp_pair = torch.empty(2, i1 - i0, 3072, dtype=torch.bfloat16, device=dev)
+    xp_both = torch.empty(2, S, 3072, dtype=torch.bfloat16, device=dev) if (pair and sp_size == 1) else None
 
     def step_device(i, zin, zout):
         s0, s1 = sig[i % STEPS_PER_IMAGE], sig[i % STEPS_PER_IMAGE + 1]
         if not pair:
             eng.denoise_step_cfg(ids_c, ids_u, posd, zin, s0, s1, GUIDANCE, zout)
             return
-        mine = xp_both[branch]
-        eng.forward(ids_u if branch else ids_c, posd, zin, 1.0 - s0, out=mine)
-        dist.all_gather_into_tensor(xp_both.view(-1), mine.view(-1), group=pair_group)
-        rc = lib.o1_sched_cfg_flow_step(pkg.ptr(zin), pkg.ptr(xp_both[0, T:]), pkg.ptr(xp_both[1, T:]), s0, s1,
-                                        GUIDANCE, pkg.ptr(zout), I * 3072)
+        ids_b = ids_u if branch else ids_c
+        if sp_size == 1:
+            mine = xp_both[branch]
+            eng.forward(ids_b, posd, zin, 1.0 - s0, out=mine)
+            dist.all_gather_into_tensor(xp_both.view(-1), mine.view(-1), group=cfg_group)
+            rc = lib.o1_sched_cfg_flow_step(pkg.ptr(zin), pkg.ptr(xp_both[0, T:]), pkg.ptr(xp_both[1, T:]), s0, s1,
+                                            GUIDANCE, pkg.ptr(zout), I * 3072)
+        else:
+            eng.forward(ids_b, posd, zin if zin.numel() else None, 1.0 - s0, out_local=xp_local)
+            mine = xp_local[n_text_local:]
+            dist.all_gather_into_tensor(xp_pair.view(-1), mine.reshape(-1), group=cfg_group)
+            rc = lib.o1_sched_cfg_flow_step(pkg.ptr(zin), pkg.ptr(xp_pair[0]), pkg.ptr(xp_pair[1]), s0, s1,
+                                            GUIDANCE, pkg.ptr(zout), zin.numel()) if zin.numel() else 0
         assert rc == 0
 
     def step_host(i):
@@ -238,7 +267,7 @@ def run_ours(args):
         dist.all_reduce(te, op=dist.ReduceOp.MAX)
     e2e_ms = float(te.item())
 
-    images = max(1, world // 2) if pair else 1       # images in flight (data-parallel pairs)
+    images = n_images                                # images in flight (1 unless more GPUs than one image uses)
     sec_per_image = ms_step * STEPS_PER_IMAGE / 1e3 / images
     e2e_sec = e2e_ms * STEPS_PER_IMAGE / 1e3 / images
 
@@ -252,21 +281,23 @@ def run_ours(args):
         out = {
             "metric": "sec/image 2048^2 28-step CFG T2I", "value": round(sec_per_image, 4), "unit": "s/image",
             "n_gpus": world, "steps": args.steps, "warmup": warm, "ms_per_step": round(ms_step, 3),
-            "higher_is_better": False, "scaling": "strong" if world <= 2 else "weak", "vs_baseline": None,
+            "higher_is_better": False, "scaling": "strong" if images == 1 else "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"{args.workload}: {I} image tokens ({gh}x{gw}) + {T} text tokens, "
                                    f"{layers} decoder blocks, CFG (2 forwards/step), guidance {GUIDANCE}, "
                                    f"flow-match Euler, Dev sigmas",
                        "seq_len": S, "layers": layers, "steps_per_image": STEPS_PER_IMAGE,
-                       "parallelism": "1 GPU" if world == 1 else f"cfg pair x dp{world // 2}",
+                       "parallelism": "1 GPU" if world == 1 else
+                                      f"cfg pair x ulysses sp{sp_size}" + (f" x dp{images}" if images > 1 else ""),
                        "weights": "random-init N(0,0.02) bf16, seed 1234",
                        "l2": "no flush needed: every step streams 2 x %.1f GB of weights (L2 is 126 MB)"
                              % (w.nbytes() / 1e9)},
             "steps_per_s": round(1e3 / ms_step * images, 4),
             "model_tflops_per_step": round(fl_step / 1e12, 2),
-            "achieved_tflops": round(fl_step / ms_step / 1e9 * (images if pair else 1) / world, 1),
-            "e2e": {"value": round(e2e_sec, 4), "unit": "s/image", "h2d_bytes_per_step": z_host.numel() * 2 + 4,
-                    "d2h_bytes_per_step": z_host.numel() * 2},
+            "achieved_tflops_per_gpu": round(fl_step * images / ms_step / 1e9 / world, 1),
+            "e2e": {"value": round(e2e_sec, 4), "unit": "s/image",
+                    "h2d_bytes_per_step": (I * 3072 * 2 + 4) * (2 if pair else 1) * images,
+                    "d2h_bytes_per_step": I * 3072 * 2 * (2 if pair else 1) * images},
             "gpu_launches": int(launches),
             "clocks": clocks,
             "roofline": {"bound": "tensor", "kernel": top[0], "achieved": achieved, "peak": sustained,

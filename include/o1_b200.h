@@ -365,6 +365,37 @@ hd_status o1_denoise_step_cfg_host(const hd_forward_binding *bw, hd_forward_work
                                    int heads, int kv_heads, int hidden, int ff_hidden,
                                    int head_dim, int tms_token_id);
 
+/* ------------------------------------------- sequence-parallel (Ulysses) form, added
+ * No counterpart in the reference (it is single-GPU, src/main.c:242-243).  Token rows are sharded
+ * over sp_size ranks: rank r owns rows [r*rows, (r+1)*rows), S = rows*sp_size.  Per block the caller
+ * runs  o1_sp_block_pre -> exchange(send -> gath) -> o1_sp_block_attn -> exchange(attn -> recv) ->
+ * o1_sp_block_post, where both exchanges are equal-split all-to-alls of contiguous slabs:
+ *   send [sp_size][rows][C]   slab d = this rank's rows of q|k|v for the heads rank d owns,
+ *   gath [S][C]               row block s = slab received from rank s   (C = (heads+2*kv_heads)*128/sp_size)
+ *   attn [S][Hc]              row block d = slab sent to rank d          (Hc = heads*128/sp_size)
+ *   recv [sp_size][rows][Hc]  slab s = this rank's rows of the heads rank s owns.
+ * With sp_size == 1, send == gath and attn == recv may alias and no exchange is needed. */
+typedef struct {
+    int sp_size, sp_rank;
+    int S, T;          /* global token count, text token count */
+    int row0, rows;    /* this rank's rows */
+    int heads, kv_heads, hidden, ff, head_dim;
+    int ar_len;
+    void *send, *gath, *attn, *recv;
+    void *ln, *ar, *post, *swi;    /* [rows,hidden] x3, [rows,ff] */
+    float *rope;                   /* [rows,128] */
+} o1_sp_ws;
+void o1_launch_count_add(int n);
+hd_status o1_sp_rope_table(const o1_sp_ws *w, const float *pos_global /* [3,S] */);
+hd_status o1_sp_block_pre(const hd_block_binding *bw, const o1_sp_ws *w, const void *in);
+hd_status o1_sp_block_attn(const o1_sp_ws *w);
+hd_status o1_sp_block_post(const hd_block_binding *bw, const o1_sp_ws *w, const void *in, void *out);
+hd_status o1_sp_forward_begin(const hd_forward_binding *bw, const o1_sp_ws *w, const int64_t *ids_global,
+                              const void *vin_local, const float *timestep_dev, void *small, void *xe_stage,
+                              int tms_token_id, void *hidden_out);
+hd_status o1_sp_forward_end(const hd_forward_binding *bw, const o1_sp_ws *w, const void *hidden,
+                            void *norm_scratch, void *out_local);
+
 #ifdef __cplusplus
 }
 #endif

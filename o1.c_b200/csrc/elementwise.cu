@@ -257,7 +257,7 @@ bool mrope_cos_sin(const float* pos, int bs, int seq, const int64_t* section, in
 // attention_scaling 1: cs[s][kk] = cos, cs[s][64+kk] = sin, kk in [0,64).
 // Layer-invariant, so it is built once per forward instead of once per block.
 __global__ void mrope_table64_kernel(const float* __restrict__ pos, float* __restrict__ cs, int seq,
-                                     float theta) {
+                                     float theta, int pos_stride) {
     const int s = blockIdx.x * 4 + (threadIdx.x >> 6);
     const int kk = threadIdx.x & 63;
     if (s >= seq) return;
@@ -265,7 +265,7 @@ __global__ void mrope_table64_kernel(const float* __restrict__ pos, float* __res
     int axis = 0;
     if (slot == 1 && chunk < 20) axis = 1;
     if (slot == 2 && chunk < 20) axis = 2;
-    const float p = pos[(size_t)axis * seq + s];
+    const float p = pos[(size_t)axis * pos_stride + s];
     const float base = expf(-logf(theta) * (2.0f * (float)kk) / 128.0f);
     const float ang = base * p;
     cs[(size_t)s * 128 + kk] = cosf(ang) * 1.0f;
@@ -273,7 +273,14 @@ __global__ void mrope_table64_kernel(const float* __restrict__ pos, float* __res
 }
 bool mrope_table64(const float* pos, int seq, float theta, float* cs, cudaStream_t st) {
     if (!pos || !cs || seq <= 0) { set_error("mrope_table: bad args"); return false; }
-    mrope_table64_kernel<<<(seq + 3) / 4, 256, 0, st>>>(pos, cs, seq, theta);
+    mrope_table64_kernel<<<(seq + 3) / 4, 256, 0, st>>>(pos, cs, seq, theta, seq);
+    O1_LAUNCH_CHECK("mrope_table");
+    return true;
+}
+bool mrope_table64_rows(const float* pos, int pos_stride, int row0, int rows, float theta, float* cs,
+                        cudaStream_t st) {
+    if (!pos || !cs || rows <= 0 || row0 < 0 || row0 + rows > pos_stride) { set_error("mrope_table: bad args"); return false; }
+    mrope_table64_kernel<<<(rows + 3) / 4, 256, 0, st>>>(pos + row0, cs, rows, theta, pos_stride);
     O1_LAUNCH_CHECK("mrope_table");
     return true;
 }
@@ -325,7 +332,7 @@ bool apply_rotary(const void* x, const float* cosd, const float* sind, void* y, 
 // points: normed value -> bf16 (norm.cu:45-46), then the three roundings of
 // rope.cu:123-133.
 __global__ void __launch_bounds__(256)
-qk_norm_rope_kernel(uint16_t* __restrict__ x, int ld, int S, int heads,
+qk_norm_rope_kernel(uint16_t* __restrict__ x, int ld, int S, int heads, int hpb, long blk_stride,
                     const uint16_t* __restrict__ w, const float* __restrict__ cs, float eps) {
     const int gid = blockIdx.x * 32 + (threadIdx.x >> 3);  // (token, head) pair index
     const int t = threadIdx.x & 7;
@@ -333,7 +340,7 @@ qk_norm_rope_kernel(uint16_t* __restrict__ x, int ld, int S, int heads,
     const bool active = gid < total;
     const int s = active ? gid / heads : 0;
     const int h = active ? gid % heads : 0;
-    uint16_t* base = x + (size_t)s * ld + h * 128;
+    uint16_t* base = x + (size_t)(h / hpb) * blk_stride + (size_t)s * ld + (h % hpb) * 128;
     float lo[8], hi[8];
     float sq = 0.f;
     if (active) {
@@ -372,9 +379,18 @@ bool qk_norm_rope(void* x, int ld, int S, int heads, const void* w, const float*
         set_error("qk_norm_rope: bad args");
         return false;
     }
+    return qk_norm_rope_blocked(x, ld, S, heads, heads, 0, w, cs_table, eps, st);
+}
+bool qk_norm_rope_blocked(void* x, int ld, int S, int heads, int hpb, long blk_stride, const void* w,
+                          const float* cs_table, float eps, cudaStream_t st) {
+    if (!x || !w || !cs_table || S <= 0 || heads <= 0 || hpb <= 0 || (heads % hpb) != 0 || (ld % 8) != 0 ||
+        (blk_stride % 8) != 0 || (((uintptr_t)x) & 15)) {
+        set_error("qk_norm_rope: bad args");
+        return false;
+    }
     const long total = (long)S * heads;
     qk_norm_rope_kernel<<<(unsigned)((total + 31) / 32), 256, 0, st>>>(
-        (uint16_t*)x, ld, S, heads, (const uint16_t*)w, cs_table, eps);
+        (uint16_t*)x, ld, S, heads, hpb, blk_stride, (const uint16_t*)w, cs_table, eps);
     O1_LAUNCH_CHECK("qk_norm_rope");
     return true;
 }

@@ -129,6 +129,7 @@ const char* hd_lora_last_error(void) { return g_lora_err; }
 void o1_set_stream(void* stream) { g_stream = (cudaStream_t)stream; }
 void* o1_get_stream(void) { return (void*)g_stream; }
 int o1_sm_count(void) { return sm_count(); }
+void o1_launch_count_add(int n) { count(n); }
 int64_t o1_launch_count(int reset) {
     int64_t v = g_launches.load();
     if (reset) g_launches.store(0);

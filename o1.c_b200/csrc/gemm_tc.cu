@@ -37,6 +37,14 @@ struct GemmArgs {
     int ldr;
     float scale;
     int num_m, num_n, group_m;
+    // Output column blocks: column c lives at out + (c / o_cb) * o_cb_stride + row * ldo + c % o_cb
+    // (o_cb == 0: plain row-major).  Lets a projection write its head groups into per-destination
+    // slabs of an all-to-all send buffer.  o_cb must be a multiple of the tile width.
+    int o_cb;
+    long o_cb_stride;
+    // Input K blocks: K columns [b*a_kblk, (b+1)*a_kblk) of row r live at x[(b*a_rows + r) * ldx + ...]
+    // (a_kblk == 0: plain).  Lets a projection read the slabs an all-to-all received, one per source.
+    int a_kblk, a_rows;
     int* err;
 };
 
@@ -149,7 +157,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     uint8_t* a_s = smem + stage * Cfg::STAGE_BYTES;
                     uint8_t* b_s = a_s + Cfg::A_BYTES;
                     mbar_expect_tx(&full[stage], Cfg::STAGE_BYTES);
-                    tma_load_2d(a_s, &tmA, &full[stage], kb * BK, mb * BM);
+                    int a_c0 = kb * BK, a_c1 = mb * BM;
+                    if (g.a_kblk > 0) {
+                        const int blk = a_c0 / g.a_kblk;
+                        a_c0 -= blk * g.a_kblk;
+                        a_c1 += blk * g.a_rows;
+                    }
+                    tma_load_2d(a_s, &tmA, &full[stage], a_c0, a_c1);
                     if (EPI == EPI_SWIGLU) {
                         // 128 gate rows then 128 up rows of the same output columns
                         tma_load_2d(b_s, &tmB, &full[stage], kb * BK, nb * 128);
@@ -235,6 +249,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     tmem_ld_wait();
                     if (row_ok) {
                         const int col = nb * BN + c * 32;
+                        const size_t ocol = g.o_cb ? (size_t)(col / g.o_cb) * g.o_cb_stride + (col % g.o_cb)
+                                                   : (size_t)col;
                         float v[32];
 #pragma unroll
                         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
@@ -250,11 +266,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                             for (int j = 0; j < 32; ++j) v[j] = bf16_round(v[j]) + b[j];
                         } else if (EPI == EPI_LORA) {
                             float b[32];
-                            load32_bf16(g.out + (size_t)row * g.ldo + col, b);
+                            load32_bf16(g.out + (size_t)row * g.ldo + ocol, b);
 #pragma unroll
                             for (int j = 0; j < 32; ++j) v[j] = b[j] + g.scale * v[j];
                         }
-                        store32_bf16(g.out + (size_t)row * g.ldo + col, v);
+                        store32_bf16(g.out + (size_t)row * g.ldo + ocol, v);
                     }
                 }
             }
@@ -405,7 +421,25 @@ bool gemm_bf16(const void* x, const void* w, const void* w2, void* y, int M, int
 bool gemm_bf16_ld(const void* x, int ldx, const void* w, const void* w2, void* y, int ldy, int M,
                   int N, int K, int epi, const void* bias, const void* resid, int ldr, float scale,
                   int force_bn, cudaStream_t st) {
+    return gemm_bf16_ex(x, ldx, w, w2, y, ldy, M, N, K, epi, bias, resid, ldr, scale, force_bn, 0, 0, 0, 0, st);
+}
+
+bool gemm_bf16_ex(const void* x, int ldx, const void* w, const void* w2, void* y, int ldy, int M, int N,
+                  int K, int epi, const void* bias, const void* resid, int ldr, float scale, int force_bn,
+                  int o_cb, long o_cb_stride, int a_kblk, int a_rows, cudaStream_t st) {
     if (!x || !w || !y || M <= 0 || N <= 0 || K <= 0) { set_error("gemm: bad args"); return false; }
+    if ((o_cb || a_kblk) && !gemm_tc_supported(M, N, K, epi)) {
+        set_error("gemm: blocked operand layouts need a tensor-core shape");
+        return false;
+    }
+    if (o_cb && ((o_cb % 128) != 0 || (N % o_cb) != 0 || epi == EPI_SWIGLU)) {
+        set_error("gemm: bad output column block %d", o_cb);
+        return false;
+    }
+    if (a_kblk && ((a_kblk % BK) != 0 || (K % a_kblk) != 0)) {
+        set_error("gemm: bad input K block %d", a_kblk);
+        return false;
+    }
     if (!gemm_tc_supported(M, N, K, epi)) {
         if (epi != EPI_STORE && epi != EPI_BIAS) { set_error("gemm: shape unsupported for fused epilogue"); return false; }
         dim3 block(128);
@@ -426,8 +460,11 @@ bool gemm_bf16_ld(const void* x, int ldx, const void* w, const void* w2, void* y
     g.err = device_error_word();
     g.num_m = (M + BM - 1) / BM;
     g.group_m = 32;
+    g.o_cb = o_cb; g.o_cb_stride = o_cb_stride;
+    g.a_kblk = a_kblk; g.a_rows = a_rows;
 
-    const CUtensorMap* tA = cached_tmap(x, M, K, ldx, 128);
+    const CUtensorMap* tA = a_kblk ? cached_tmap(x, (uint64_t)(K / a_kblk) * a_rows, a_kblk, ldx, 128)
+                                   : cached_tmap(x, M, K, ldx, 128);
     const CUtensorMap* tB = cached_tmap(w, N, K, K, 128);
     const CUtensorMap* tB2 = (epi == EPI_SWIGLU) ? cached_tmap(w2, N, K, K, 128) : tB;
     if (!tA || !tB || !tB2) return false;
@@ -437,14 +474,17 @@ bool gemm_bf16_ld(const void* x, int ldx, const void* w, const void* w2, void* y
         return launch_tc<EPI_SWIGLU, 256>(tA, tB, tB2, g, st);
     }
     int bn = 256;
-    if ((N % 256) != 0) bn = 128;
+    if ((N % 256) != 0 || (o_cb && (o_cb % 256) != 0)) bn = 128;
     else {
         // small problems: halve the tile to fill the SMs
         const int tiles256 = g.num_m * (N / 256);
         if (tiles256 < 2 * sm_count()) bn = 128;
     }
     if (force_bn == 128 || force_bn == 256) {
-        if (force_bn == 256 && (N % 256) != 0) { set_error("gemm: BN=256 needs N %% 256 == 0"); return false; }
+        if (force_bn == 256 && ((N % 256) != 0 || (o_cb && (o_cb % 256) != 0))) {
+            set_error("gemm: BN=256 needs N (and the output column block) %% 256 == 0");
+            return false;
+        }
         bn = force_bn;
     }
     g.num_n = N / bn;

@@ -25,6 +25,12 @@ bool gemm_bf16(const void* x, const void* w, const void* w2, void* y, int M, int
 bool gemm_bf16_ld(const void* x, int ldx, const void* w, const void* w2, void* y, int ldy, int M,
                   int N, int K, int epi, const void* bias, const void* resid, int ldr, float scale,
                   int force_bn, cudaStream_t st);
+// Same, plus blocked operand layouts for sequence-parallel exchanges:
+//  o_cb / o_cb_stride: output column c is stored at y + (c / o_cb) * o_cb_stride + row * ldy + c % o_cb
+//  a_kblk / a_rows   : input column k of row r is read from x[((k / a_kblk) * a_rows + r) * ldx + k % a_kblk]
+bool gemm_bf16_ex(const void* x, int ldx, const void* w, const void* w2, void* y, int ldy, int M, int N,
+                  int K, int epi, const void* bias, const void* resid, int ldr, float scale, int force_bn,
+                  int o_cb, long o_cb_stride, int a_kblk, int a_rows, cudaStream_t st);
 bool gemm_tc_supported(int M, int N, int K, int epi);
 const CUtensorMap* cached_tmap(const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
                                uint32_t box_rows);
@@ -49,12 +55,18 @@ bool mrope_cos_sin(const float* pos, int bs, int seq, const int64_t* section, in
                    float* sind, cudaStream_t st);
 // compact table: cs[s][0..63] = cos, cs[s][64..127] = sin of the 64 distinct angles
 bool mrope_table64(const float* pos, int seq, float theta, float* cs, cudaStream_t st);
+// rows [row0, row0+rows) of a sequence whose position ids are pos[3, pos_stride]
+bool mrope_table64_rows(const float* pos, int pos_stride, int row0, int rows, float theta, float* cs,
+                        cudaStream_t st);
 bool apply_rotary(const void* x, const float* cosd, const float* sind, void* y, int heads, int seq,
                   int dim, int f32_mode, cudaStream_t st);
 // fused per-head RMSNorm + rotary, in place on a seq-major [S, ld] buffer
 // holding `heads` heads of 128 starting at column 0 (weights w[128]).
 bool qk_norm_rope(void* x, int ld, int S, int heads, const void* w, const float* cs_table,
                   float eps, cudaStream_t st);
+// same with heads grouped in slabs: head h sits at x + (h / hpb) * blk_stride + s * ld + (h % hpb) * 128
+bool qk_norm_rope_blocked(void* x, int ld, int S, int heads, int hpb, long blk_stride, const void* w,
+                          const float* cs_table, float eps, cudaStream_t st);
 bool head_split(const void* in, void* out, int seq, int heads, int dim, cudaStream_t st);
 bool head_merge(const void* in, void* out, int seq, int heads, int dim, cudaStream_t st);
 bool gather_rows(const void* table, const void* idx, void* out, int M, int cols, int64_t nrows,

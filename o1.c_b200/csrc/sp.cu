@@ -1,0 +1,144 @@
+// Sequence-parallel (Ulysses) form of the forward: token rows are sharded across P ranks for every
+// token-wise op (norms, all GEMMs, SwiGLU, residuals, embedding, head); around attention two all-to-all
+// exchanges turn [S/P rows, all heads] into [all rows, heads/P] and back.  The reference has no
+// multi-GPU code; this splits hd_decoder_block (o1.c src/model/block.c:247-356) at its two exchange
+// points into three calls, and hd_forward (src/model/forward.c:249-397) into begin / end calls.
+//
+// No pack or unpack pass exists: the q/k/v projections write straight into the all-to-all send
+// layout (one slab per destination rank), attention reads the received slabs as one [S, C] matrix and
+// writes its output as [S, Hc] whose row blocks are the second exchange's send slabs, and o_proj reads
+// the received slabs as K blocks of its A operand.  The exchanges themselves are the caller's
+// (NCCL all-to-all with equal splits, or peer copies).
+#include "common.cuh"
+#include "kernels.h"
+#include "../../include/o1_b200.h"
+
+#include <math.h>
+
+using namespace o1;
+
+#define SP_TRY(expr, what)                                                                  \
+    do {                                                                                    \
+        if (!(expr)) { hd_set_error("sp: %s: %s", what, hd_cuda_last_error()); return HD_ERR_RUNTIME; } \
+        o1_launch_count_add(1);                                                             \
+    } while (0)
+
+extern "C" void o1_launch_count_add(int n);
+
+static bool sp_ok(const o1_sp_ws* w) {
+    return w && w->sp_size >= 1 && w->sp_rank >= 0 && w->sp_rank < w->sp_size && w->head_dim == 128 &&
+           w->heads % w->sp_size == 0 && w->kv_heads % w->sp_size == 0 && w->S == w->rows * w->sp_size &&
+           w->row0 == w->sp_rank * w->rows && (w->hidden % 256) == 0 && (w->ff % 128) == 0 &&
+           ((w->heads / w->sp_size) * 128) % 128 == 0;
+}
+
+extern "C" {
+
+hd_status o1_sp_rope_table(const o1_sp_ws* w, const float* pos_global) {
+    if (!sp_ok(w) || !pos_global || !w->rope) { hd_set_error("sp: bad workspace"); return HD_ERR_MISSING; }
+    SP_TRY(mrope_table64_rows(pos_global, w->S, w->row0, w->rows, 5000000.0f, w->rope, current_stream()),
+           "rope table");
+    return HD_OK;
+}
+
+// in [rows, hidden] -> send [P][rows][C]: RMSNorm, q/k/v projections, per-head norm + rope
+hd_status o1_sp_block_pre(const hd_block_binding* bw, const o1_sp_ws* w, const void* in) {
+    if (!sp_ok(w) || !bw || !in) { hd_set_error("sp: bad arguments"); return HD_ERR_MISSING; }
+    cudaStream_t st = current_stream();
+    const int P = w->sp_size, R = w->rows, H = w->hidden;
+    const int qc = w->heads * 128, kc = w->kv_heads * 128;
+    const int qcp = qc / P, kcp = kc / P, C = qcp + 2 * kcp;
+    const long slab = (long)R * C;
+    uint16_t* send = (uint16_t*)w->send;
+    SP_TRY(rmsnorm(in, bw->input_ln, w->ln, R, H, 1e-6f, st), "input_norm");
+    SP_TRY(gemm_bf16_ex(w->ln, H, bw->q_proj, nullptr, send, C, R, qc, H, EPI_STORE, nullptr, nullptr, 0, 0.f, 0,
+                        qcp, slab, 0, 0, st), "q_proj");
+    SP_TRY(gemm_bf16_ex(w->ln, H, bw->k_proj, nullptr, send + qcp, C, R, kc, H, EPI_STORE, nullptr, nullptr, 0, 0.f,
+                        0, kcp, slab, 0, 0, st), "k_proj");
+    SP_TRY(gemm_bf16_ex(w->ln, H, bw->v_proj, nullptr, send + qcp + kcp, C, R, kc, H, EPI_STORE, nullptr, nullptr, 0,
+                        0.f, 0, kcp, slab, 0, 0, st), "v_proj");
+    SP_TRY(qk_norm_rope_blocked(send, C, R, w->heads, w->heads / P, slab, bw->q_norm, w->rope, 1e-6f, st), "q_norm_rope");
+    SP_TRY(qk_norm_rope_blocked(send + qcp, C, R, w->kv_heads, w->kv_heads / P, slab, bw->k_norm, w->rope, 1e-6f, st),
+           "k_norm_rope");
+    return HD_OK;
+}
+
+// gath [S][C] (all rows, this rank's heads) -> attn [S][Hc]
+hd_status o1_sp_block_attn(const o1_sp_ws* w) {
+    if (!sp_ok(w)) { hd_set_error("sp: bad workspace"); return HD_ERR_MISSING; }
+    const int P = w->sp_size;
+    const int qcp = w->heads * 128 / P, kcp = w->kv_heads * 128 / P, C = qcp + 2 * kcp;
+    const uint16_t* g = (const uint16_t*)w->gath;
+    SP_TRY(flash_attention(g, C, g + qcp, C, g + qcp + kcp, C, w->attn, qcp, w->S, w->heads / P, w->kv_heads / P,
+                           w->ar_len, (float)(1.0 / sqrt(128.0)), current_stream()), "attention");
+    return HD_OK;
+}
+
+// recv [P][rows][Hc] + in [rows, hidden] -> out [rows, hidden]: o_proj(+residual), RMSNorm, SwiGLU MLP(+residual)
+hd_status o1_sp_block_post(const hd_block_binding* bw, const o1_sp_ws* w, const void* in, void* out) {
+    if (!sp_ok(w) || !bw || !in || !out) { hd_set_error("sp: bad arguments"); return HD_ERR_MISSING; }
+    cudaStream_t st = current_stream();
+    const int P = w->sp_size, R = w->rows, H = w->hidden, qc = w->heads * 128, hc = qc / P;
+    SP_TRY(gemm_bf16_ex(w->recv, hc, bw->o_proj, nullptr, w->ar, H, R, H, qc, EPI_RESID, nullptr, in, H, 0.f, 0, 0, 0,
+                        P > 1 ? hc : 0, R, st), "o_proj+resid");
+    SP_TRY(rmsnorm(w->ar, bw->post_ln, w->post, R, H, 1e-6f, st), "post_norm");
+    SP_TRY(gemm_bf16(w->post, bw->gate_proj, bw->up_proj, w->swi, R, w->ff, H, EPI_SWIGLU, nullptr, nullptr, 0.f, 0,
+                     st), "gate_up_swiglu");
+    SP_TRY(gemm_bf16_ld(w->swi, w->ff, bw->down_proj, nullptr, out, H, R, H, w->ff, EPI_RESID, nullptr, w->ar, H,
+                        0.f, 0, st), "down_proj+resid");
+    return HD_OK;
+}
+
+// Embedding of this rank's rows: timestep MLP (replicated), text rows from the table with the tms row
+// replaced, image rows through x_embedder.  ids_global [T] int64; vin_local: the latent rows of this
+// rank's image tokens.  small: >= 4*hidden*2 + 4096 bytes of scratch; xe_stage [img_local, 1024] bf16.
+hd_status o1_sp_forward_begin(const hd_forward_binding* bw, const o1_sp_ws* w, const int64_t* ids_global,
+                              const void* vin_local, const float* timestep_dev, void* small, void* xe_stage,
+                              int tms_token_id, void* hidden_out) {
+    if (!sp_ok(w) || !bw || !ids_global || !timestep_dev || !small || !hidden_out) {
+        hd_set_error("sp: bad arguments");
+        return HD_ERR_MISSING;
+    }
+    cudaStream_t st = current_stream();
+    const int H = w->hidden, T = w->T;
+    uint8_t* sm = (uint8_t*)small;
+    uint16_t* t_emb = (uint16_t*)sm;
+    uint16_t* te_hidden = (uint16_t*)(sm + (size_t)H * 2);
+    float* freq = (float*)(sm + (size_t)H * 4);
+    uint16_t* freq_bf16 = (uint16_t*)(sm + (size_t)H * 4 + 1024);
+    float* t_scaled = (float*)(sm + (size_t)H * 4 + 2048);
+    SP_TRY(scale_f32(timestep_dev, t_scaled, 1000.0f, 1, st), "t_scale");
+    SP_TRY(timestep_embed(t_scaled, freq, 1, 256, st), "t_sinusoid");
+    SP_TRY(f32_to_bf16_buf(freq, freq_bf16, 256, st), "t_cast");
+    SP_TRY(gemm_bf16(freq_bf16, bw->te0_w, nullptr, te_hidden, 1, H, 256, EPI_BIAS, bw->te0_b, nullptr, 0.f, 0, st), "t_mlp0");
+    SP_TRY(silu(te_hidden, t_emb, (size_t)H, st), "t_silu");
+    SP_TRY(gemm_bf16(t_emb, bw->te2_w, nullptr, te_hidden, 1, H, H, EPI_BIAS, bw->te2_b, nullptr, 0.f, 0, st), "t_mlp2");
+    const int t0 = w->row0 < T ? w->row0 : T;
+    const int t1 = (w->row0 + w->rows) < T ? (w->row0 + w->rows) : T;
+    const int n_text = t1 - t0, n_img = w->rows - n_text;
+    uint16_t* hid = (uint16_t*)hidden_out;
+    if (n_text > 0)
+        SP_TRY(embed_text(bw->embed_tokens, ids_global + t0, te_hidden, hid, n_text, H, 151936, tms_token_id, st),
+               "embed+tms");
+    if (n_img > 0) {
+        if (!vin_local || !xe_stage) { hd_set_error("sp: image rows without latents"); return HD_ERR_MISSING; }
+        SP_TRY(gemm_bf16(vin_local, bw->xe1_w, nullptr, xe_stage, n_img, 1024, 3072, EPI_STORE, nullptr, nullptr, 0.f,
+                         0, st), "x_embed1");
+        SP_TRY(gemm_bf16(xe_stage, bw->xe2_w, nullptr, hid + (size_t)n_text * H, n_img, H, 1024, EPI_BIAS, bw->xe2_b,
+                         nullptr, 0.f, 0, st), "x_embed2");
+    }
+    return HD_OK;
+}
+
+// final RMSNorm + head on this rank's rows: hidden [rows, hidden] -> out_local [rows, 3072]
+hd_status o1_sp_forward_end(const hd_forward_binding* bw, const o1_sp_ws* w, const void* hidden, void* norm_scratch,
+                            void* out_local) {
+    if (!sp_ok(w) || !bw || !hidden || !norm_scratch || !out_local) { hd_set_error("sp: bad arguments"); return HD_ERR_MISSING; }
+    cudaStream_t st = current_stream();
+    SP_TRY(rmsnorm(hidden, bw->fnorm_w, norm_scratch, w->rows, w->hidden, 1e-6f, st), "final_norm");
+    SP_TRY(gemm_bf16(norm_scratch, bw->fl_w, nullptr, out_local, w->rows, 3072, w->hidden, EPI_BIAS, bw->fl_b, nullptr,
+                     0.f, 0, st), "head");
+    return HD_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,152 @@
+"""Sequence-parallel (Ulysses) engine: drives the o1_sp_* stage functions of libo1b200.so and the two
+all-to-all exchanges per block.  The reference is single-GPU; this is the added multi-GPU form of the
+same forward.  Layout rules live in `layout()` and `shard_rows()` so they can be tested without a GPU.
+
+Ranks of one forward form an SP group of size P (P divides the 8 KV heads).  With CFG the two branches
+run on two SP groups; rank pairs with equal sp_rank exchange their predictions (all-gather) and apply the
+identical fused scheduler update to their own rows of the latent.
+"""
+import ctypes as C
+
+import torch
+
+from . import lib, ptr, check, BlockBinding, ForwardBinding, PATCH_DIM, TMS_ID
+
+c_int, c_void_p = C.c_int, C.c_void_p
+
+
+class SpWs(C.Structure):
+    """o1_sp_ws (include/o1_b200.h)."""
+    _fields_ = [(n, c_int) for n in ("sp_size", "sp_rank", "S", "T", "row0", "rows", "heads", "kv_heads",
+                                     "hidden", "ff", "head_dim", "ar_len")] + \
+               [(n, c_void_p) for n in ("send", "gath", "attn", "recv", "ln", "ar", "post", "swi", "rope")]
+
+
+for _name, _args in (("o1_sp_rope_table", (C.POINTER(SpWs), c_void_p)),
+                     ("o1_sp_block_pre", (C.POINTER(BlockBinding), C.POINTER(SpWs), c_void_p)),
+                     ("o1_sp_block_attn", (C.POINTER(SpWs),)),
+                     ("o1_sp_block_post", (C.POINTER(BlockBinding), C.POINTER(SpWs), c_void_p, c_void_p)),
+                     ("o1_sp_forward_begin", (C.POINTER(ForwardBinding), C.POINTER(SpWs), c_void_p, c_void_p,
+                                              c_void_p, c_void_p, c_void_p, c_int, c_void_p)),
+                     ("o1_sp_forward_end", (C.POINTER(ForwardBinding), C.POINTER(SpWs), c_void_p, c_void_p,
+                                            c_void_p))):
+    _f = getattr(lib, _name)
+    _f.restype, _f.argtypes = c_int, list(_args)
+
+
+def layout(world, cfg=True, max_sp=8):
+    """rank -> (image index, cfg branch, sp_rank), plus sp_size, for `world` GPUs working on ONE image
+    when possible: world 1 -> both branches on one GPU; 2 -> CFG pair; 4 -> CFG x SP2; 8 -> CFG x SP4."""
+    if world == 1 or not cfg:
+        sp = min(world, max_sp)
+        return {r: (r // sp, None, r % sp) for r in range(world)}, sp
+    sp = min(world // 2, max_sp)
+    per_image = 2 * sp
+    return {r: (r // per_image, (r % per_image) // sp, r % sp) for r in range(world)}, sp
+
+
+def shard_rows(S, T, P, r):
+    """Rows, text rows and image rows (as half-open ranges) of SP rank r; S must be a multiple of P."""
+    if S % P:
+        raise ValueError(f"sequence length {S} is not a multiple of the SP degree {P}")
+    rows = S // P
+    row0 = r * rows
+    t0, t1 = min(row0, T), min(row0 + rows, T)
+    i0, i1 = max(row0, T) - T, max(row0 + rows, T) - T
+    return (row0, row0 + rows), (t0, t1), (i0, i1)
+
+
+class EngineSP:
+    """One SP rank of one forward.  `exchange(src, dst)` performs the equal-split all-to-all of the
+    contiguous tensor `src` into `dst` (same shape): torch.distributed.all_to_all_single in a real
+    job, a peer-copy emulation in single-process tests."""
+
+    def __init__(self, weights, text_len, img_tokens, sp_size, sp_rank, exchange, ar_len=None):
+        self.w, self.P, self.r, self.exchange = weights, sp_size, sp_rank, exchange
+        d = weights.dims
+        self.T, self.I, self.S = text_len, img_tokens, text_len + img_tokens
+        (self.row0, _), (self.t0, self.t1), (self.i0, self.i1) = shard_rows(self.S, self.T, sp_size, sp_rank)
+        self.rows = self.S // sp_size
+        H, ff, hd = d["hidden"], d["ff"], d["head_dim"]
+        qc, kc = d["heads"] * hd, d["kv_heads"] * hd
+        if d["kv_heads"] % sp_size:
+            raise ValueError("SP degree must divide the KV heads")
+        self.C, self.Hc = (qc + 2 * kc) // sp_size, qc // sp_size
+        dev = weights.device
+        bf = dict(dtype=torch.bfloat16, device=dev)
+        R, S = self.rows, self.S
+        self.send = torch.empty(sp_size, R, self.C, **bf)
+        self.gath = self.send.view(S, self.C) if sp_size == 1 else torch.empty(S, self.C, **bf)
+        self.attn = torch.empty(S, self.Hc, **bf)
+        self.recv = self.attn.view(sp_size, R, self.Hc) if sp_size == 1 else torch.empty(sp_size, R, self.Hc, **bf)
+        self.ln, self.ar, self.post = (torch.empty(R, H, **bf) for _ in range(3))
+        self.swi = torch.empty(R, ff, **bf)
+        self.hid = [torch.empty(R, H, **bf) for _ in range(2)]
+        self.rope = torch.empty(R, 128, dtype=torch.float32, device=dev)
+        self.small = torch.empty(4 * H * 2 + 4096, dtype=torch.uint8, device=dev)
+        self.xe_stage = torch.empty(max(1, self.i1 - self.i0), 1024, **bf)
+        self.timestep = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.ws = SpWs(sp_size=sp_size, sp_rank=sp_rank, S=S, T=self.T, row0=self.row0, rows=R, heads=d["heads"],
+                       kv_heads=d["kv_heads"], hidden=H, ff=ff, head_dim=hd,
+                       ar_len=(text_len - 1 if ar_len is None else ar_len),
+                       send=self.send.data_ptr(), gath=self.gath.data_ptr(), attn=self.attn.data_ptr(),
+                       recv=self.recv.data_ptr(), ln=self.ln.data_ptr(), ar=self.ar.data_ptr(),
+                       post=self.post.data_ptr(), swi=self.swi.data_ptr(), rope=self.rope.data_ptr())
+
+    # the forward is split into generator-style stages so that a single process can interleave several
+    # emulated ranks; `forward()` runs them back to back for a real rank
+    def stages(self, ids, pos, vin_local, t, out_local):
+        ws, w = C.byref(self.ws), self.w
+        self.timestep.fill_(float(t))
+        check(lib.o1_sp_rope_table(ws, ptr(pos)), "sp_rope_table")
+        check(lib.o1_sp_forward_begin(C.byref(w.binding), ws, ptr(ids), ptr(vin_local), ptr(self.timestep),
+                                      ptr(self.small), ptr(self.xe_stage), TMS_ID, ptr(self.hid[0])), "sp_begin")
+        cur, nxt = self.hid
+        for l in range(w.n_layers):
+            bb = C.byref(w.block_binding(l))
+            check(lib.o1_sp_block_pre(bb, ws, ptr(cur)), "sp_block_pre")
+            yield ("a2a", self.send, self.gath.view(self.P, self.rows, self.C))
+            check(lib.o1_sp_block_attn(ws), "sp_block_attn")
+            yield ("a2a", self.attn.view(self.P, self.rows, self.Hc), self.recv)
+            check(lib.o1_sp_block_post(bb, ws, ptr(cur), ptr(nxt)), "sp_block_post")
+            cur, nxt = nxt, cur
+        check(lib.o1_sp_forward_end(C.byref(w.binding), ws, ptr(cur), ptr(self.ln), ptr(out_local)), "sp_end")
+
+    def forward(self, ids, pos, vin_local, t, out_local=None):
+        """x_pred rows of this rank, [rows, 3072] bf16."""
+        if out_local is None:
+            out_local = torch.empty(self.rows, PATCH_DIM, dtype=torch.bfloat16, device=self.w.device)
+        for _, src, dst in self.stages(ids, pos, vin_local, t, out_local):
+            if self.P > 1:
+                self.exchange(src, dst)
+        return out_local
+
+
+def nccl_exchange(group):
+    """Equal-split all-to-all over a torch.distributed process group (NCCL over NVLink)."""
+    import torch.distributed as dist
+
+    def ex(src, dst):
+        dist.all_to_all_single(dst.view(-1), src.view(-1), group=group)
+    return ex
+
+
+def run_emulated(engines, ids, pos, vin, t):
+    """Single-process emulation of P ranks on one device: stages are advanced in lock step and each
+    all-to-all is done by copies (slab d of rank s -> slab s of rank d).  Returns x_pred [S, 3072]."""
+    P = len(engines)
+    outs = [torch.empty(e.rows, PATCH_DIM, dtype=torch.bfloat16, device=e.w.device) for e in engines]
+    gens = [e.stages(ids, pos, vin[e.i0:e.i1] if e.i1 > e.i0 else None, t, o) for e, o in zip(engines, outs)]
+    while True:
+        steps = []
+        for g in gens:
+            try:
+                steps.append(next(g))
+            except StopIteration:
+                steps.append(None)
+        if all(s is None for s in steps):
+            break
+        for s in range(P):
+            for d in range(P):
+                steps[d][2][s].copy_(steps[s][1][d])
+    return torch.cat(outs, 0)

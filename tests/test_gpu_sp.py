@@ -1,0 +1,46 @@
+"""Sequence-parallel (Ulysses) stages on ONE GPU: P emulated ranks advanced in lock step, exchanges
+done by copies.  The sharded forward must reproduce the single-rank hd_forward (same kernels, same
+rounding points; only GEMM tile shapes change with the row count), for P = 1, 2, 4, 8."""
+import numpy as np
+import pytest
+import torch
+
+import parity
+from parity import seeded_bf16, torch_to_u16, u16_to_torch, assert_close
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("P", [1, 2, 4, 8])
+def test_sp_forward_matches_single_rank(pkg, dev, P):
+    from o1c_b200 import sp
+    T, gh, gw, L = 24, 8, 13, 2          # S = 128: every P divides it; shard 0 mixes text and image rows
+    I, S = gh * gw, 24 + 8 * 13
+    w = pkg.Weights(n_layers=L, seed=1234, weight_set="B", device=dev)
+    pos, ar = pkg.seq_t2i(T, gh, gw)
+    rng = np.random.default_rng(1)
+    ids = rng.integers(0, 151000, size=T).astype(np.int64)
+    ids[-1] = pkg.TMS_ID
+    idsd, posd = torch.from_numpy(ids).to(dev), pos.to(dev)
+    vin = u16_to_torch(seeded_bf16((I, 3072), 43), dev)
+    ref = pkg.Engine(w, T, I).forward(idsd, posd, vin, 0.5)
+    engines = [sp.EngineSP(w, T, I, P, r, None) for r in range(P)]
+    out = sp.run_emulated(engines, idsd, posd, vin, 0.5)
+    torch.cuda.synchronize()
+    assert out.shape == ref.shape
+    assert_close(out, ref, "B", f"SP{P} forward vs single rank")
+    if P == 1:
+        assert torch.equal(out.view(torch.int16), ref.view(torch.int16))
+    # and against the CPU oracle, as the unsharded forward is
+    hw = parity.HostWeights(pkg, L, 1234, "B")
+    oref = parity.oracle_forward(hw, ids, pos.numpy(), ar, torch_to_u16(vin), 0.5)
+    assert_close(torch_to_u16(out), oref, "E", f"SP{P} forward vs oracle")
+
+
+def test_sp_rejects_bad_geometry(pkg, dev):
+    from o1c_b200 import sp
+    w = pkg.Weights(n_layers=1, device=dev)
+    with pytest.raises(ValueError):
+        sp.EngineSP(w, 24, 103, 2, 0, None)          # S = 127 not divisible
+    with pytest.raises(ValueError):
+        sp.EngineSP(w, 24, 120, 16, 0, None)         # 16 does not divide the 8 KV heads
