@@ -288,7 +288,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 }
 
 // ---------------------------------------------------------------- SIMT path
-// One warp per output element; used for M < 16 (timestep MLP, M = 1) and
+// One warp per output element; used for M < 8 (timestep MLP, M = 1) and
 // for shapes the tensor-core tiles do not cover (N % 128 or K % 64 != 0).
 __global__ void gemm_simt_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ w,
                                  const uint16_t* __restrict__ bias, uint16_t* __restrict__ y, int M,
@@ -407,7 +407,7 @@ static bool launch_tc(const CUtensorMap* tA, const CUtensorMap* tB, const CUtens
 }
 
 bool gemm_tc_supported(int M, int N, int K, int epi) {
-    if (M < 16 || (K % BK) != 0) return false;
+    if (M < 8 || (K % BK) != 0) return false;   // tiny M (timestep MLP, M = 1) is a GEMV: SIMT path
     if (epi == EPI_SWIGLU) return (N % 128) == 0;  // N = ff columns of each of gate/up
     return (N % 128) == 0;
 }
