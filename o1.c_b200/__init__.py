@@ -207,5 +207,5 @@ def use_torch_stream():
 
 
 from .model import (  # noqa: E402
-    Weights, Engine, seq_t2i, dev_sigmas, weight_seed, SLOT_NAMES, GLOBAL_NAMES, tensor_shape,
+    Weights, Engine, seq_t2i, seq_ref, dev_sigmas, weight_seed, SLOT_NAMES, GLOBAL_NAMES, tensor_shape,
 )

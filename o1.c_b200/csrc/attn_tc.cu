@@ -9,17 +9,22 @@
 // One CTA = 128 query rows of one head.  Operands stay seq-major
 // ([S, heads*128]); head split / merge (attn.cu:180-218) disappear into the
 // TMA coordinates and the output addressing.
-//   warp 0     : TMA producer (Q once, then K/V tiles of 128 keys, 2 stages each)
+//   warp 0     : TMA producer (Q once, then K/V tiles of 128 keys, 3 stages each)
 //   warp 1     : tcgen05.mma issuer.  S_j = Q K_j^T into TMEM (double buffered),
-//                O += P_j V_j with P from shared memory, V as an MN-major operand
-//   warps 2..5 : softmax, one thread per query row (TMEM lane == row): fp32
-//                scores -> running max / sum in the exp2 domain -> bf16 P tile
-//                written in the 128B-swizzled K-major layout the MMA reads.
-// O is only rescaled when the running max grows by more than 2^8 (the sum and
-// O then share the same stale max, so the final division is still exact).
+//                O += P_j V_j with P read from tensor memory, V as an MN-major operand
+//   warps 2..9 : two softmax groups of four warps; group g takes key tiles j = g (mod 2)
+//                with its own score buffer, P buffer and output accumulator, one thread
+//                per query row (TMEM lane == row): fp32 scores -> running max / sum in
+//                the exp2 domain -> bf16 P written back into tensor memory over the
+//                scores (shared memory carries only Q, K and V: its bandwidth is what
+//                bounds this kernel).  The two partial results are merged at the end
+//                like split-KV decoding: O = sum_g O_g 2^(m_g-m) / sum_g l_g 2^(m_g-m).
+// An accumulator is only rescaled when its running max grows by more than 2^8 (sum
+// and accumulator share the same stale max, so the final division is still exact).
 #include "common.cuh"
 #include "ptx.cuh"
 #include "kernels.h"
+#include <stdlib.h>
 
 namespace o1 {
 
@@ -28,10 +33,11 @@ static constexpr int AKV = 128;     // keys per tile
 static constexpr int AD = 128;      // head dim
 static constexpr int TILE_BYTES = 128 * 128 * 2;   // 32 KB: two 64-column panels of 16 KB
 static constexpr int PANEL_BYTES = 128 * 64 * 2;
-static constexpr int KV_STAGES = 2;
-static constexpr int ATTN_THREADS = 192;
-// Q | K x2 | V x2 | P x2
-static constexpr int ATTN_SMEM = TILE_BYTES * (1 + 2 * KV_STAGES + 2) + 1024 + 256;
+static constexpr int KV_STAGES = 3;
+static constexpr int ATTN_THREADS = 320;   // TMA warp, MMA warp, two softmax groups of four warps
+// Q | K x3 | V x3 (P lives in tensor memory)
+// tiles + 128 B of barriers / slots + 2 KB of per-row max / sum exchange
+static constexpr int ATTN_SMEM = TILE_BYTES * (1 + 2 * KV_STAGES) + 192 + 4 * AQ * 4;
 
 struct AttnArgs {
     uint16_t* out;
@@ -43,6 +49,7 @@ struct AttnArgs {
     int q_hc, q_hr, kv_hc, kv_hr;
     long out_hoff;      // element offset of head h in the output: h * out_hoff
     int* err;
+    int dbg;
 };
 
 __device__ __forceinline__ float ex2_approx(float x) {
@@ -59,14 +66,13 @@ __device__ __forceinline__ uint32_t cvt_bf16x2(float lo, float hi) {
 __global__ void __launch_bounds__(ATTN_THREADS, 1)
 flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const AttnArgs a) {
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                               ~(uintptr_t)1023);
+    // 7 tiles of 32 KB fill the SM's shared memory, so there is no room for an alignment pad or
+    // static arrays: the dynamic window itself is declared 1024-byte aligned (checked below).
+    extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* q_s = smem;
     uint8_t* k_s = q_s + TILE_BYTES;
     uint8_t* v_s = k_s + KV_STAGES * TILE_BYTES;
-    uint8_t* p_s = v_s + KV_STAGES * TILE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + 2 * TILE_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + KV_STAGES * TILE_BYTES);
     uint64_t* q_full = bars;                // 1
     uint64_t* k_full = bars + 1;            // KV_STAGES
     uint64_t* k_empty = k_full + KV_STAGES;
@@ -74,8 +80,12 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     uint64_t* v_empty = v_full + KV_STAGES;
     uint64_t* s_full = v_empty + KV_STAGES; // 2
     uint64_t* p_ready = s_full + 2;         // 2
-    uint64_t* o_ready = p_ready + 2;        // 1
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_ready + 1);
+    uint64_t* o_done = p_ready + 2;         // 1
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 1);
+    int* s_abort = reinterpret_cast<int*>(tmem_slot + 1);
+    // running max / sum of the two softmax groups, exchanged once at the end
+    float (*s_m)[AQ] = reinterpret_cast<float (*)[AQ]>(bars + 24);
+    float (*s_l)[AQ] = s_m + 2;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -90,10 +100,13 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     const int n_tiles = (kv_end + AKV - 1) / AKV;
 
     // a kernel that already failed on this device leaves its code in *err: do nothing then
-    __shared__ int s_abort;
-    if (threadIdx.x == 0) s_abort = *reinterpret_cast<volatile int*>(a.err);
+    if (threadIdx.x == 0) {
+        int ab = *reinterpret_cast<volatile int*>(a.err);
+        if (ab == 0 && (smem_u32(smem) & 1023u) != 0) { ab = 20; atomicExch(a.err, 20); }
+        *s_abort = ab;
+    }
     __syncthreads();
-    if (s_abort != 0) return;
+    if (*s_abort != 0) return;
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
@@ -107,7 +120,7 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             mbar_init(&s_full[s], 1);
             mbar_init(&p_ready[s], 4);
         }
-        mbar_init(o_ready, 1);
+        mbar_init(o_done, 1);
         fence_mbar_init();
     }
     if (warp == 1) {
@@ -118,8 +131,8 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_S = tmem_base;         // two score buffers: columns [0,128), [128,256)
-    const uint32_t tmem_O = tmem_base + 256;   // output accumulator: columns [256,384)
+    const uint32_t tmem_S = tmem_base;         // score buffers: columns [0,128) and [128,256)
+    const uint32_t tmem_O = tmem_base + 256;   // output accumulators of the two groups: [256,384), [384,512)
 
     if (warp == 0) {
         // -------------------------------------------------------- TMA producer
@@ -130,19 +143,30 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             mbar_expect_tx(q_full, TILE_BYTES);
             tma_load_2d(q_s, &tmQ, q_full, h * a.q_hc, h * a.q_hr + q0);
             tma_load_2d(q_s + PANEL_BYTES, &tmQ, q_full, h * a.q_hc + 64, h * a.q_hr + q0);
-            int st = 0;
-            uint32_t ph = 0;
-            for (int j = 0; j < n_tiles; ++j) {
-                const int kv0 = j * AKV;
-                if (!mbar_wait(&k_empty[st], ph ^ 1)) { atomicExch(a.err, 11); break; }
+            // load order follows the consumer: K0, K1, V0, K2, V1, K3, ...
+            auto load_k = [&](int j) -> bool {
+                const int st = j % KV_STAGES;
+                if (!mbar_wait(&k_empty[st], ((j / KV_STAGES) & 1) ^ 1)) { atomicExch(a.err, 11); return false; }
                 mbar_expect_tx(&k_full[st], TILE_BYTES);
-                tma_load_2d(k_s + st * TILE_BYTES, &tmK, &k_full[st], kh * a.kv_hc, kh * a.kv_hr + kv0);
-                tma_load_2d(k_s + st * TILE_BYTES + PANEL_BYTES, &tmK, &k_full[st], kh * a.kv_hc + 64, kh * a.kv_hr + kv0);
-                if (!mbar_wait(&v_empty[st], ph ^ 1)) { atomicExch(a.err, 12); break; }
+                tma_load_2d(k_s + st * TILE_BYTES, &tmK, &k_full[st], kh * a.kv_hc, kh * a.kv_hr + j * AKV);
+                tma_load_2d(k_s + st * TILE_BYTES + PANEL_BYTES, &tmK, &k_full[st], kh * a.kv_hc + 64,
+                            kh * a.kv_hr + j * AKV);
+                return true;
+            };
+            auto load_v = [&](int j) -> bool {
+                const int st = j % KV_STAGES;
+                if (!mbar_wait(&v_empty[st], ((j / KV_STAGES) & 1) ^ 1)) { atomicExch(a.err, 12); return false; }
                 mbar_expect_tx(&v_full[st], TILE_BYTES);
-                tma_load_2d(v_s + st * TILE_BYTES, &tmV, &v_full[st], kh * a.kv_hc, kh * a.kv_hr + kv0);
-                tma_load_2d(v_s + st * TILE_BYTES + PANEL_BYTES, &tmV, &v_full[st], kh * a.kv_hc + 64, kh * a.kv_hr + kv0);
-                if (++st == KV_STAGES) { st = 0; ph ^= 1; }
+                tma_load_2d(v_s + st * TILE_BYTES, &tmV, &v_full[st], kh * a.kv_hc, kh * a.kv_hr + j * AKV);
+                tma_load_2d(v_s + st * TILE_BYTES + PANEL_BYTES, &tmV, &v_full[st], kh * a.kv_hc + 64,
+                            kh * a.kv_hr + j * AKV);
+                return true;
+            };
+            bool ok = load_k(0);
+            if (ok && n_tiles > 1) ok = load_k(1);
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                ok = load_v(j);
+                if (ok && j + 2 < n_tiles) ok = load_k(j + 2);
             }
         }
     } else if (warp == 1) {
@@ -150,7 +174,7 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         if (lane == 0) {
             constexpr uint32_t idesc_qk = umma_idesc_bf16(128, 128, 0, 0);
             constexpr uint32_t idesc_pv = umma_idesc_bf16(128, 128, 0, 1);  // V is MN-major
-            const uint32_t q_addr = smem_u32(q_s);
+            const uint64_t q_desc = umma_desc_sw128(smem_u32(q_s), 16, 1024);
             bool ok = mbar_wait(q_full, 0);
             if (!ok) atomicExch(a.err, 13);
             auto issue_qk = [&](int j) -> bool {
@@ -158,165 +182,185 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 const uint32_t ph = (j / KV_STAGES) & 1;
                 if (!mbar_wait(&k_full[st], ph)) { atomicExch(a.err, 14); return false; }
                 tc_fence_after();
-                const uint32_t k_addr = smem_u32(k_s + st * TILE_BYTES);
+                // one descriptor per operand tile; the eight K steps only move its 16-byte-unit address field
+                const uint64_t k_desc = umma_desc_sw128(smem_u32(k_s + st * TILE_BYTES), 16, 1024);
                 const uint32_t d = tmem_S + (j & 1) * 128;
 #pragma unroll
                 for (int kk = 0; kk < AD / 16; ++kk) {
-                    const uint32_t off = (kk >> 2) * PANEL_BYTES + (kk & 3) * 32;
-                    umma_ss(d, umma_desc_sw128(q_addr + off, 16, 1024),
-                            umma_desc_sw128(k_addr + off, 16, 1024), idesc_qk, kk != 0);
+                    const uint64_t off = (uint64_t)(((kk >> 2) * PANEL_BYTES + (kk & 3) * 32) >> 4);
+                    umma_ss(d, q_desc + off, k_desc + off, idesc_qk, kk != 0);
                 }
                 umma_commit(&k_empty[st]);
                 umma_commit(&s_full[j & 1]);
                 return true;
             };
+            // Scores run two tiles ahead of the PV products: tile j belongs to softmax group j & 1, which
+            // owns score buffer j & 1, P buffer j & 1 and output accumulator j & 1.
             if (ok) ok = issue_qk(0);
+            if (ok && n_tiles > 1) ok = issue_qk(1);
             for (int j = 0; j < n_tiles && ok; ++j) {
-                if (j + 1 < n_tiles) {
-                    // S buffer (j+1)&1 is free: the softmax of tile j-1 finished reading it
-                    // before it signalled p_ready(j-1), which PV(j-1) already waited on.
-                    ok = issue_qk(j + 1);
-                    if (!ok) break;
-                }
                 const int st = j % KV_STAGES;
                 const uint32_t ph = (j / KV_STAGES) & 1;
+                const int g = j & 1;
                 if (!mbar_wait(&v_full[st], ph)) { atomicExch(a.err, 15); ok = false; break; }
-                if (!mbar_wait(&p_ready[j & 1], (j >> 1) & 1)) { atomicExch(a.err, 16); ok = false; break; }
+                if (!mbar_wait(&p_ready[g], (j >> 1) & 1)) { atomicExch(a.err, 16); ok = false; break; }
                 tc_fence_after();
-                const uint32_t p_addr = smem_u32(p_s + (j & 1) * TILE_BYTES);
-                const uint32_t v_addr = smem_u32(v_s + st * TILE_BYTES);
+                const uint32_t p_tmem = tmem_S + g * 128;   // bf16 P overlays the first 64 score columns
+                const uint64_t v_desc = umma_desc_sw128(smem_u32(v_s + st * TILE_BYTES), PANEL_BYTES, 1024);
 #pragma unroll
                 for (int kk = 0; kk < AKV / 16; ++kk) {
-                    const uint32_t p_off = (kk >> 2) * PANEL_BYTES + (kk & 3) * 32;
-                    const uint32_t v_off = kk * 16 * 128;  // 16 keys down, 128 B per key row
-                    umma_ss(tmem_O, umma_desc_sw128(p_addr + p_off, 16, 1024),
-                            umma_desc_sw128(v_addr + v_off, PANEL_BYTES, 1024), idesc_pv,
-                            (j | kk) != 0);
+                    // 16 keys down per step, 128 B per key row
+                    umma_ts(tmem_O + g * 128, p_tmem + kk * 8, v_desc + (uint64_t)((kk * 16 * 128) >> 4), idesc_pv,
+                            (j >= 2) || (kk != 0));
                 }
                 umma_commit(&v_empty[st]);
-                umma_commit(o_ready);
+                // Score buffer g is reused by tile j+2.  Group g finished reading S(j) before p_ready(j);
+                // P(j) overlays it and is read by the PV(j) just issued: MMAs of one thread execute in
+                // issue order, so QK(j+2) overwrites it only after PV(j) has consumed it.
+                if (j + 2 < n_tiles) ok = issue_qk(j + 2);
             }
+            umma_commit(o_done);
         }
     } else {
-        // -------------------------------------------------------- softmax + output
+        // -------------------------------------------------------- softmax groups + output
+        const int grp = (warp - 2) >> 2;         // 0: even key tiles, 1: odd key tiles
         const int qd = warp & 3;                 // TMEM lane quadrant of this warp
         const int row = qd * 32 + lane;          // row within the query tile
         const int row_g = q0 + row;              // global query index
         const uint32_t lane_off = (uint32_t)(qd * 32) << 16;
         const bool tile_has_causal = q0 < a.ar_len;
-        float m_used = -INFINITY;                // max the stored P / l / O are relative to
+        const bool row_causal = row_g < a.ar_len;
+        const uint32_t t_o = tmem_O + grp * 128 + lane_off;
+        float m_used = -INFINITY;                // max the stored P / l / O of this group are relative to
         float l = 0.f;
         bool ok = true;
-        for (int j = 0; j < n_tiles && ok; ++j) {
+        for (int j = grp; j < n_tiles && ok; j += 2) {
             const int kv0 = j * AKV;
-            if (!mbar_wait(&s_full[j & 1], (j >> 1) & 1)) { atomicExch(a.err, 17); ok = false; break; }
+            if (!mbar_wait(&s_full[grp], (j >> 1) & 1)) { atomicExch(a.err, 17); ok = false; break; }
             tc_fence_after();
+            const uint32_t t_s = tmem_S + grp * 128 + lane_off;
+            const bool need_mask = (kv0 + AKV > a.S) || (tile_has_causal && kv0 + AKV - 1 > q0);
+            // the whole score row (128 fp32) goes to registers with one wait
             uint32_t r[4][32];
-            const uint32_t t_s = tmem_S + (j & 1) * 128 + lane_off;
             tmem_ld32(t_s + 0, r[0]);
             tmem_ld32(t_s + 32, r[1]);
             tmem_ld32(t_s + 64, r[2]);
             tmem_ld32(t_s + 96, r[3]);
             tmem_ld_wait();
-            const bool need_mask = (kv0 + AKV > a.S) || (tile_has_causal && kv0 + AKV - 1 > q0);
             float mx = -INFINITY;
             if (need_mask) {
-                const bool row_causal = row_g < a.ar_len;
 #pragma unroll
                 for (int c = 0; c < 4; ++c)
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
                         const int key = kv0 + c * 32 + i;
                         const bool allow = key < a.S && (!row_causal || key <= row_g);
-                        const float v = allow ? __uint_as_float(r[c][i]) : -INFINITY;
-                        r[c][i] = __float_as_uint(v);
-                        mx = fmaxf(mx, v);
+                        if (!allow) r[c][i] = 0xff800000u;   // -inf
                     }
-            } else {
+            }
+            {
+                float mxa = -INFINITY, mxb = -INFINITY, mxc = -INFINITY, mxd = -INFINITY;
 #pragma unroll
-                for (int c = 0; c < 4; ++c)
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[c][i]));
+                for (int i = 0; i < 32; ++i) {
+                    mxa = fmaxf(mxa, __uint_as_float(r[0][i]));
+                    mxb = fmaxf(mxb, __uint_as_float(r[1][i]));
+                    mxc = fmaxf(mxc, __uint_as_float(r[2][i]));
+                    mxd = fmaxf(mxd, __uint_as_float(r[3][i]));
+                }
+                mx = fmaxf(fmaxf(mxa, mxb), fmaxf(mxc, mxd));
             }
             const float m_tile = mx * a.scale_log2;
             const bool grow = (m_tile - m_used) > 8.0f;      // also true while m_used == -inf
             if (__any_sync(0xffffffffu, grow)) {
                 float alpha = 1.0f;
                 if (grow) {
-                    alpha = ex2_approx(m_used - m_tile);         // 0 on the first tile
+                    alpha = ex2_approx(m_used - m_tile);         // 0 on the group's first tile
                     m_used = m_tile;
                     l *= alpha;
                 }
-                if (j > 0) {
-                    // O of tiles < j must be complete before it is rescaled
-                    if (!mbar_wait(o_ready, (j - 1) & 1)) { atomicExch(a.err, 18); ok = false; }
-                    tc_fence_after();
+                if (j >= 2) {
+                    // this group's previous product PV(j-2) was issued before QK(j), whose completion
+                    // s_full just reported: O is complete and idle until PV(j), which waits for p_ready
 #pragma unroll 1
                     for (int c = 0; c < 4; ++c) {
                         uint32_t o[32];
-                        tmem_ld32(tmem_O + lane_off + c * 32, o);
+                        tmem_ld32(t_o + c * 32, o);
                         tmem_ld_wait();
 #pragma unroll
                         for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                        tmem_st32(tmem_O + lane_off + c * 32, o);
+                        tmem_st32(t_o + c * 32, o);
                     }
                     tmem_st_wait();
                 }
             }
-            // P = exp2(s * scale_log2 - m_used), bf16, into the swizzled K-major tile
-            uint8_t* p_row = p_s + (j & 1) * TILE_BYTES + row * 128;
-            const float neg_m = -m_used;
-            float lsum = 0.f;
+            // P = exp2(s * scale_log2 - m_used) as packed bf16 pairs, written over the score columns
+            // (all of them are in registers by now): 128 scores become 64 columns.
+            // A causal row may have no visible key in any tile of this group so far: m_used is still
+            // -inf then and every score is masked; 0 keeps exp2(-inf + 0) = 0 instead of exp2(-inf + inf)
+            const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
+            float ls0 = 0.f, ls1 = 0.f;
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
+                uint32_t pk[16];
 #pragma unroll
-                for (int g8 = 0; g8 < 4; ++g8) {
-                    float p[8];
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        p[i] = ex2_approx(fmaf(__uint_as_float(r[c][g8 * 8 + i]), a.scale_log2, neg_m));
-                        lsum += p[i];
-                    }
-                    uint4 pk;
-                    pk.x = cvt_bf16x2(p[0], p[1]);
-                    pk.y = cvt_bf16x2(p[2], p[3]);
-                    pk.z = cvt_bf16x2(p[4], p[5]);
-                    pk.w = cvt_bf16x2(p[6], p[7]);
-                    const int col = c * 32 + g8 * 8;          // key column of this 16-byte chunk
-                    const int panel = col >> 6;
-                    const int chunk = (col & 63) >> 3;
-                    *reinterpret_cast<uint4*>(p_row + panel * PANEL_BYTES +
-                                              ((chunk ^ (row & 7)) << 4)) = pk;
+                for (int i = 0; i < 16; ++i) {
+                    float p0 = fmaf(__uint_as_float(r[c][2 * i]), a.scale_log2, neg_m);
+                    float p1 = fmaf(__uint_as_float(r[c][2 * i + 1]), a.scale_log2, neg_m);
+                    if (!(a.dbg & 1)) { p0 = ex2_approx(p0); p1 = ex2_approx(p1); }
+                    ls0 += p0;
+                    ls1 += p1;
+                    pk[i] = cvt_bf16x2(p0, p1);
                 }
+                tmem_st16(t_s + c * 16, pk);
             }
+            tmem_st_wait();
+            const float lsum = ls0 + ls1;
             l += lsum;
-            fence_proxy_async_smem();   // generic-proxy smem writes -> visible to the MMA (async proxy)
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&p_ready[j & 1]);
+            if (lane == 0) mbar_arrive(&p_ready[grp]);
         }
-        // ---- output: O / l -> bf16 -> out[row_g, h*128 ..]
+        // ---- combine the two groups: out = (O0 e^{m0-m} + O1 e^{m1-m}) / (l0 e^{m0-m} + l1 e^{m1-m})
+        s_m[grp][row] = m_used;
+        s_l[grp][row] = l;
+        asm volatile("bar.sync 1, 256;" ::: "memory");      // the eight softmax warps only
         if (ok && n_tiles > 0) {
-            if (!mbar_wait(o_ready, (n_tiles - 1) & 1)) { atomicExch(a.err, 19); ok = false; }
+            if (!mbar_wait(o_done, 0)) { atomicExch(a.err, 19); ok = false; }
             tc_fence_after();
         }
         if (ok) {
-            const float inv_l = 1.0f / l;
-            uint16_t* dst = a.out + (size_t)row_g * a.ldo + (size_t)h * a.out_hoff;
+            const float m0 = s_m[0][row], m1 = s_m[1][row];
+            const float l0 = s_l[0][row], l1 = s_l[1][row];
+            const bool has1 = n_tiles > 1;
+            const float m = has1 ? fmaxf(m0, m1) : m0;
+            const float w0 = ex2_approx(m0 - m);
+            const float w1 = has1 ? ex2_approx(m1 - m) : 0.f;
+            const float inv_l = 1.0f / (l0 * w0 + l1 * w1);
+            const float f0 = w0 * inv_l, f1 = w1 * inv_l;
+            // group 0 writes head-dim columns [0,64), group 1 columns [64,128)
+            uint16_t* dst = a.out + (size_t)row_g * a.ldo + (size_t)h * a.out_hoff + grp * 64;
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                uint32_t o[32];
-                tmem_ld32(tmem_O + lane_off + c * 32, o);
+            for (int c = 0; c < 2; ++c) {
+                uint32_t o0[32], o1[32];
+                const uint32_t col = grp * 64 + c * 32;
+                tmem_ld32(tmem_O + lane_off + col, o0);
+                if (has1) tmem_ld32(tmem_O + 128 + lane_off + col, o1);
                 tmem_ld_wait();
                 if (row_g < a.S) {
+                    float v[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        v[i] = __uint_as_float(o0[i]) * f0;
+                        if (has1) v[i] = fmaf(__uint_as_float(o1[i]), f1, v[i]);
+                    }
                     uint4* d4 = reinterpret_cast<uint4*>(dst + c * 32);
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         uint4 pk;
-                        pk.x = cvt_bf16x2(__uint_as_float(o[i * 8 + 0]) * inv_l, __uint_as_float(o[i * 8 + 1]) * inv_l);
-                        pk.y = cvt_bf16x2(__uint_as_float(o[i * 8 + 2]) * inv_l, __uint_as_float(o[i * 8 + 3]) * inv_l);
-                        pk.z = cvt_bf16x2(__uint_as_float(o[i * 8 + 4]) * inv_l, __uint_as_float(o[i * 8 + 5]) * inv_l);
-                        pk.w = cvt_bf16x2(__uint_as_float(o[i * 8 + 6]) * inv_l, __uint_as_float(o[i * 8 + 7]) * inv_l);
+                        pk.x = cvt_bf16x2(v[i * 8 + 0], v[i * 8 + 1]);
+                        pk.y = cvt_bf16x2(v[i * 8 + 2], v[i * 8 + 3]);
+                        pk.z = cvt_bf16x2(v[i * 8 + 4], v[i * 8 + 5]);
+                        pk.w = cvt_bf16x2(v[i * 8 + 6], v[i * 8 + 7]);
                         d4[i] = pk;
                     }
                 }
@@ -368,6 +412,7 @@ static bool flash_attention_impl(const void* q, int ldq, const void* k, int ldk,
     a.out_hoff = out_head_major ? (long)S * AD : AD;
     if (out_head_major) a.ldo = AD;
     a.err = device_error_word();
+    { const char* e = getenv("O1_ATTN_DBG"); a.dbg = e ? atoi(e) : 0; }
     dim3 grid((S + AQ - 1) / AQ, heads);
     {
         // QK^T + PV over the keys each row can see: 4*heads*128*(ar(ar+1)/2 + (S-ar)*S)

@@ -195,13 +195,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     if (!mbar_wait(&full[stage], phase)) { ok = false; atomicExch(g.err, 3); break; }
                     tc_fence_after();
                     const uint32_t a_addr = smem_u32(smem + stage * Cfg::STAGE_BYTES);
-                    const uint32_t b_addr = a_addr + Cfg::A_BYTES;
+                    const uint64_t ad = umma_desc_sw128(a_addr, 16, 1024);
+                    const uint64_t bd = umma_desc_sw128(a_addr + Cfg::A_BYTES, 16, 1024);
 #pragma unroll
-                    for (int k = 0; k < BK / 16; ++k) {
-                        const uint64_t ad = umma_desc_sw128(a_addr + k * 32, 16, 1024);
-                        const uint64_t bd = umma_desc_sw128(b_addr + k * 32, 16, 1024);
-                        umma_ss(d_tmem, ad, bd, idesc, (kb | k) != 0);
-                    }
+                    for (int k = 0; k < BK / 16; ++k)   // 32 bytes per K step = 2 units of the address field
+                        umma_ss(d_tmem, ad + 2 * k, bd + 2 * k, idesc, (kb | k) != 0);
                     umma_commit(&empty[stage]);
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }

@@ -65,6 +65,50 @@ def seq_t2i(text_len, grid_h, grid_w, fix_point=4096):
     return pos, text_len - 1
 
 
+def seq_ref(text_ids, refs, grid_h, grid_w, fix_point=4096, vision_start_id=151652, image_pad_id=151655):
+    """Token ids, position ids fp32 [3, S] and ar_len for a K-reference (edit / personalise) sequence
+    (o1.c src/runtime/sequence.c:232-410).  `text_ids`: the expanded template -- K runs of
+    <|vision_start|> + cond_h*cond_w <|image_pad|> -- followed by boi and the tms token.  `refs`: one
+    (tokens, grid_h, grid_w, cond_h, cond_w) per reference.  Sequence = text | target grid | reference grids;
+    the target grid sits at fix_point, each reference grid starts at (largest position so far) + 1 on all
+    three axes, and every row from the tms token on attends to everything."""
+    K, T = len(refs), len(text_ids)
+    image_len = grid_h * grid_w
+    S = T + image_len + sum(r[0] for r in refs)
+    ids = list(int(t) for t in text_ids)
+    ids += [vision_start_id] + [image_pad_id] * (image_len - 1)
+    for r in refs:
+        ids += [vision_start_id] + [image_pad_id] * (r[0] - 1)
+    vs = [i for i, t in enumerate(ids) if t == vision_start_id]
+    if len(vs) != 2 * K + 1:
+        raise ValueError("expected %d vision-start tokens, found %d" % (2 * K + 1, len(vs)))
+    pos = torch.zeros(3, S, dtype=torch.float32)
+    max_pos, fp, st_pos = -1, fix_point, 0
+    for v in range(2 * K + 1):
+        skip = v >= K
+        tlen = max(0, vs[v] + 1 - st_pos - (1 if skip else 0))
+        st_idx = max_pos + 1 if max_pos >= 0 else 0
+        pos[:, st_pos:st_pos + tlen] = torch.arange(st_idx, st_idx + tlen, dtype=torch.float32)
+        max_pos = st_idx + tlen - 1
+        gh, gw = (refs[v][3], refs[v][4]) if v < K else ((grid_h, grid_w) if v == K else
+                                                         (refs[v - K - 1][1], refs[v - K - 1][2]))
+        if skip:
+            if fp > 0:
+                fp -= st_idx
+            base, fp = fp + st_idx, 0
+        else:
+            base = tlen + st_idx
+        g0 = st_pos + tlen
+        pos[0, g0:g0 + gh * gw] = float(base)
+        pos[1, g0:g0 + gh * gw] = base + torch.arange(gh, dtype=torch.float32).repeat_interleave(gw)
+        pos[2, g0:g0 + gh * gw] = base + torch.arange(gw, dtype=torch.float32).repeat(gh)
+        max_pos = max(max_pos, base + max(gh, gw) - 1)
+        st_pos += tlen + gh * gw
+    if st_pos < S:
+        pos[:, st_pos:] = torch.arange(max_pos + 1, max_pos + 1 + S - st_pos, dtype=torch.float32)
+    return torch.tensor(ids, dtype=torch.int64), pos, T - 1
+
+
 class Weights:
     """One 256-byte-aligned device arena of bf16 tensors, filled by the library's
     counter-based generator so that the CPU oracle can regenerate any tensor.

@@ -746,6 +746,71 @@ ORC_API int orc_seq_t2i(int text_len, int grid_h, int grid_w, int fix_point, flo
         }
     return text_len - 1;
 }
+/* src/runtime/sequence.c:232-363: K-reference layout.  text_ids [text_len] is the expanded template
+ * (K runs of <|vision_start|> + cond_h*cond_w <|image_pad|>) + boi + tms.  Sequence = text | target
+ * grid | K reference grids.  Vision blocks in order: K template blocks (positions continue the text,
+ * grid at text position), the target (grid at fix_point), K reference blocks (grid at max_pos+1 on all
+ * three axes).  geom[r] = {tokens, grid_h, grid_w, cond_h, cond_w}.  Writes ids [S], pos [3,S];
+ * returns ar_len = text_len - 1 (rows from the tms token on attend to everything, :375-410), or -1. */
+ORC_API int orc_seq_ref(const int64_t *text_ids, int text_len, int K, const int *geom /* [K][5] */, int grid_h,
+                        int grid_w, int fix_point, int64_t vision_start_id, int64_t image_pad_id,
+                        int64_t *ids, float *pos, int S) {
+    const int image_len = grid_h * grid_w;
+    int total = text_len + image_len;
+    for (int r = 0; r < K; ++r) total += geom[r * 5 + 0];
+    if (total != S || K < 0 || K > 20) return -1;
+    memcpy(ids, text_ids, (size_t)text_len * sizeof(int64_t));
+    int off = text_len;
+    ids[off++] = vision_start_id;
+    for (int i = 1; i < image_len; ++i) ids[off++] = image_pad_id;
+    for (int r = 0; r < K; ++r) {
+        ids[off++] = vision_start_id;
+        for (int i = 1; i < geom[r * 5 + 0]; ++i) ids[off++] = image_pad_id;
+    }
+    int vs_pos[41], vs_n = 0;
+    for (int i = 0; i < S && vs_n < 41; ++i)
+        if (ids[i] == vision_start_id) vs_pos[vs_n++] = i;
+    if (vs_n != 2 * K + 1) return -1;
+    int max_pos = -1, fp = fix_point, st_pos = 0;
+    for (int v = 0; v < 2 * K + 1; ++v) {
+        const int ed = vs_pos[v] + 1;
+        const int skip = (v < K) ? 0 : 1;
+        int tlen = ed - st_pos - (skip ? 1 : 0);
+        if (tlen < 0) tlen = 0;
+        const int st_idx = (max_pos >= 0) ? max_pos + 1 : 0;
+        for (int i = 0; i < tlen; ++i)
+            pos[st_pos + i] = pos[S + st_pos + i] = pos[2 * S + st_pos + i] = (float)(st_idx + i);
+        max_pos = st_idx + tlen - 1;
+        int gh, gw;
+        if (v < K) { gh = geom[v * 5 + 3]; gw = geom[v * 5 + 4]; }
+        else if (v == K) { gh = grid_h; gw = grid_w; }
+        else { gh = geom[(v - K - 1) * 5 + 1]; gw = geom[(v - K - 1) * 5 + 2]; }
+        if (gh <= 0 || gw <= 0) return -1;
+        int base;
+        if (skip) {
+            if (fp > 0) fp -= st_idx;
+            base = fp + st_idx;
+            fp = 0;
+        } else {
+            base = tlen + st_idx;
+        }
+        for (int h = 0; h < gh; ++h)
+            for (int w = 0; w < gw; ++w) {
+                const int idx = st_pos + tlen + h * gw + w;
+                pos[idx] = (float)base;
+                pos[S + idx] = (float)(base + h);
+                pos[2 * S + idx] = (float)(base + w);
+            }
+        const int gmax = base + ((gh > gw ? gh : gw) - 1);
+        if (gmax > max_pos) max_pos = gmax;
+        st_pos += tlen + gh * gw;
+    }
+    for (int i = st_pos; i < S; ++i) {
+        const float p = (float)(max_pos + 1 + (i - st_pos));
+        pos[i] = pos[S + i] = pos[2 * S + i] = p;
+    }
+    return text_len - 1;
+}
 /* the bf16 additive mask itself (0 / 0xFF7F), for checking the mask probe */
 ORC_API void orc_prefix_causal_mask(int S, int ar_len, uint16_t *mask /* [S,S] */) {
     for (int r = 0; r < S; ++r)

@@ -7,6 +7,7 @@ needed to RUN the tests, which only read the files written here.
   rng_ref.npz         : outputs of the reference's torch_rng.c (hd_torch_randn_f32,
                         hd_torch_rng_u32), seed 123457, n in {1,8,15,16,17,31,32,1024}
   seq_t2i.npz         : hd_seq_t2i position ids and mask-derived ar_len for three geometries
+  seq_ref.npz         : hd_seq_build ids / position ids / ar_len for K = 1 and K = 4 references
   sigmas_ref.json     : hd_scheduler_derive_{dev,flash,flow_match,default} outputs
 """
 import ctypes as C
@@ -104,6 +105,41 @@ def main():
         seqs[f"{tag}_meta"] = np.array([T, hpx // 32, wpx // 32, S, ar, s.text_len, s.image_len, s.img_begin])
         ref.hd_sequence_free(C.byref(s))
     np.savez_compressed(os.path.join(HERE, "seq_t2i.npz"), **seqs)
+
+    # --- K-reference sequences through hd_seq_build (needs the reference tokenizer, linked into libo1ref)
+    class HdRequest(C.Structure):        # src/runtime/request.h:90-120 (leading fields; the rest zero)
+        _fields_ = [("prompt", C.c_char_p), ("mode", C.c_int), ("profile", C.c_char_p), ("width", C.c_int),
+                    ("height", C.c_int), ("seed", C.c_uint64), ("steps", C.c_int), ("guidance", C.c_float),
+                    ("shift", C.c_float), ("scheduler", C.c_int), ("references", C.c_void_p),
+                    ("reference_count", C.c_size_t), ("tail", C.c_uint8 * 128)]
+
+    class HdRefGeom(C.Structure):
+        _fields_ = [(n, C.c_int) for n in ("tokens", "grid_h", "grid_w", "cond_h", "cond_w")]
+
+    refseq = {}
+    cases = {"k1": ((1024, 1024), [(256, 16, 16, 12, 12)]),                 # tests/unit/test_seq_ref.c:97-119
+             "k4": ((512, 512), [(64, 8, 8, 4, 4), (64, 8, 8, 4, 6), (16, 4, 4, 2, 2), (96, 8, 12, 3, 5)])}
+    for tag, ((hpx, wpx), geoms) in cases.items():
+        K = len(geoms)
+        req = HdRequest(prompt=b"a red fox on the snow", reference_count=K)
+        arr = (HdRefGeom * K)(*[HdRefGeom(*g_) for g_ in geoms])
+        s = HdSequence()
+        rc = ref.hd_seq_build(C.byref(req), 32, 151655, 151656, 151652, 151673, 1, 1, 4096, hpx, wpx, arr, C.byref(s))
+        assert rc == 0, ref.hd_last_error
+        S = s.S
+        ids = np.ctypeslib.as_array(C.cast(s.input_ids, C.POINTER(C.c_int64)), shape=(S,)).copy()
+        pos = np.ctypeslib.as_array(s.pos_f32, shape=(3 * S,)).copy().reshape(3, S)
+        mask = np.ctypeslib.as_array(s.mask_bf16, shape=(S * S,)).copy().reshape(S, S)
+        full_rows = (mask == 0).all(1)
+        ar = int((~full_rows).sum())
+        assert (~full_rows[:ar]).all() and full_rows[ar:].all()
+        for r in range(ar):
+            assert (mask[r, :r + 1] == 0).all() and (mask[r, r + 1:] == 0xFF7F).all()
+        refseq[f"{tag}_ids"], refseq[f"{tag}_pos"] = ids, pos
+        refseq[f"{tag}_geom"] = np.array(geoms, dtype=np.int32)
+        refseq[f"{tag}_meta"] = np.array([s.text_len, hpx // 32, wpx // 32, S, ar, K])
+        ref.hd_sequence_free(C.byref(s))
+    np.savez_compressed(os.path.join(HERE, "seq_ref.npz"), **refseq)
 
     # --- sigma schedules straight from scheduler.c
     sig = {}

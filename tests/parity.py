@@ -96,6 +96,7 @@ def oracle():
     sig("orc_initial_latent", _i, _u64, _i, _i, _i, _f, _P)
     sig("orc_seq_t2i", _i, _i, _i, _i, _i, _P)
     sig("orc_prefix_causal_mask", None, _i, _i, _P)
+    sig("orc_seq_ref", _i, _P, _i, _i, _P, _i, _i, _i, _i64, _i64, _P, _P, _i)
     _oracle = lib
     return lib
 

@@ -324,3 +324,25 @@ def test_initial_latent_layout(orc):
     img = noise.reshape(3, Hpx // p, p, Wpx // p, p)                     # c, h, p1, w, p2
     want = np.transpose(img, (1, 3, 0, 2, 4)).reshape(z.shape) * np.float32(8.0)
     assert (z == f32_to_bf16_np(want)).all()
+
+
+def test_seq_ref_positions(orc, golden, pkg):
+    """K-reference layout against hd_seq_build outputs (K = 1 is the case of tests/unit/test_seq_ref.c:97-119:
+    target at (4096,4096,4096)..4127, the reference grid at max_pos+1 = 4128 on all three axes)."""
+    g = np.load(os.path.join(golden, "seq_ref.npz"))
+    for tag in ("k1", "k4"):
+        T, gh, gw, S, ar, K = (int(v) for v in g[f"{tag}_meta"])
+        geom = np.ascontiguousarray(g[f"{tag}_geom"], dtype=np.int32)
+        want_ids, want_pos = g[f"{tag}_ids"], g[f"{tag}_pos"]
+        text = np.ascontiguousarray(want_ids[:T], dtype=np.int64)
+        ids, pos = np.empty(S, dtype=np.int64), np.empty((3, S), dtype=np.float32)
+        got_ar = orc.orc_seq_ref(np_ptr(text), T, K, np_ptr(geom), gh, gw, 4096, 151652, 151655, np_ptr(ids),
+                                 np_ptr(pos), S)
+        assert got_ar == ar == T - 1
+        assert (ids == want_ids).all() and (pos == want_pos).all()
+        pids, ppos, par = pkg.seq_ref(text.tolist(), [tuple(int(x) for x in r) for r in geom], gh, gw)
+        assert par == ar and (pids.numpy() == want_ids).all() and (ppos.numpy() == want_pos).all()
+    k = g["k1_pos"]
+    T = int(g["k1_meta"][0])
+    assert list(k[:, T]) == [4096, 4096, 4096] and k[:, T:T + 1024].max() == 4127
+    assert list(k[:, T + 1024]) == [4128, 4128, 4128] and list(k[:, -1]) == [4128, 4143, 4143]
