@@ -6,38 +6,35 @@
 //   kh = h / (heads / kv_heads); mask: rows s < ar_len see keys t <= s,
 //   rows s >= ar_len see every key (o1.c src/runtime/sequence.c:120-142).
 //
-// One CTA = 128 query rows of one head.  Operands stay seq-major
-// ([S, heads*128]); head split / merge (attn.cu:180-218) disappear into the
-// TMA coordinates and the output addressing.
-//   warp 0     : TMA producer (Q once, then K/V tiles of 128 keys, 3 stages each)
-//   warp 1     : tcgen05.mma issuer.  S_j = Q K_j^T into TMEM (double buffered),
-//                O += P_j V_j with P read from tensor memory, V as an MN-major operand
-//   warps 2..9 : two softmax groups of four warps; group g takes key tiles j = g (mod 2)
-//                with its own score buffer, P buffer and output accumulator, one thread
-//                per query row (TMEM lane == row): fp32 scores -> running max / sum in
-//                the exp2 domain -> bf16 P written back into tensor memory over the
-//                scores (shared memory carries only Q, K and V: its bandwidth is what
-//                bounds this kernel).  The two partial results are merged at the end
-//                like split-KV decoding: O = sum_g O_g 2^(m_g-m) / sum_g l_g 2^(m_g-m).
-// An accumulator is only rescaled when its running max grows by more than 2^8 (sum
-// and accumulator share the same stale max, so the final division is still exact).
+// One CTA = 256 query rows of one head: two query tiles of 128 rows that share every K/V tile
+// brought into shared memory (shared-memory bandwidth is what bounds this kernel; the K/V
+// fill is its largest avoidable part).  Operands stay seq-major ([S, heads*128]); head split /
+// merge (attn.cu:180-218) disappear into the TMA coordinates and the output addressing.
+//   warp 0     : TMA producer (two Q tiles once, then K tiles (2 stages) and V tiles (3 stages))
+//   warp 1     : tcgen05.mma issuer: S_g = Q_g K_j^T into TMEM, O_g += P_g V_j with P_g read from
+//                tensor memory and V as an MN-major operand, alternating between the groups
+//   warps 2..9 : two softmax groups of four warps, one per query tile, one thread per query row
+//                (TMEM lane == row): fp32 scores -> running max / sum in the exp2 domain ->
+//                bf16 P written back into tensor memory over the scores.
+// An accumulator is only rescaled when its running max grows by more than 2^8 (sum and
+// accumulator share the same stale max, so the final division is still exact).
 #include "common.cuh"
 #include "ptx.cuh"
 #include "kernels.h"
-#include <stdlib.h>
 
 namespace o1 {
 
-static constexpr int AQ = 128;      // query rows per CTA
+static constexpr int AQ = 128;      // query rows per softmax group
+static constexpr int AQ2 = 256;     // query rows per CTA (two groups)
 static constexpr int AKV = 128;     // keys per tile
 static constexpr int AD = 128;      // head dim
 static constexpr int TILE_BYTES = 128 * 128 * 2;   // 32 KB: two 64-column panels of 16 KB
 static constexpr int PANEL_BYTES = 128 * 64 * 2;
-static constexpr int KV_STAGES = 3;
+static constexpr int K_STAGES = 2;
+static constexpr int V_STAGES = 3;
 static constexpr int ATTN_THREADS = 320;   // TMA warp, MMA warp, two softmax groups of four warps
-// Q | K x3 | V x3 (P lives in tensor memory)
-// tiles + 128 B of barriers / slots + 2 KB of per-row max / sum exchange
-static constexpr int ATTN_SMEM = TILE_BYTES * (1 + 2 * KV_STAGES) + 192 + 4 * AQ * 4;
+// Q x2 | K x2 | V x3 (P lives in tensor memory) + 192 B of barriers / slots
+static constexpr int ATTN_SMEM = TILE_BYTES * (2 + K_STAGES + V_STAGES) + 192;
 
 struct AttnArgs {
     uint16_t* out;
@@ -49,7 +46,6 @@ struct AttnArgs {
     int q_hc, q_hr, kv_hc, kv_hr;
     long out_hoff;      // element offset of head h in the output: h * out_hoff
     int* err;
-    int dbg;
 };
 
 __device__ __forceinline__ float ex2_approx(float x) {
@@ -69,33 +65,30 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     // 7 tiles of 32 KB fill the SM's shared memory, so there is no room for an alignment pad or
     // static arrays: the dynamic window itself is declared 1024-byte aligned (checked below).
     extern __shared__ __align__(1024) uint8_t smem[];
-    uint8_t* q_s = smem;
-    uint8_t* k_s = q_s + TILE_BYTES;
-    uint8_t* v_s = k_s + KV_STAGES * TILE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + KV_STAGES * TILE_BYTES);
+    uint8_t* q_s = smem;                               // two query tiles
+    uint8_t* k_s = q_s + 2 * TILE_BYTES;
+    uint8_t* v_s = k_s + K_STAGES * TILE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + V_STAGES * TILE_BYTES);
     uint64_t* q_full = bars;                // 1
-    uint64_t* k_full = bars + 1;            // KV_STAGES
-    uint64_t* k_empty = k_full + KV_STAGES;
-    uint64_t* v_full = k_empty + KV_STAGES;
-    uint64_t* v_empty = v_full + KV_STAGES;
-    uint64_t* s_full = v_empty + KV_STAGES; // 2
+    uint64_t* k_full = bars + 1;            // K_STAGES
+    uint64_t* k_empty = k_full + K_STAGES;
+    uint64_t* v_full = k_empty + K_STAGES;  // V_STAGES
+    uint64_t* v_empty = v_full + V_STAGES;
+    uint64_t* s_full = v_empty + V_STAGES;  // 2 (one per group)
     uint64_t* p_ready = s_full + 2;         // 2
     uint64_t* o_done = p_ready + 2;         // 1
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 1);
     int* s_abort = reinterpret_cast<int*>(tmem_slot + 1);
-    // running max / sum of the two softmax groups, exchanged once at the end
-    float (*s_m)[AQ] = reinterpret_cast<float (*)[AQ]>(bars + 24);
-    float (*s_l)[AQ] = s_m + 2;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int q0 = blockIdx.x * AQ;
+    const int q0 = blockIdx.x * AQ2;
     const int h = blockIdx.y;
     const int kh = h / (a.heads / a.kv_heads);
 
-    // keys this query tile can see
+    // keys this pair of query tiles can see (the second tile's range covers the first's)
     int kv_end = a.S;
-    if (q0 + AQ - 1 < a.ar_len) kv_end = q0 + AQ;   // all rows causal: keys <= last row
+    if (q0 + AQ2 - 1 < a.ar_len) kv_end = q0 + AQ2;   // all rows causal: keys <= last row
     if (kv_end > a.S) kv_end = a.S;
     const int n_tiles = (kv_end + AKV - 1) / AKV;
 
@@ -110,16 +103,9 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
-        for (int s = 0; s < KV_STAGES; ++s) {
-            mbar_init(&k_full[s], 1);
-            mbar_init(&k_empty[s], 1);
-            mbar_init(&v_full[s], 1);
-            mbar_init(&v_empty[s], 1);
-        }
-        for (int s = 0; s < 2; ++s) {
-            mbar_init(&s_full[s], 1);
-            mbar_init(&p_ready[s], 4);
-        }
+        for (int s = 0; s < K_STAGES; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
+        for (int s = 0; s < V_STAGES; ++s) { mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
+        for (int s = 0; s < 2; ++s) { mbar_init(&s_full[s], 1); mbar_init(&p_ready[s], 4); }
         mbar_init(o_done, 1);
         fence_mbar_init();
     }
@@ -131,7 +117,7 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_S = tmem_base;         // score buffers: columns [0,128) and [128,256)
+    const uint32_t tmem_S = tmem_base;         // scores of the two groups: columns [0,128) and [128,256)
     const uint32_t tmem_O = tmem_base + 256;   // output accumulators of the two groups: [256,384), [384,512)
 
     if (warp == 0) {
@@ -140,13 +126,16 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             tma_prefetch_desc(&tmQ);
             tma_prefetch_desc(&tmK);
             tma_prefetch_desc(&tmV);
-            mbar_expect_tx(q_full, TILE_BYTES);
-            tma_load_2d(q_s, &tmQ, q_full, h * a.q_hc, h * a.q_hr + q0);
-            tma_load_2d(q_s + PANEL_BYTES, &tmQ, q_full, h * a.q_hc + 64, h * a.q_hr + q0);
-            // load order follows the consumer: K0, K1, V0, K2, V1, K3, ...
+            mbar_expect_tx(q_full, 2 * TILE_BYTES);
+#pragma unroll
+            for (int g = 0; g < 2; ++g) {
+                tma_load_2d(q_s + g * TILE_BYTES, &tmQ, q_full, h * a.q_hc, h * a.q_hr + q0 + g * AQ);
+                tma_load_2d(q_s + g * TILE_BYTES + PANEL_BYTES, &tmQ, q_full, h * a.q_hc + 64,
+                            h * a.q_hr + q0 + g * AQ);
+            }
             auto load_k = [&](int j) -> bool {
-                const int st = j % KV_STAGES;
-                if (!mbar_wait(&k_empty[st], ((j / KV_STAGES) & 1) ^ 1)) { atomicExch(a.err, 11); return false; }
+                const int st = j % K_STAGES;
+                if (!mbar_wait(&k_empty[st], ((j / K_STAGES) & 1) ^ 1)) { atomicExch(a.err, 11); return false; }
                 mbar_expect_tx(&k_full[st], TILE_BYTES);
                 tma_load_2d(k_s + st * TILE_BYTES, &tmK, &k_full[st], kh * a.kv_hc, kh * a.kv_hr + j * AKV);
                 tma_load_2d(k_s + st * TILE_BYTES + PANEL_BYTES, &tmK, &k_full[st], kh * a.kv_hc + 64,
@@ -154,19 +143,19 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 return true;
             };
             auto load_v = [&](int j) -> bool {
-                const int st = j % KV_STAGES;
-                if (!mbar_wait(&v_empty[st], ((j / KV_STAGES) & 1) ^ 1)) { atomicExch(a.err, 12); return false; }
+                const int st = j % V_STAGES;
+                if (!mbar_wait(&v_empty[st], ((j / V_STAGES) & 1) ^ 1)) { atomicExch(a.err, 12); return false; }
                 mbar_expect_tx(&v_full[st], TILE_BYTES);
                 tma_load_2d(v_s + st * TILE_BYTES, &tmV, &v_full[st], kh * a.kv_hc, kh * a.kv_hr + j * AKV);
                 tma_load_2d(v_s + st * TILE_BYTES + PANEL_BYTES, &tmV, &v_full[st], kh * a.kv_hc + 64,
                             kh * a.kv_hr + j * AKV);
                 return true;
             };
+            // load order follows the consumer: K0, then per tile V(j), K(j+1)
             bool ok = load_k(0);
-            if (ok && n_tiles > 1) ok = load_k(1);
             for (int j = 0; j < n_tiles && ok; ++j) {
                 ok = load_v(j);
-                if (ok && j + 2 < n_tiles) ok = load_k(j + 2);
+                if (ok && j + 1 < n_tiles) ok = load_k(j + 1);
             }
         }
     } else if (warp == 1) {
@@ -174,72 +163,80 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         if (lane == 0) {
             constexpr uint32_t idesc_qk = umma_idesc_bf16(128, 128, 0, 0);
             constexpr uint32_t idesc_pv = umma_idesc_bf16(128, 128, 0, 1);  // V is MN-major
-            const uint64_t q_desc = umma_desc_sw128(smem_u32(q_s), 16, 1024);
             bool ok = mbar_wait(q_full, 0);
             if (!ok) atomicExch(a.err, 13);
-            auto issue_qk = [&](int j) -> bool {
-                const int st = j % KV_STAGES;
-                const uint32_t ph = (j / KV_STAGES) & 1;
-                if (!mbar_wait(&k_full[st], ph)) { atomicExch(a.err, 14); return false; }
-                tc_fence_after();
-                // one descriptor per operand tile; the eight K steps only move its 16-byte-unit address field
-                const uint64_t k_desc = umma_desc_sw128(smem_u32(k_s + st * TILE_BYTES), 16, 1024);
-                const uint32_t d = tmem_S + (j & 1) * 128;
+            // S_g = Q_g K_j^T; one descriptor per operand tile, the eight K steps only move its
+            // 16-byte-unit address field
+            auto issue_qk = [&](int g, uint64_t k_desc) {
+                const uint64_t q_desc = umma_desc_sw128(smem_u32(q_s + g * TILE_BYTES), 16, 1024);
 #pragma unroll
                 for (int kk = 0; kk < AD / 16; ++kk) {
                     const uint64_t off = (uint64_t)(((kk >> 2) * PANEL_BYTES + (kk & 3) * 32) >> 4);
-                    umma_ss(d, q_desc + off, k_desc + off, idesc_qk, kk != 0);
+                    umma_ss(tmem_S + g * 128, q_desc + off, k_desc + off, idesc_qk, kk != 0);
                 }
-                umma_commit(&k_empty[st]);
-                umma_commit(&s_full[j & 1]);
+                umma_commit(&s_full[g]);
+            };
+            auto k_ready = [&](int j, uint64_t& k_desc) -> bool {
+                const int st = j % K_STAGES;
+                if (!mbar_wait(&k_full[st], (j / K_STAGES) & 1)) { atomicExch(a.err, 14); return false; }
+                tc_fence_after();
+                k_desc = umma_desc_sw128(smem_u32(k_s + st * TILE_BYTES), 16, 1024);
                 return true;
             };
-            // Scores run two tiles ahead of the PV products: tile j belongs to softmax group j & 1, which
-            // owns score buffer j & 1, P buffer j & 1 and output accumulator j & 1.
-            if (ok) ok = issue_qk(0);
-            if (ok && n_tiles > 1) ok = issue_qk(1);
+            uint64_t k_desc = 0;
+            if (ok) ok = k_ready(0, k_desc);
+            if (ok) {
+                issue_qk(0, k_desc);
+                issue_qk(1, k_desc);
+                umma_commit(&k_empty[0]);
+            }
+            // Per key tile j and group g: O_g += P_g(j) V_j, then S_g = Q_g K_{j+1}^T.  P_g overlays S_g in
+            // tensor memory: MMAs of one thread execute in issue order, so the next score product
+            // overwrites it only after the PV product has consumed it.  While group g runs its softmax
+            // the tensor pipe works on the other group.
             for (int j = 0; j < n_tiles && ok; ++j) {
-                const int st = j % KV_STAGES;
-                const uint32_t ph = (j / KV_STAGES) & 1;
-                const int g = j & 1;
-                if (!mbar_wait(&v_full[st], ph)) { atomicExch(a.err, 15); ok = false; break; }
-                if (!mbar_wait(&p_ready[g], (j >> 1) & 1)) { atomicExch(a.err, 16); ok = false; break; }
-                tc_fence_after();
-                const uint32_t p_tmem = tmem_S + g * 128;   // bf16 P overlays the first 64 score columns
-                const uint64_t v_desc = umma_desc_sw128(smem_u32(v_s + st * TILE_BYTES), PANEL_BYTES, 1024);
+                const int vst = j % V_STAGES;
+                if (!mbar_wait(&v_full[vst], (j / V_STAGES) & 1)) { atomicExch(a.err, 15); ok = false; break; }
+                const uint64_t v_desc = umma_desc_sw128(smem_u32(v_s + vst * TILE_BYTES), PANEL_BYTES, 1024);
+                const bool more = j + 1 < n_tiles;
+                if (more && !k_ready(j + 1, k_desc)) { ok = false; break; }
 #pragma unroll
-                for (int kk = 0; kk < AKV / 16; ++kk) {
-                    // 16 keys down per step, 128 B per key row
-                    umma_ts(tmem_O + g * 128, p_tmem + kk * 8, v_desc + (uint64_t)((kk * 16 * 128) >> 4), idesc_pv,
-                            (j >= 2) || (kk != 0));
+                for (int g = 0; g < 2; ++g) {
+                    if (!mbar_wait(&p_ready[g], j & 1)) { atomicExch(a.err, 16); ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t p_tmem = tmem_S + g * 128;   // bf16 P in the first 64 score columns
+#pragma unroll
+                    for (int kk = 0; kk < AKV / 16; ++kk)       // 16 keys down per step, 128 B per key row
+                        umma_ts(tmem_O + g * 128, p_tmem + kk * 8, v_desc + (uint64_t)((kk * 16 * 128) >> 4),
+                                idesc_pv, (j | kk) != 0);
+                    if (more) issue_qk(g, k_desc);
                 }
-                umma_commit(&v_empty[st]);
-                // Score buffer g is reused by tile j+2.  Group g finished reading S(j) before p_ready(j);
-                // P(j) overlays it and is read by the PV(j) just issued: MMAs of one thread execute in
-                // issue order, so QK(j+2) overwrites it only after PV(j) has consumed it.
-                if (j + 2 < n_tiles) ok = issue_qk(j + 2);
+                if (!ok) break;
+                umma_commit(&v_empty[vst]);
+                if (more) umma_commit(&k_empty[(j + 1) % K_STAGES]);
             }
             umma_commit(o_done);
         }
     } else {
         // -------------------------------------------------------- softmax groups + output
-        const int grp = (warp - 2) >> 2;         // 0: even key tiles, 1: odd key tiles
+        const int grp = (warp - 2) >> 2;         // which of the CTA's two query tiles
         const int qd = warp & 3;                 // TMEM lane quadrant of this warp
         const int row = qd * 32 + lane;          // row within the query tile
-        const int row_g = q0 + row;              // global query index
+        const int qg0 = q0 + grp * AQ;           // first row of this group's tile
+        const int row_g = qg0 + row;             // global query index
         const uint32_t lane_off = (uint32_t)(qd * 32) << 16;
-        const bool tile_has_causal = q0 < a.ar_len;
+        const bool tile_has_causal = qg0 < a.ar_len;
         const bool row_causal = row_g < a.ar_len;
+        const uint32_t t_s = tmem_S + grp * 128 + lane_off;
         const uint32_t t_o = tmem_O + grp * 128 + lane_off;
-        float m_used = -INFINITY;                // max the stored P / l / O of this group are relative to
+        float m_used = -INFINITY;                // max the stored P / l / O of this row are relative to
         float l = 0.f;
         bool ok = true;
-        for (int j = grp; j < n_tiles && ok; j += 2) {
+        for (int j = 0; j < n_tiles && ok; ++j) {
             const int kv0 = j * AKV;
-            if (!mbar_wait(&s_full[grp], (j >> 1) & 1)) { atomicExch(a.err, 17); ok = false; break; }
+            if (!mbar_wait(&s_full[grp], j & 1)) { atomicExch(a.err, 17); ok = false; break; }
             tc_fence_after();
-            const uint32_t t_s = tmem_S + grp * 128 + lane_off;
-            const bool need_mask = (kv0 + AKV > a.S) || (tile_has_causal && kv0 + AKV - 1 > q0);
+            const bool need_mask = (kv0 + AKV > a.S) || (tile_has_causal && kv0 + AKV - 1 > qg0);
             // the whole score row (128 fp32) goes to registers with one wait
             uint32_t r[4][32];
             tmem_ld32(t_s + 0, r[0]);
@@ -247,7 +244,6 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             tmem_ld32(t_s + 64, r[2]);
             tmem_ld32(t_s + 96, r[3]);
             tmem_ld_wait();
-            float mx = -INFINITY;
             if (need_mask) {
 #pragma unroll
                 for (int c = 0; c < 4; ++c)
@@ -258,6 +254,7 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                         if (!allow) r[c][i] = 0xff800000u;   // -inf
                     }
             }
+            float mx;
             {
                 float mxa = -INFINITY, mxb = -INFINITY, mxc = -INFINITY, mxd = -INFINITY;
 #pragma unroll
@@ -274,13 +271,13 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             if (__any_sync(0xffffffffu, grow)) {
                 float alpha = 1.0f;
                 if (grow) {
-                    alpha = ex2_approx(m_used - m_tile);         // 0 on the group's first tile
+                    alpha = ex2_approx(m_used - m_tile);         // 0 on the first tile
                     m_used = m_tile;
                     l *= alpha;
                 }
-                if (j >= 2) {
-                    // this group's previous product PV(j-2) was issued before QK(j), whose completion
-                    // s_full just reported: O is complete and idle until PV(j), which waits for p_ready
+                if (j >= 1) {
+                    // PV_g(j-1) was issued before QK_g(j), whose completion s_full just reported: O is
+                    // complete and idle until PV_g(j), which waits for p_ready
 #pragma unroll 1
                     for (int c = 0; c < 4; ++c) {
                         uint32_t o[32];
@@ -295,8 +292,8 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             }
             // P = exp2(s * scale_log2 - m_used) as packed bf16 pairs, written over the score columns
             // (all of them are in registers by now): 128 scores become 64 columns.
-            // A causal row may have no visible key in any tile of this group so far: m_used is still
-            // -inf then and every score is masked; 0 keeps exp2(-inf + 0) = 0 instead of exp2(-inf + inf)
+            // A causal row may have no visible key in this tile and none before: m_used is still -inf
+            // then and every score is masked; 0 keeps exp2(-inf + 0) = 0 instead of exp2(-inf + inf)
             const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
             float ls0 = 0.f, ls1 = 0.f;
 #pragma unroll
@@ -304,9 +301,8 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 uint32_t pk[16];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
-                    float p0 = fmaf(__uint_as_float(r[c][2 * i]), a.scale_log2, neg_m);
-                    float p1 = fmaf(__uint_as_float(r[c][2 * i + 1]), a.scale_log2, neg_m);
-                    if (!(a.dbg & 1)) { p0 = ex2_approx(p0); p1 = ex2_approx(p1); }
+                    const float p0 = ex2_approx(fmaf(__uint_as_float(r[c][2 * i]), a.scale_log2, neg_m));
+                    const float p1 = ex2_approx(fmaf(__uint_as_float(r[c][2 * i + 1]), a.scale_log2, neg_m));
                     ls0 += p0;
                     ls1 += p1;
                     pk[i] = cvt_bf16x2(p0, p1);
@@ -314,53 +310,33 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 tmem_st16(t_s + c * 16, pk);
             }
             tmem_st_wait();
-            const float lsum = ls0 + ls1;
-            l += lsum;
+            l += ls0 + ls1;
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&p_ready[grp]);
         }
-        // ---- combine the two groups: out = (O0 e^{m0-m} + O1 e^{m1-m}) / (l0 e^{m0-m} + l1 e^{m1-m})
-        s_m[grp][row] = m_used;
-        s_l[grp][row] = l;
-        asm volatile("bar.sync 1, 256;" ::: "memory");      // the eight softmax warps only
+        // ---- output: O / l -> bf16 -> out[row_g, h*128 ..]
         if (ok && n_tiles > 0) {
             if (!mbar_wait(o_done, 0)) { atomicExch(a.err, 19); ok = false; }
             tc_fence_after();
         }
         if (ok) {
-            const float m0 = s_m[0][row], m1 = s_m[1][row];
-            const float l0 = s_l[0][row], l1 = s_l[1][row];
-            const bool has1 = n_tiles > 1;
-            const float m = has1 ? fmaxf(m0, m1) : m0;
-            const float w0 = ex2_approx(m0 - m);
-            const float w1 = has1 ? ex2_approx(m1 - m) : 0.f;
-            const float inv_l = 1.0f / (l0 * w0 + l1 * w1);
-            const float f0 = w0 * inv_l, f1 = w1 * inv_l;
-            // group 0 writes head-dim columns [0,64), group 1 columns [64,128)
-            uint16_t* dst = a.out + (size_t)row_g * a.ldo + (size_t)h * a.out_hoff + grp * 64;
+            const float inv_l = 1.0f / l;
+            uint16_t* dst = a.out + (size_t)row_g * a.ldo + (size_t)h * a.out_hoff;
 #pragma unroll 1
-            for (int c = 0; c < 2; ++c) {
-                uint32_t o0[32], o1[32];
-                const uint32_t col = grp * 64 + c * 32;
-                tmem_ld32(tmem_O + lane_off + col, o0);
-                if (has1) tmem_ld32(tmem_O + 128 + lane_off + col, o1);
+            for (int c = 0; c < 4; ++c) {
+                uint32_t o[32];
+                tmem_ld32(t_o + c * 32, o);
                 tmem_ld_wait();
                 if (row_g < a.S) {
-                    float v[32];
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        v[i] = __uint_as_float(o0[i]) * f0;
-                        if (has1) v[i] = fmaf(__uint_as_float(o1[i]), f1, v[i]);
-                    }
                     uint4* d4 = reinterpret_cast<uint4*>(dst + c * 32);
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         uint4 pk;
-                        pk.x = cvt_bf16x2(v[i * 8 + 0], v[i * 8 + 1]);
-                        pk.y = cvt_bf16x2(v[i * 8 + 2], v[i * 8 + 3]);
-                        pk.z = cvt_bf16x2(v[i * 8 + 4], v[i * 8 + 5]);
-                        pk.w = cvt_bf16x2(v[i * 8 + 6], v[i * 8 + 7]);
+                        pk.x = cvt_bf16x2(__uint_as_float(o[i * 8 + 0]) * inv_l, __uint_as_float(o[i * 8 + 1]) * inv_l);
+                        pk.y = cvt_bf16x2(__uint_as_float(o[i * 8 + 2]) * inv_l, __uint_as_float(o[i * 8 + 3]) * inv_l);
+                        pk.z = cvt_bf16x2(__uint_as_float(o[i * 8 + 4]) * inv_l, __uint_as_float(o[i * 8 + 5]) * inv_l);
+                        pk.w = cvt_bf16x2(__uint_as_float(o[i * 8 + 6]) * inv_l, __uint_as_float(o[i * 8 + 7]) * inv_l);
                         d4[i] = pk;
                     }
                 }
@@ -412,8 +388,7 @@ static bool flash_attention_impl(const void* q, int ldq, const void* k, int ldk,
     a.out_hoff = out_head_major ? (long)S * AD : AD;
     if (out_head_major) a.ldo = AD;
     a.err = device_error_word();
-    { const char* e = getenv("O1_ATTN_DBG"); a.dbg = e ? atoi(e) : 0; }
-    dim3 grid((S + AQ - 1) / AQ, heads);
+    dim3 grid((S + AQ2 - 1) / AQ2, heads);
     {
         // QK^T + PV over the keys each row can see: 4*heads*128*(ar(ar+1)/2 + (S-ar)*S)
         const double keys = 0.5 * ar_len * (ar_len + 1.0) + (double)(S - ar_len) * S;
