@@ -365,6 +365,27 @@ hd_status o1_denoise_step_cfg_host(const hd_forward_binding *bw, hd_forward_work
                                    int heads, int kv_heads, int hidden, int ff_hidden,
                                    int head_dim, int tms_token_id);
 
+/* ------------------------------------------- host pieces of the step loop + final decode
+ * torch-compatible MT19937 float randn: src/runtime/torch_rng.c:34-121 (hd_torch_rng_seed / _u32 / _randn_f32) */
+void *o1_torch_rng_create(uint64_t seed);
+void o1_torch_rng_randn(void *rng, float *out_host, int64_t n);
+uint32_t o1_torch_rng_u32(void *rng);
+void o1_torch_rng_free(void *rng);
+/* randn(1,3,H,W; seed+1) -> pixel_unshuffle -> x noise_scale -> bf16 [tokens, 3*patch*patch]:
+ * src/runtime/generate.c:78-104, :1264-1268 */
+hd_status o1_initial_latent_host(uint64_t seed, int height, int width, int patch, float noise_scale,
+                                 void *z_host);
+/* src/model/scheduler.c:53-64 (Dev list), :117-158 (flash / flow_match), :173-195 (default); return count */
+int o1_sigmas_dev(float *sigmas /* [29] */);
+int o1_sigmas_flash(int steps, float shift, float *sigmas /* [steps+1] */);
+int o1_sigmas_default(int steps, float shift, float *sigmas /* [steps+1] */);
+/* src/model/scheduler.c:197-208; src/runtime/generate.c:1423-1438 */
+float o1_noise_scale(int n_sigmas, int step_index, float start, float end);
+void o1_noise_clamp_host(float *noise, size_t n, float clip_std);
+/* src/runtime/decode.c:5-27 fused with the NaN / range scan of src/runtime/generate.c:1474-1496, on the device */
+hd_status o1_decode_to_rgb(const void *z_dev, int grid_h, int grid_w, int patch, int channels, void *rgb_dev,
+                           void *stats_dev /* 12 bytes */, int *n_bad, float *vmin, float *vmax);
+
 /* ------------------------------------------- sequence-parallel (Ulysses) form, added
  * No counterpart in the reference (it is single-GPU, src/main.c:242-243).  Token rows are sharded
  * over sp_size ranks: rank r owns rows [r*rows, (r+1)*rows), S = rows*sp_size.  Per block the caller

@@ -144,6 +144,18 @@ _sig("hd_forward", c_int, C.POINTER(ForwardBinding), C.POINTER(ForwardWorkspace)
      C.POINTER(ForwardDiagnostics), _P, _P)
 _sig("hd_lora_merge_gpu", c_int, C.POINTER(LoraEntry), c_size_t, _P)
 _sig("o1_lora_merge_static", c_int, _P, _P, _P, C.c_uint32, C.c_uint32, C.c_uint32, c_float, _P)
+_sig("o1_torch_rng_create", _P, c_uint64)
+_sig("o1_torch_rng_randn", None, _P, _P, c_int64)
+_sig("o1_torch_rng_u32", C.c_uint32, _P)
+_sig("o1_torch_rng_free", None, _P)
+_sig("o1_initial_latent_host", c_int, c_uint64, c_int, c_int, c_int, c_float, _P)
+_sig("o1_sigmas_dev", c_int, _P)
+_sig("o1_sigmas_flash", c_int, c_int, c_float, _P)
+_sig("o1_sigmas_default", c_int, c_int, c_float, _P)
+_sig("o1_noise_scale", c_float, c_int, c_int, c_float, c_float)
+_sig("o1_noise_clamp_host", None, _P, c_size_t, c_float)
+_sig("o1_decode_to_rgb", c_int, _P, c_int, c_int, c_int, c_int, _P, _P, C.POINTER(c_int), C.POINTER(c_float),
+     C.POINTER(c_float))
 _sig("o1_set_stream", None, _P)
 _sig("o1_get_stream", _P)
 _sig("o1_device_error", c_int)

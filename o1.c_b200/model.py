@@ -228,8 +228,16 @@ class Engine:
         check(rc, "hd_decoder_block")
         return (out, bufs) if internals else out
 
-    def forward(self, ids, pos, vinputs, t, out=None, diag_names=()):
-        """hd_forward; t is the model timestep (1 - sigma). Returns x_pred [S, 3072] bf16."""
+    def set_ref_cache(self, xe_ref):
+        """Precomputed x_embedder rows of the trailing reference tokens (forward.h:79-88): the edit path
+        feeds the same reference pixels every step, so their embedding is computed once."""
+        self._xe_ref = xe_ref
+        self.ws.xe_ref = xe_ref.data_ptr() if xe_ref is not None else None
+        self.ws.n_ref = xe_ref.shape[0] if xe_ref is not None else 0
+
+    def forward(self, ids, pos, vinputs, t, out=None, diag_names=(), visual=None):
+        """hd_forward; t is the model timestep (1 - sigma). Returns x_pred [S, 3072] bf16.
+        visual = (mask uint8 [S], image_embeds [V,H], (deepstack0, 1, 2)) device tensors, or None."""
         if out is None:
             out = torch.empty(self.S, PATCH_DIM, dtype=torch.bfloat16, device=self.device)
         self.timestep.fill_(float(t))
@@ -244,8 +252,15 @@ class Engine:
                 bufs[n] = torch.empty(rows, cols, dtype=torch.bfloat16, device=self.device)
                 setattr(diag, n, bufs[n].data_ptr())
         d = self.w.dims
+        vc = None
+        if visual is not None:
+            from . import VisualCond
+            vmask, emb, dss = visual
+            vc = VisualCond(image_embeds=emb.data_ptr(), visual_mask=vmask.data_ptr(), v_tokens=emb.shape[0])
+            for k in range(3):
+                vc.deepstack[k] = dss[k].data_ptr()
         rc = lib.hd_forward(C.byref(self.w.binding), C.byref(self.ws), ptr(ids), self.T, ptr(pos), None,
-                            ptr(vinputs), self.I, None, ptr(self.timestep), ptr(self.sec), self.S,
+                            ptr(vinputs), self.I, C.byref(vc) if vc else None, ptr(self.timestep), ptr(self.sec), self.S,
                             *self.dimargs, TMS_ID, C.byref(diag) if diag else None, ptr(out), None)
         check(rc, "hd_forward")
         return (out, bufs) if diag_names else out

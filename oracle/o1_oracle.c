@@ -412,11 +412,29 @@ typedef struct {
     const uint16_t *te0_w, *te0_b, *te2_w, *te2_b, *xe1_w, *xe2_w, *xe2_b, *fl_w, *fl_b, *fnorm_w;
 } orc_forward_globals;
 
+/* visual conditioning (forward.c:277-285, 363-369; vision_kernels.cu:344-401): rows of the text block
+ * whose vmask byte is set receive the next row of image_embeds before the tms substitution, and after
+ * each of the first three blocks the same rows get deepstack[i] added (bf16 add).  vmask NULL = plain T2I. */
+ORC_API int orc_forward_visual(const orc_forward_globals *g, const orc_block_weights *blocks, int n_layers,
+                               const int64_t *ids, const uint16_t *embed_rows, int T, const float *pos,
+                               int ar_len, const uint16_t *vinputs, int I, float timestep, int64_t tms_id,
+                               uint16_t *out, uint16_t *hidden_dump, int heads, int kv_heads, int H, int ff,
+                               int hd, const uint8_t *vmask /* [S] */, const uint16_t *image_embeds,
+                               const uint16_t *const *deepstack /* [3] */);
 ORC_API int orc_forward(const orc_forward_globals *g, const orc_block_weights *blocks, int n_layers,
                         const int64_t *ids, const uint16_t *embed_rows, int T, const float *pos,
                         int ar_len, const uint16_t *vinputs, int I, float timestep, int64_t tms_id,
                         uint16_t *out, uint16_t *hidden_dump /* [n_layers+1][S,hidden] or NULL */,
                         int heads, int kv_heads, int H, int ff, int hd) {
+    return orc_forward_visual(g, blocks, n_layers, ids, embed_rows, T, pos, ar_len, vinputs, I, timestep, tms_id, out,
+                              hidden_dump, heads, kv_heads, H, ff, hd, NULL, NULL, NULL);
+}
+ORC_API int orc_forward_visual(const orc_forward_globals *g, const orc_block_weights *blocks, int n_layers,
+                               const int64_t *ids, const uint16_t *embed_rows, int T, const float *pos,
+                               int ar_len, const uint16_t *vinputs, int I, float timestep, int64_t tms_id,
+                               uint16_t *out, uint16_t *hidden_dump, int heads, int kv_heads, int H, int ff,
+                               int hd, const uint8_t *vmask, const uint16_t *image_embeds,
+                               const uint16_t *const *deepstack) {
     const int S = T + I;
     const float eps = 1e-6f;
     uint16_t *ha = malloc((size_t)S * H * 2), *hb = malloc((size_t)S * H * 2);
@@ -433,8 +451,12 @@ ORC_API int orc_forward(const orc_forward_globals *g, const orc_block_weights *b
     orc_linear(t_emb, g->te2_w, g->te2_b, te_hidden, 1, H, H);
     memcpy(t_emb, te_hidden, (size_t)H * 2);
     /* steps 1+3 (:272-292): text rows, tms rows replaced by t_emb (embed.cu:44-58) */
-    for (int i = 0; i < T; ++i)
-        memcpy(ha + (size_t)i * H, ids[i] == tms_id ? t_emb : embed_rows + (size_t)i * H, (size_t)H * 2);
+    for (int i = 0, vr = 0; i < T; ++i) {
+        const uint16_t *src = embed_rows + (size_t)i * H;
+        if (vmask && vmask[i]) src = image_embeds + (size_t)(vr++) * H;   /* masked scatter first ... */
+        if (ids[i] == tms_id) src = t_emb;                                /* ... then the tms substitution */
+        memcpy(ha + (size_t)i * H, src, (size_t)H * 2);
+    }
     /* steps 4+5 (:301-325): x_embedder proj1 (no bias), proj2 (+bias), concatenated after the text */
     orc_linear(vinputs, g->xe1_w, NULL, xs, I, 1024, 3072);
     orc_linear(xs, g->xe2_w, g->xe2_b, ha + (size_t)T * H, I, H, 1024);
@@ -444,6 +466,14 @@ ORC_API int orc_forward(const orc_forward_globals *g, const orc_block_weights *b
     int rc = 0;
     for (int l = 0; l < n_layers && rc == 0; ++l) {
         rc = orc_decoder_block(cur_in, pos, ar_len, &blocks[l], cur_out, NULL, S, heads, kv_heads, H, ff, hd);
+        if (vmask && l < 3 && rc == 0) {                                  /* DeepStack add on the pad rows */
+            for (int i = 0, vr = 0; i < S; ++i) {
+                if (!vmask[i]) continue;
+                const uint16_t *d = deepstack[l] + (size_t)(vr++) * H;
+                uint16_t *row = cur_out + (size_t)i * H;
+                for (int c = 0; c < H; ++c) row[c] = f2bf(bf2f(row[c]) + bf2f(d[c]));
+            }
+        }
         if (hidden_dump) memcpy(hidden_dump + (size_t)(l + 1) * S * H, cur_out, (size_t)S * H * 2);
         uint16_t *t = cur_in; cur_in = cur_out; cur_out = t;
     }

@@ -73,6 +73,8 @@ def oracle():
     sig("orc_decoder_block", _i, _P, _P, _i, C.POINTER(BlockW), _P, C.POINTER(_P), _i, _i, _i, _i, _i, _i)
     sig("orc_forward", _i, C.POINTER(Globals), C.POINTER(BlockW), _i, _P, _P, _i, _P, _i, _P, _i, _f,
         _i64, _P, _P, _i, _i, _i, _i, _i)
+    sig("orc_forward_visual", _i, C.POINTER(Globals), C.POINTER(BlockW), _i, _P, _P, _i, _P, _i, _P, _i, _f,
+        _i64, _P, _P, _i, _i, _i, _i, _i, _P, _P, _P)
     sig("orc_sched_vcond", None, _P, _P, _f, _P, _sz)
     sig("orc_sched_cfg_guided", None, _P, _P, _f, _P, _sz)
     sig("orc_sched_flow_match_step", None, _P, _P, _f, _f, _P, _sz)
@@ -297,7 +299,8 @@ def oracle_block(hw, layer, x_u16, pos_np, ar_len, want_ints=True):
     return out, ints
 
 
-def oracle_forward(hw, ids_np, pos_np, ar_len, vin_u16, t, dump=False):
+def oracle_forward(hw, ids_np, pos_np, ar_len, vin_u16, t, dump=False, visual=None):
+    """visual = (vmask uint8 [S], image_embeds u16 [V,H], [deepstack0, 1, 2] u16 [V,H]) or None."""
     d = hw.dims
     T, I = len(ids_np), vin_u16.shape[0]
     S = T + I
@@ -314,10 +317,16 @@ def oracle_forward(hw, ids_np, pos_np, ar_len, vin_u16, t, dump=False):
     ids64 = np.ascontiguousarray(ids_np, dtype=np.int64)
     pos_np = np.ascontiguousarray(pos_np, dtype=np.float32)
     hd = np.empty((hw.n_layers + 1, S, d["hidden"]), dtype=np.uint16) if dump else None
-    rc = oracle().orc_forward(C.byref(g), blocks, hw.n_layers, np_ptr(ids64), np_ptr(rows), T, np_ptr(pos_np),
-                              ar_len, np_ptr(vin_u16), I, float(t), hw.pkg.TMS_ID, np_ptr(out),
-                              np_ptr(hd) if dump else None, d["heads"], d["kv_heads"], d["hidden"], d["ff"],
-                              d["head_dim"])
+    vm = emb = ds = None
+    if visual is not None:
+        vm, emb, dss = visual
+        vm = np.ascontiguousarray(vm, dtype=np.uint8)
+        ds = (C.c_void_p * 3)(*[a.ctypes.data for a in dss])
+    rc = oracle().orc_forward_visual(C.byref(g), blocks, hw.n_layers, np_ptr(ids64), np_ptr(rows), T,
+                                     np_ptr(pos_np), ar_len, np_ptr(vin_u16), I, float(t), hw.pkg.TMS_ID,
+                                     np_ptr(out), np_ptr(hd) if dump else None, d["heads"], d["kv_heads"],
+                                     d["hidden"], d["ff"], d["head_dim"], np_ptr(vm) if visual else None,
+                                     np_ptr(emb) if visual else None, ds)
     assert rc == 0
     return (out, hd) if dump else out
 

@@ -115,3 +115,49 @@ def test_importing_without_the_library_fails_loudly(pkg, tmp_path):
     mod = importlib.util.module_from_spec(spec)
     with pytest.raises(ImportError, match="no fallback"):
         spec.loader.exec_module(mod)
+
+
+def test_host_rng_schedules_and_initial_latent_match_reference_vectors(pkg, golden):
+    """The library's own host code for the step loop (not the oracle): MT19937 randn against the
+    reference's torch_rng.c outputs, sigma schedules against scheduler.c outputs, initial latent layout."""
+    import json
+    import numpy as np
+    lib = pkg.lib
+    g = np.load(os.path.join(golden, "rng_ref.npz"))
+    for n in (1, 8, 15, 16, 17, 31, 32, 1024):
+        h = lib.o1_torch_rng_create(123457)
+        out = np.empty(n, dtype=np.float32)
+        lib.o1_torch_rng_randn(h, out.ctypes.data_as(C.c_void_p), n)
+        lib.o1_torch_rng_free(h)
+        assert (out.view(np.uint32) == g[f"randn_{n}"].view(np.uint32)).all(), n
+    h = lib.o1_torch_rng_create(123457)
+    assert [lib.o1_torch_rng_u32(h) for _ in range(2000)] == g["u32_2000"].tolist()
+    lib.o1_torch_rng_free(h)
+    h = lib.o1_torch_rng_create(1234)
+    chain = np.empty((8, 64), dtype=np.float32)
+    for i in range(8):
+        lib.o1_torch_rng_randn(h, chain[i].ctypes.data_as(C.c_void_p), 64)
+    lib.o1_torch_rng_free(h)
+    assert (chain.view(np.uint32) == g["chain_1234_8x64"].view(np.uint32)).all()
+    ref = json.load(open(os.path.join(golden, "sigmas_ref.json")))
+    s = np.zeros(64, dtype=np.float32)
+    p = s.ctypes.data_as(C.c_void_p)
+    assert lib.o1_sigmas_dev(p) == 29 and s[:29].tolist() == ref["dev"]
+    assert lib.o1_sigmas_flash(28, 1.0, p) == 29 and s[:29].tolist() == ref["flash_28_1"]
+    assert lib.o1_sigmas_flash(28, 3.0, p) == 29 and s[:29].tolist() == ref["flow_match_28_3"]
+    assert lib.o1_sigmas_default(50, 3.0, p) == 51 and s[:51].tolist() == ref["default_50_3"]
+    assert lib.o1_noise_scale(29, 5, 8.0, 4.0) == np.float32(8.0 + (4.0 - 8.0) * 5 / 27)
+    # initial latent: same as the oracle's restatement, and a torch-free layout check
+    import parity
+    Hpx, Wpx = 64, 96
+    z = np.empty(((Hpx // 32) * (Wpx // 32), 3072), dtype=np.uint16)
+    assert lib.o1_initial_latent_host(123456, Hpx, Wpx, 32, 8.0, z.ctypes.data_as(C.c_void_p)) == 0
+    zo = np.empty_like(z)
+    assert parity.oracle().orc_initial_latent(123456, Hpx, Wpx, 32, 8.0, parity.np_ptr(zo)) == 0
+    assert (z == zo).all()
+    assert lib.o1_initial_latent_host(1, 65, 96, 32, 8.0, z.ctypes.data_as(C.c_void_p)) == 6
+    x = np.random.default_rng(0).standard_normal(5000).astype(np.float32) * 3
+    a, b = x.copy(), x.copy()
+    lib.o1_noise_clamp_host(a.ctypes.data_as(C.c_void_p), a.size, 1.5)
+    parity.oracle().orc_noise_clamp(parity.np_ptr(b), b.size, 1.5)
+    assert (a == b).all() and a.max() < x.max()

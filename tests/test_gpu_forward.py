@@ -1,6 +1,7 @@
 """hd_forward and the CFG denoise step through the C ABI against the CPU oracle (and the reference's
 CUDA build when present): few-layer stacks at small geometry, then a short latent chain."""
 import ctypes as C
+import os
 
 import numpy as np
 import pytest
@@ -128,3 +129,78 @@ def test_cfg_denoise_chain_vs_oracle(pkg, orc, dev):
         zo = zn
         nrmse, cos, _, bad = parity.metrics(torch_to_u16(z), zo)
         assert bad == 0 and nrmse <= 5e-3 and cos >= 0.9999, (i, nrmse, cos)
+
+
+def test_decode_to_rgb_and_gate(pkg, dev):
+    """Final latent -> uint8 RGB on the device against the formula of o1.c src/runtime/decode.c:5-27, plus
+    the non-finite count and range the reference's gate (generate.c:1474-1496) is built on."""
+    gh, gw, p = 3, 5, 32
+    z = seeded_bf16((gh * gw, 3 * p * p), 77, 0.0, 0.6)
+    zf = parity.bf16_to_f32_np(z)
+    rgb = torch.zeros(gh * p, gw * p, 3, dtype=torch.uint8, device=dev)
+    stats = torch.zeros(3, dtype=torch.int32, device=dev)
+    nb, mn, mx = C.c_int(), C.c_float(), C.c_float()
+    zd = u16_to_torch(z, dev)
+    rc = pkg.lib.o1_decode_to_rgb(pkg.ptr(zd), gh, gw, p, 3, pkg.ptr(rgb), pkg.ptr(stats), C.byref(nb), C.byref(mn),
+                                  C.byref(mx))
+    assert rc == 0, pkg.last_error()
+    img = zf.reshape(gh, gw, 3, p, p).transpose(0, 3, 1, 4, 2).reshape(gh * p, gw * p, 3)
+    want = np.clip(np.floor((img + 1.0) / 2.0 * 255.0 + 0.5), 0, 255)          # roundf: half away from zero, v >= 0
+    neg = (img + 1.0) / 2.0 * 255.0 < 0
+    want[neg] = 0
+    assert (rgb.cpu().numpy() == want.astype(np.uint8)).all()
+    assert nb.value == 0 and mn.value == zf.min() and mx.value == zf.max()
+    z2 = z.copy()
+    z2[3, 7] = 0x7FC0            # NaN
+    z2[5, 9] = 0x7F80            # +inf
+    zd2 = u16_to_torch(z2, dev)
+    pkg.lib.o1_decode_to_rgb(pkg.ptr(zd2), gh, gw, p, 3, pkg.ptr(rgb), pkg.ptr(stats), C.byref(nb), C.byref(mn), C.byref(mx))
+    assert nb.value == 2
+
+
+def test_multi_reference_forward_with_visual_conditioning(pkg, orc, dev, golden):
+    """Edit / personalise layout (BASELINE config 3 in miniature): text with <image_pad> runs, target grid,
+    K = 4 reference grids with their own 3-axis positions from the hd_seq_build fixture; vision-tower outputs
+    (image_embeds, DeepStack x3) scattered / added on the pad rows; reference rows taken from the x_embedder
+    cache.  Against the oracle, and cache path == recompute path bit for bit."""
+    g = np.load(os.path.join(golden, "seq_ref.npz"))
+    T, gh, gw, S, ar, K = (int(v) for v in g["k4_meta"])
+    ids_all, pos = g["k4_ids"], g["k4_pos"]
+    geom = g["k4_geom"]
+    I_tgt, n_ref = gh * gw, int(geom[:, 0].sum())
+    I = I_tgt + n_ref                                  # every row after the text goes through x_embedder
+    assert T + I == S
+    text = np.ascontiguousarray(ids_all[:T])
+    L = 4                                              # DeepStack touches blocks 0..2
+    w = pkg.Weights(n_layers=L, seed=1234, weight_set="B", device=dev)
+    eng = pkg.Engine(w, T, I, ar_len=ar)
+    vmask = np.zeros(S, dtype=np.uint8)
+    vmask[:T] = (text == 151655)
+    V = int(vmask.sum())
+    assert V == int((geom[:, 3] * geom[:, 4]).sum())
+    emb = seeded_bf16((V, 4096), 81)
+    dss = [seeded_bf16((V, 4096), 82 + k, 0.0, 0.5) for k in range(3)]
+    vin = seeded_bf16((I, 3072), 90)                   # target latent rows, then reference pixel rows
+    idsd, posd = torch.from_numpy(text).to(dev), torch.from_numpy(pos).to(dev)
+    vind = u16_to_torch(vin, dev)
+    vis = (torch.from_numpy(vmask).to(dev), u16_to_torch(emb, dev), [u16_to_torch(d, dev) for d in dss])
+    out = eng.forward(idsd, posd, vind, 0.3, visual=vis)
+    # x_embedder cache for the reference rows (computed once with the same weights)
+    stage = torch.empty(n_ref, 1024, dtype=torch.bfloat16, device=dev)
+    xe_ref = torch.empty(n_ref, 4096, dtype=torch.bfloat16, device=dev)
+    ref_rows = vind[I_tgt:].contiguous()
+    pkg.lib.hd_linear(pkg.ptr(ref_rows), C.c_void_p(w.addr(-1, "xe1_w")), None, pkg.ptr(stage), n_ref, 1024, 3072, 1)
+    pkg.lib.hd_linear(pkg.ptr(stage), C.c_void_p(w.addr(-1, "xe2_w")), C.c_void_p(w.addr(-1, "xe2_b")), pkg.ptr(xe_ref),
+                      n_ref, 4096, 1024, 1)
+    eng.set_ref_cache(xe_ref)
+    out_cached = eng.forward(idsd, posd, vind, 0.3, visual=vis)
+    eng.set_ref_cache(None)
+    torch.cuda.synchronize()
+    assert torch.equal(out.view(torch.int16), out_cached.view(torch.int16)), "x_embedder cache changed the result"
+    hw = parity.HostWeights(pkg, L, 1234, "B")
+    ref = parity.oracle_forward(hw, text, pos, ar, vin, 0.3, visual=(vmask, emb, dss))
+    assert_close(torch_to_u16(out), ref, "E", "multi-reference forward")
+    # the visual inputs matter: without them the prediction differs
+    out_plain = eng.forward(idsd, posd, vind, 0.3)
+    torch.cuda.synchronize()
+    assert parity.metrics(out_plain, out)[0] > 1e-2
