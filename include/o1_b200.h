@@ -259,6 +259,40 @@ typedef struct {
     int v_tokens;
 } hd_visual_cond;
 
+/* src/model/weights.h:75-106: one tensor of the device store / the store itself (one arena) */
+typedef struct {
+    void *dev_ptr;
+    int64_t nbytes;
+    char name[256];
+} hd_device_alloc;
+typedef struct {
+    int device_id;
+    char device_name[256];
+    int compute_major;
+    int compute_minor;
+    int64_t device_mem_bytes;
+    int64_t host_bytes_loaded;
+    int64_t device_bytes_allocated;
+    int64_t n_allocations;
+    int64_t largest_numel;
+    char largest_name[256];
+    hd_device_alloc *allocs;
+    int64_t n_allocs;
+    struct hd_gemm_runtime *gemm;
+    void *arena_ptr;
+    int64_t arena_bytes;
+    void *upload_stream; /* cudaStream_t */
+} hd_weight_store;
+/* src/model/weights.h:125-131.  GGUF v3, tensors F32 / F16 / BF16 (io/gguf.c:196-206), all stored bf16. */
+hd_status hd_weights_to_device_gguf(const char *gguf_path, int device_id, hd_weight_store *out);
+void hd_weight_store_free(hd_weight_store *s);
+const char *hd_weights_last_error(void);
+/* header-only parse, no GPU needed: returns the tensor count (or -1) and describes tensor `index` */
+int64_t o1_gguf_probe(const char *path, int64_t index, char *name_out, size_t name_cap, int64_t *numel, int *type,
+                      int64_t *file_offset);
+/* src/model/block.h:68-70, src/model/forward.h:115-118: bind tensors by their manifest names */
+hd_status hd_block_resolve(const hd_weight_store *wstore, int layer_idx, hd_block_binding *out);
+
 /* src/model/forward.h:122-124 */
 int64_t hd_forward_workspace_bytes(int64_t seq, int img_tokens, int heads, int kv_heads, int hidden,
                                    int ff_hidden, int head_dim, int64_t *block_scratch_bytes);
@@ -272,6 +306,8 @@ hd_status hd_forward(const hd_forward_binding *bw, hd_forward_workspace *ws,
                      int seq, int heads, int kv_heads, int hidden, int ff_hidden, int head_dim,
                      int tms_token_id, hd_forward_diagnostics *diag, void *out_dev, void *stream);
 int hd_forward_num_layers(const hd_forward_binding *bw);
+hd_status hd_forward_resolve(const hd_weight_store *wstore, int n_layers, hd_forward_binding *out);
+void hd_forward_binding_free(hd_forward_binding *b);
 /* src/model/forward.h:177-181 */
 int64_t hd_forward_ws_offset(const char *name, int64_t seq, int text_len, int img_tokens, int heads,
                              int kv_heads, int hidden, int ff_hidden, int head_dim,

@@ -81,6 +81,20 @@ class LoraEntry(C.Structure):
                 ("down_dev", c_void_p), ("up_dev", c_void_p), ("base_dev", c_void_p)]
 
 
+class DeviceAlloc(C.Structure):
+    """hd_device_alloc (src/model/weights.h:75-79)."""
+    _fields_ = [("dev_ptr", c_void_p), ("nbytes", c_int64), ("name", C.c_char * 256)]
+
+
+class WeightStore(C.Structure):
+    """hd_weight_store (src/model/weights.h:81-106)."""
+    _fields_ = [("device_id", c_int), ("device_name", C.c_char * 256), ("compute_major", c_int),
+                ("compute_minor", c_int), ("device_mem_bytes", c_int64), ("host_bytes_loaded", c_int64),
+                ("device_bytes_allocated", c_int64), ("n_allocations", c_int64), ("largest_numel", c_int64),
+                ("largest_name", C.c_char * 256), ("allocs", C.POINTER(DeviceAlloc)), ("n_allocs", c_int64),
+                ("gemm", c_void_p), ("arena_ptr", c_void_p), ("arena_bytes", c_int64), ("upload_stream", c_void_p)]
+
+
 # ----------------------------------------------------------------- signatures
 def _sig(name, restype, *argtypes):
     fn = getattr(lib, name)
@@ -156,6 +170,14 @@ _sig("o1_noise_scale", c_float, c_int, c_int, c_float, c_float)
 _sig("o1_noise_clamp_host", None, _P, c_size_t, c_float)
 _sig("o1_decode_to_rgb", c_int, _P, c_int, c_int, c_int, c_int, _P, _P, C.POINTER(c_int), C.POINTER(c_float),
      C.POINTER(c_float))
+_sig("hd_weights_to_device_gguf", c_int, C.c_char_p, c_int, C.POINTER(WeightStore))
+_sig("hd_weight_store_free", None, C.POINTER(WeightStore))
+_sig("hd_weights_last_error", C.c_char_p)
+_sig("o1_gguf_probe", c_int64, C.c_char_p, c_int64, C.c_char_p, c_size_t, C.POINTER(c_int64), C.POINTER(c_int),
+     C.POINTER(c_int64))
+_sig("hd_block_resolve", c_int, C.POINTER(WeightStore), c_int, C.POINTER(BlockBinding))
+_sig("hd_forward_resolve", c_int, C.POINTER(WeightStore), c_int, C.POINTER(ForwardBinding))
+_sig("hd_forward_binding_free", None, C.POINTER(ForwardBinding))
 _sig("o1_set_stream", None, _P)
 _sig("o1_get_stream", _P)
 _sig("o1_device_error", c_int)
@@ -219,5 +241,5 @@ def use_torch_stream():
 
 
 from .model import (  # noqa: E402
-    Weights, Engine, seq_t2i, seq_ref, dev_sigmas, weight_seed, SLOT_NAMES, GLOBAL_NAMES, tensor_shape,
+    Weights, Engine, seq_t2i, seq_ref, dev_sigmas, write_gguf, gguf_tensor_name, weight_seed, SLOT_NAMES, GLOBAL_NAMES, tensor_shape,
 )

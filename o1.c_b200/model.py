@@ -287,3 +287,59 @@ class Engine:
                                           ptr(z_next_dev), ptr(z_next_host), *self.dimargs, TMS_ID)
         check(rc, "o1_denoise_step_cfg_host")
         return z_next_host
+
+
+# ------------------------------------------------------------------ GGUF packs
+GGUF_NAMES = {
+    "embed_tokens": "model.language_model.embed_tokens.weight", "te0_w": "model.t_embedder1.mlp.0.weight",
+    "te0_b": "model.t_embedder1.mlp.0.bias", "te2_w": "model.t_embedder1.mlp.2.weight",
+    "te2_b": "model.t_embedder1.mlp.2.bias", "xe1_w": "model.x_embedder.proj1.weight",
+    "xe2_w": "model.x_embedder.proj2.weight", "xe2_b": "model.x_embedder.proj2.bias",
+    "fl_w": "model.final_layer2.linear.weight", "fl_b": "model.final_layer2.linear.bias",
+    "fnorm_w": "model.language_model.norm.weight",
+    "q_proj": "self_attn.q_proj.weight", "k_proj": "self_attn.k_proj.weight", "v_proj": "self_attn.v_proj.weight",
+    "o_proj": "self_attn.o_proj.weight", "input_ln": "input_layernorm.weight",
+    "post_ln": "post_attention_layernorm.weight", "gate_proj": "mlp.gate_proj.weight",
+    "up_proj": "mlp.up_proj.weight", "down_proj": "mlp.down_proj.weight", "q_norm": "self_attn.q_norm.weight",
+    "k_norm": "self_attn.k_norm.weight",
+}
+
+
+def gguf_tensor_name(layer, name):
+    """Manifest name of a bound tensor (o1.c src/model/forward.c:70-80, block.c:70-82)."""
+    return GGUF_NAMES[name] if layer < 0 else f"model.language_model.layers.{layer}.{GGUF_NAMES[name]}"
+
+
+def write_gguf(path, tensors, metadata=None, alignment=256):
+    """Writes a GGUF v3 pack in the byte layout of o1.c's tools/hidream_convert.py:223-286: magic, version 3,
+    string key/values + general.alignment (u32), tensor table (dims in torch order, F32 = 0 / F16 = 1 /
+    BF16 = 30), data section aligned to `alignment`, every tensor at an aligned offset.
+    tensors: list of (name, numpy array) with dtype float32, float16 or uint16 (bf16 bit patterns)."""
+    import struct
+    import numpy as np
+
+    def s(b):
+        b = b.encode() if isinstance(b, str) else b
+        return struct.pack("<Q", len(b)) + b
+
+    kv = [(k, v) for k, v in (metadata or {}).items()]
+    head = struct.pack("<IIQQ", 0x46554747, 3, len(tensors), len(kv) + 1)
+    for k, v in kv:
+        head += s(k) + struct.pack("<I", 8) + s(v)
+    head += s("general.alignment") + struct.pack("<I", 4) + struct.pack("<I", alignment)
+    table, off, offsets = b"", 0, []
+    for name, a in tensors:
+        t = {np.dtype(np.float32): 0, np.dtype(np.float16): 1, np.dtype(np.uint16): 30}[a.dtype]
+        table += s(name) + struct.pack("<I", a.ndim) + b"".join(struct.pack("<Q", d) for d in a.shape)
+        table += struct.pack("<I", t) + struct.pack("<Q", off)
+        offsets.append(off)
+        off += (a.nbytes + alignment - 1) // alignment * alignment
+    with open(path, "wb") as f:
+        f.write(head + table)
+        pos = f.tell()
+        f.write(b"\0" * ((pos + alignment - 1) // alignment * alignment - pos))
+        start = f.tell()
+        for (name, a), o in zip(tensors, offsets):
+            f.seek(start + o)
+            f.write(np.ascontiguousarray(a).tobytes())
+        f.truncate(start + off)

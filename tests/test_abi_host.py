@@ -161,3 +161,46 @@ def test_host_rng_schedules_and_initial_latent_match_reference_vectors(pkg, gold
     lib.o1_noise_clamp_host(a.ctypes.data_as(C.c_void_p), a.size, 1.5)
     parity.oracle().orc_noise_clamp(parity.np_ptr(b), b.size, 1.5)
     assert (a == b).all() and a.max() < x.max()
+
+
+def _small_pack(pkg, path, n_layers=2, with_f32=True):
+    import numpy as np
+    rng = np.random.default_rng(3)
+    tensors = []
+    for name in pkg.GLOBAL_NAMES:
+        tensors.append((pkg.gguf_tensor_name(-1, name), rng.integers(0, 65535, size=(3, 40), dtype=np.uint16)))
+    for l in range(n_layers):
+        for name in pkg.SLOT_NAMES:
+            if with_f32 and name == "q_norm":
+                a = rng.standard_normal(128).astype(np.float32)
+            elif with_f32 and name == "k_norm":
+                a = rng.standard_normal(128).astype(np.float16)
+            else:
+                a = rng.integers(0, 0x7F00, size=(5, 24), dtype=np.uint16)
+            tensors.append((pkg.gguf_tensor_name(l, name), a))
+    pkg.write_gguf(path, tensors, {"general.architecture": "hidream_o1", "hidream.profile": "dev",
+                                   "hidream.num_layers": str(n_layers)})
+    return tensors
+
+
+def test_gguf_header_parse_without_gpu(pkg, tmp_path):
+    import numpy as np
+    path = str(tmp_path / "pack.gguf")
+    tensors = _small_pack(pkg, path)
+    n = pkg.lib.o1_gguf_probe(path.encode(), -1, None, 0, None, None, None)
+    assert n == len(tensors)
+    raw = open(path, "rb").read()
+    for i, (name, a) in enumerate(tensors):
+        buf = C.create_string_buffer(256)
+        numel, typ, off = C.c_int64(), C.c_int(), C.c_int64()
+        assert pkg.lib.o1_gguf_probe(path.encode(), i, buf, 256, C.byref(numel), C.byref(typ), C.byref(off)) == n
+        assert buf.value.decode() == name and numel.value == a.size
+        assert typ.value == {np.dtype(np.float32): 0, np.dtype(np.float16): 1, np.dtype(np.uint16): 30}[a.dtype]
+        assert off.value % 256 == 0 and raw[off.value:off.value + a.nbytes] == a.tobytes()
+    bad = tmp_path / "bad.gguf"
+    bad.write_bytes(b"GGUX" + raw[4:200])
+    assert pkg.lib.o1_gguf_probe(str(bad).encode(), -1, None, 0, None, None, None) == -1
+    assert b"bad magic" in pkg.lib.hd_weights_last_error()
+    trunc = tmp_path / "trunc.gguf"
+    trunc.write_bytes(raw[:60])
+    assert pkg.lib.o1_gguf_probe(str(trunc).encode(), -1, None, 0, None, None, None) == -1

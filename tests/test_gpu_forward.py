@@ -204,3 +204,43 @@ def test_multi_reference_forward_with_visual_conditioning(pkg, orc, dev, golden)
     out_plain = eng.forward(idsd, posd, vind, 0.3)
     torch.cuda.synchronize()
     assert parity.metrics(out_plain, out)[0] > 1e-2
+
+
+def test_gguf_pack_to_device_and_resolve(pkg, dev, tmp_path):
+    """hd_weights_to_device_gguf + hd_forward_resolve / hd_block_resolve: every tensor lands bit-exact (bf16
+    unchanged, F32 / F16 rounded to bf16) at a 256-byte aligned address inside one arena, and the bindings
+    point at the right tensors by manifest name; a pack lacking a tensor fails closed."""
+    from test_abi_host import _small_pack
+    path = str(tmp_path / "pack.gguf")
+    tensors = _small_pack(pkg, path, n_layers=2)
+    store = pkg.WeightStore()
+    rc = pkg.lib.hd_weights_to_device_gguf(path.encode(), 0, C.byref(store))
+    assert rc == 0, pkg.lib.hd_weights_last_error()
+    assert store.n_allocs == len(tensors) and store.n_allocations == 1 and store.arena_ptr
+    by_name = {}
+    for i, (name, a) in enumerate(tensors):
+        al = store.allocs[i]
+        assert al.name.decode() == name and al.dev_ptr % 256 == 0 and al.nbytes == a.size * 2
+        assert store.arena_ptr <= al.dev_ptr < store.arena_ptr + store.arena_bytes
+        want = a.ravel() if a.dtype == np.uint16 else parity.f32_to_bf16_np(a.astype(np.float32).ravel())
+        # read the tensor back through the library (bf16 -> fp32 is exact) and compare bit patterns
+        up = torch.empty(a.size, dtype=torch.float32, device=dev)
+        pkg.lib.hd_sched_bf16_upcast(C.c_void_p(al.dev_ptr), pkg.ptr(up), a.size)
+        torch.cuda.synchronize()
+        got = (up.cpu().numpy().view(np.uint32) >> 16).astype(np.uint16)
+        assert (got == want).all(), name
+        by_name[name] = (al.dev_ptr, want)
+    fb = pkg.ForwardBinding()
+    assert pkg.lib.hd_forward_resolve(C.byref(store), 2, C.byref(fb)) == 0, pkg.lib.hd_last_error()
+    assert fb.n_layers == 2 and fb.embed_tokens == by_name[pkg.gguf_tensor_name(-1, "embed_tokens")][0]
+    assert fb.blocks[1].down_proj == by_name[pkg.gguf_tensor_name(1, "down_proj")][0]
+    assert fb.blocks[0].k_norm == by_name[pkg.gguf_tensor_name(0, "k_norm")][0]
+    bb = pkg.BlockBinding()
+    assert pkg.lib.hd_block_resolve(C.byref(store), 2, C.byref(bb)) == 6          # layer 2 is not in the pack
+    assert b"missing weight model.language_model.layers.2." in pkg.lib.hd_last_error()
+    fb3 = pkg.ForwardBinding()
+    assert pkg.lib.hd_forward_resolve(C.byref(store), 3, C.byref(fb3)) == 6
+    pkg.lib.hd_forward_binding_free(C.byref(fb))
+    pkg.lib.hd_weight_store_free(C.byref(store))
+    assert not store.arena_ptr
+    assert pkg.lib.hd_weights_to_device_gguf(b"/nonexistent.gguf", 0, C.byref(store)) != 0
