@@ -28,7 +28,10 @@ WORKLOADS = {
     "c2": (256, 128, 128),   # "2048^2" of BASELINE.json: 16384 image tokens
     "c1": (256, 64, 64),     # 4096 image tokens
     "c0": (256, 32, 32),     # 1024 image tokens
+    "c3": (512, 128, 128),   # multi-reference edit: + 4 reference images of 64x64 tokens (1 GPU only here)
+    "c4": (256, 64, 64),     # c1 geometry after a rank-64 LoRA merge, one image per GPU (data parallel)
 }
+C3_REFS = [(4096, 64, 64, 8, 8)] * 4     # (tokens, grid_h, grid_w, cond_h, cond_w) per reference
 STEPS_PER_IMAGE = 28
 GUIDANCE = 5.0
 
@@ -121,22 +124,42 @@ def run_ours(args):
     lib = pkg.lib
 
     T, gh, gw = WORKLOADS[args.workload]
-    I = gh * gw
+    I_tgt = gh * gw
+    is_ref, is_lora = args.workload == "c3", args.workload == "c4"
+    if is_ref and world > 1:
+        raise SystemExit("workload c3 is measured on one GPU here")
+    I = I_tgt + (sum(r[0] for r in C3_REFS) if is_ref else 0)      # rows that go through x_embedder
     S = T + I
     layers = args.layers
     w = pkg.Weights(n_layers=layers, seed=1234, weight_set="A", device=dev)
-    eng = pkg.Engine(w, T, I)
-    pos, ar = pkg.seq_t2i(T, gh, gw)
-    posd = pos.to(dev)
-    g = torch.Generator().manual_seed(7)
+    g = torch.Generator().manual_seed(7 + (rank if is_lora else 0))
     ids_c = torch.randint(0, 151000, (T,), generator=g, dtype=torch.int64)
     ids_u = torch.randint(0, 151000, (T,), generator=g, dtype=torch.int64)
     ids_c[-1] = ids_u[-1] = pkg.TMS_ID
+    if is_ref:
+        # template with one <|vision_start|> + cond_h*cond_w <|image_pad|> run per reference, then boi + tms
+        for ids in (ids_c, ids_u):
+            o = 8
+            for (_, _, _, ch, cw) in C3_REFS:
+                ids[o] = 151652
+                ids[o + 1:o + 1 + ch * cw] = 151655
+                o += 1 + ch * cw + 3
+            ids[-2] = 151669
+        _, pos, ar = pkg.seq_ref(ids_c.tolist(), C3_REFS, gh, gw)
+    else:
+        pos, ar = pkg.seq_t2i(T, gh, gw)
+    eng = pkg.Engine(w, T, I, ar_len=ar)
+    posd = pos.to(dev)
     ids_c, ids_u = ids_c.to(dev), ids_u.to(dev)
+    lora_ms = None
+    if is_lora:
+        lora_ms = merge_synthetic_lora(pkg, w, layers, dev)
     # seeded N(0, 8^2) latent, the scale of the reference's initial noise (generate.c:1266)
     z = torch.empty(I, 3072, dtype=torch.bfloat16, device=dev)
-    assert lib.o1_fill_normal_bf16(pkg.ptr(z), z.numel(), 42 + 1, 0.0, 8.0) == 0
-    z_next = torch.empty_like(z)
+    assert lib.o1_fill_normal_bf16(pkg.ptr(z), z.numel(), 42 + 1 + (rank if is_lora else 0), 0.0, 8.0) == 0
+    if is_ref:
+        z[I_tgt:].mul_(0.125)               # reference pixel rows ~ N(0,1); the target latent stays ~ N(0,64)
+    z_next = z.clone() if is_ref else torch.empty_like(z)
     z_host = z.cpu().pin_memory()
     z_next_host = torch.empty_like(z_host).pin_memory()
     z_stage = torch.empty_like(z)
@@ -145,9 +168,12 @@ def run_ours(args):
     # parallel layout (o1c_b200.sp.layout): 2 GPUs = CFG pair; 4 / 8 GPUs = CFG pair x Ulysses SP 2 / 4 on ONE
     # image.  Rank pairs with equal sp_rank all-gather their predictions and apply the same scheduler kernel.
     from o1c_b200 import sp as spmod
-    lay, sp_size = spmod.layout(world, cfg=True)
+    if is_lora:
+        lay, sp_size = {r: (r, None, 0) for r in range(world)}, 1       # one image per GPU, no communication
+    else:
+        lay, sp_size = spmod.layout(world, cfg=True)
     image_id, branch, sp_rank = lay[rank]
-    pair = world >= 2
+    pair = world >= 2 and not is_lora
     cfg_group = sp_group = None
     if pair:
         for key in sorted({(v[0], v[2]) for v in lay.values()}):
@@ -176,6 +202,9 @@ def run_ours(args):
 
     def step_device(i, zin, zout):
         s0, s1 = sig[i % STEPS_PER_IMAGE], sig[i % STEPS_PER_IMAGE + 1]
+        if is_ref:
+            eng.denoise_step_cfg_ref(ids_c, ids_u, posd, zin, I_tgt, s0, s1, GUIDANCE, zout)
+            return
         if not pair:
             eng.denoise_step_cfg(ids_c, ids_u, posd, zin, s0, s1, GUIDANCE, zout)
             return
@@ -196,7 +225,7 @@ def run_ours(args):
 
     def step_host(i):
         s0, s1 = sig[i % STEPS_PER_IMAGE], sig[i % STEPS_PER_IMAGE + 1]
-        if not pair:
+        if not pair and not is_ref:
             eng.denoise_step_cfg_host(ids_c, ids_u, posd, z_host, z_stage, s0, s1, GUIDANCE, z_next, z_next_host)
             return
         z_stage.copy_(z_host, non_blocking=True)
@@ -283,12 +312,14 @@ def run_ours(args):
             "n_gpus": world, "steps": args.steps, "warmup": warm, "ms_per_step": round(ms_step, 3),
             "higher_is_better": False, "scaling": "strong" if images == 1 else "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"{args.workload}: {I} image tokens ({gh}x{gw}) + {T} text tokens, "
+            "config": {"workload": f"{args.workload}: {I} image tokens ({gh}x{gw}"
+                                   + (" target + 4 references of 64x64" if is_ref else "") + f") + {T} text tokens, "
                                    f"{layers} decoder blocks, CFG (2 forwards/step), guidance {GUIDANCE}, "
                                    f"flow-match Euler, Dev sigmas",
                        "seq_len": S, "layers": layers, "steps_per_image": STEPS_PER_IMAGE,
                        "parallelism": "1 GPU" if world == 1 else
-                                      f"cfg pair x ulysses sp{sp_size}" + (f" x dp{images}" if images > 1 else ""),
+                                      (f"dp{images} (one image per GPU)" if is_lora else f"cfg pair x ulysses sp{sp_size}"
+                                       + (f" x dp{images}" if images > 1 else "")),
                        "weights": "random-init N(0,0.02) bf16, seed 1234",
                        "l2": "no flush needed: every step streams 2 x %.1f GB of weights (L2 is 126 MB)"
                              % (w.nbytes() / 1e9)},
@@ -306,6 +337,9 @@ def run_ours(args):
                          "ms_per_launch": round(per_launch_ms, 4)},
             "kernels": kinds,
         }
+        if lora_ms is not None:
+            out["lora_merge_ms"] = round(lora_ms, 2)
+            out["config"]["lora"] = "rank 64, A,B ~ N(0,0.01), alpha 64, merged into the 7 linears of every block"
         if args.short:
             out["short_profiler_run"] = True
             out.pop("e2e")
@@ -314,6 +348,37 @@ def run_ours(args):
     if world > 1:
         dist.destroy_process_group()
     return out
+
+
+def merge_synthetic_lora(pkg, w, layers, dev):
+    """BASELINE config 4: rank-64 adapters (A, B ~ N(0, 0.01), alpha = 64, multiplier 1) merged at load into
+    every linear of every block through hd_lora_merge_gpu.  Returns the merge time in ms (CUDA events)."""
+    import torch
+    targets = ["q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj"]
+    R = 64
+    ents = (pkg.LoraEntry * (layers * len(targets)))()
+    keep = []
+    k = 0
+    for l in range(layers):
+        for name in targets:
+            N, K = pkg.tensor_shape(name)
+            up = torch.empty(N, R, device=dev)
+            down = torch.empty(R, K, device=dev)
+            pkg.lib.o1_fill_normal_f32(pkg.ptr(up), up.numel(), 5000 + k * 2, 0.0, 0.01)
+            pkg.lib.o1_fill_normal_f32(pkg.ptr(down), down.numel(), 5001 + k * 2, 0.0, 0.01)
+            keep += [up, down]
+            e = ents[k]
+            e.rank, e.in_dim, e.out_dim, e.alpha, e.multiplier = R, K, N, 64.0, 1.0
+            e.up_dev, e.down_dev, e.base_dev = up.data_ptr(), down.data_ptr(), w.addr(l, name)
+            k += 1
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    rc = pkg.lib.hd_lora_merge_gpu(ents, len(ents), C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    e1.record()
+    torch.cuda.synchronize()
+    assert rc == 0, pkg.last_error()
+    return e0.elapsed_time(e1)
 
 
 def cpu_baseline(pkg, flops_step, S_sample=(256, 32, 32)):

@@ -390,6 +390,16 @@ hd_status o1_denoise_step_cfg(const hd_forward_binding *bw, hd_forward_workspace
                               float guidance, void *xp_scratch, void *z_next, int heads,
                               int kv_heads, int hidden, int ff_hidden, int head_dim,
                               int tms_token_id);
+/* Same step for reference / edit sequences (src/runtime/generate.c:858-941): z holds the target latent rows
+ * followed by the static reference rows (img_tokens rows in all, the vinputs of hd_forward); only the first
+ * target_tokens rows are stepped into z_next [target_tokens, 3072].  visual may be NULL. */
+hd_status o1_denoise_step_cfg_ref(const hd_forward_binding *bw, hd_forward_workspace *ws,
+                                  const int64_t *ids_cond, const int64_t *ids_uncond, int text_len,
+                                  const float *pos_f32, int ar_len, const void *z, int img_tokens,
+                                  int target_tokens, const hd_visual_cond *visual, const float *timestep_dev,
+                                  float sigma, float sigma_next, float guidance, void *xp_scratch, void *z_next,
+                                  int heads, int kv_heads, int hidden, int ff_hidden, int head_dim,
+                                  int tms_token_id);
 /* Same step with HOST latents: copies z_host -> device, runs the step, copies
  * z_next back and synchronises.  z_dev / z_next_dev are caller-owned staging. */
 hd_status o1_denoise_step_cfg_host(const hd_forward_binding *bw, hd_forward_workspace *ws,

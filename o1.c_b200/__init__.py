@@ -199,6 +199,9 @@ _sig("o1_hash_normal_host", c_float, c_uint64, c_uint64)
 _sig("o1_denoise_step_cfg", c_int, C.POINTER(ForwardBinding), C.POINTER(ForwardWorkspace), _P, _P,
      c_int, _P, c_int, _P, c_int, _P, c_float, c_float, c_float, _P, _P, c_int, c_int, c_int, c_int,
      c_int, c_int)
+_sig("o1_denoise_step_cfg_ref", c_int, C.POINTER(ForwardBinding), C.POINTER(ForwardWorkspace), _P, _P,
+     c_int, _P, c_int, _P, c_int, c_int, C.POINTER(VisualCond), _P, c_float, c_float, c_float, _P, _P, c_int,
+     c_int, c_int, c_int, c_int, c_int)
 _sig("o1_denoise_step_cfg_host", c_int, C.POINTER(ForwardBinding), C.POINTER(ForwardWorkspace), _P,
      _P, c_int, _P, c_int, _P, _P, c_int, c_float, c_float, c_float, _P, _P, _P, _P, c_int, c_int,
      c_int, c_int, c_int, c_int)

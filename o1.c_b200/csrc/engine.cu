@@ -818,6 +818,22 @@ hd_status o1_denoise_step_cfg(const hd_forward_binding* bw, hd_forward_workspace
                               const float* timestep_dev, float sigma, float sigma_next, float guidance,
                               void* xp_scratch, void* z_next, int heads, int kv_heads, int hidden,
                               int ff_hidden, int head_dim, int tms_token_id) {
+    return o1_denoise_step_cfg_ref(bw, ws, ids_cond, ids_uncond, text_len, pos_f32, ar_len, z, img_tokens,
+                                   img_tokens, nullptr, timestep_dev, sigma, sigma_next, guidance, xp_scratch,
+                                   z_next, heads, kv_heads, hidden, ff_hidden, head_dim, tms_token_id);
+}
+
+hd_status o1_denoise_step_cfg_ref(const hd_forward_binding* bw, hd_forward_workspace* ws,
+                                  const int64_t* ids_cond, const int64_t* ids_uncond, int text_len,
+                                  const float* pos_f32, int ar_len, const void* z, int img_tokens,
+                                  int target_tokens, const hd_visual_cond* visual, const float* timestep_dev,
+                                  float sigma, float sigma_next, float guidance, void* xp_scratch, void* z_next,
+                                  int heads, int kv_heads, int hidden, int ff_hidden, int head_dim,
+                                  int tms_token_id) {
+    if (target_tokens <= 0 || target_tokens > img_tokens) {
+        hd_set_error("denoise_step: target_tokens out of range");
+        return HD_ERR_MISSING;
+    }
     if (!bw || !ws || !ws->hidden_a || !ids_cond || !ids_uncond || !pos_f32 || !z || !timestep_dev ||
         !xp_scratch || !z_next) {
         hd_set_error("denoise_step: null argument");
@@ -830,15 +846,16 @@ hd_status o1_denoise_step_cfg(const hd_forward_binding* bw, hd_forward_workspace
     const int S = text_len + img_tokens;
     uint16_t* xc = (uint16_t*)xp_scratch;
     uint16_t* xu = xc + (size_t)S * 3072;
-    hd_status s = forward_impl(bw, ws, ids_cond, text_len, pos_f32, ar_len, z, img_tokens, nullptr,
+    hd_status s = forward_impl(bw, ws, ids_cond, text_len, pos_f32, ar_len, z, img_tokens, visual,
                                timestep_dev, S, heads, kv_heads, hidden, ff_hidden, head_dim,
                                tms_token_id, nullptr, xc, g_stream);
     if (s != HD_OK) return s;
-    s = forward_impl(bw, ws, ids_uncond, text_len, pos_f32, ar_len, z, img_tokens, nullptr, timestep_dev,
+    s = forward_impl(bw, ws, ids_uncond, text_len, pos_f32, ar_len, z, img_tokens, visual, timestep_dev,
                      S, heads, kv_heads, hidden, ff_hidden, head_dim, tms_token_id, nullptr, xu, g_stream);
     if (s != HD_OK) return s;
-    // image rows start at row text_len of each prediction (generate.c:1330 slices them by a copy)
-    const size_t n = (size_t)img_tokens * 3072;
+    // target rows start at row text_len of each prediction (generate.c:1330 slices them by a copy);
+    // reference rows that follow the target in z are inputs only and are not stepped
+    const size_t n = (size_t)target_tokens * 3072;
     if (!sched_cfg_flow_step(z, xc + (size_t)text_len * 3072, xu + (size_t)text_len * 3072, sigma,
                              sigma_next, guidance, z_next, n, g_stream)) {
         hd_set_error("denoise_step: scheduler: %s", g_cuda_err);

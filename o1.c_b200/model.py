@@ -277,6 +277,17 @@ class Engine:
         check(rc, "o1_denoise_step_cfg")
         return z_next
 
+    def denoise_step_cfg_ref(self, ids_c, ids_u, pos, vin, target_tokens, sigma, sigma_next, guidance, z_next):
+        """CFG step of a reference / edit sequence: vin [I, 3072] = target latent rows then the static
+        reference rows; only the first target_tokens rows are stepped into z_next."""
+        self.timestep.fill_(1.0 - float(sigma))
+        rc = lib.o1_denoise_step_cfg_ref(C.byref(self.w.binding), C.byref(self.ws), ptr(ids_c), ptr(ids_u), self.T,
+                                         ptr(pos), self.ar_len, ptr(vin), self.I, target_tokens, None,
+                                         ptr(self.timestep), float(sigma), float(sigma_next), float(guidance),
+                                         ptr(self.xp), ptr(z_next), *self.dimargs, TMS_ID)
+        check(rc, "o1_denoise_step_cfg_ref")
+        return z_next
+
     def denoise_step_cfg_host(self, ids_c, ids_u, pos, z_host, z_dev, sigma, sigma_next, guidance,
                               z_next_dev, z_next_host):
         """Same step through host (pinned) latents: H2D, step, D2H, synchronise."""
