@@ -32,6 +32,10 @@ WORKLOADS = {
     "c4": (256, 64, 64),     # c1 geometry after a rank-64 LoRA merge, one image per GPU (data parallel)
 }
 C3_REFS = [(4096, 64, 64, 8, 8)] * 4     # (tokens, grid_h, grid_w, cond_h, cond_w) per reference
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture summarised in
+# profiles/traffic_S16640.md (same kernels, same shapes, 2 decoder blocks instead of 36)
+NCU_TRAFFIC_BYTES = {("c2", "flash_attn"): 304484864, ("c2", "gemm_swiglu"): 1563173632,
+                     ("c2", "gemm_resid"): 2490380800}
 STEPS_PER_IMAGE = 28
 GUIDANCE = 5.0
 
@@ -332,7 +336,8 @@ def run_ours(args):
             "gpu_launches": int(launches),
             "clocks": clocks,
             "roofline": {"bound": "tensor", "kernel": top[0], "achieved": achieved, "peak": sustained,
-                         "unit": "TFLOP/s", "frac": round(achieved / sustained, 4), "traffic": None,
+                         "unit": "TFLOP/s", "frac": round(achieved / sustained, 4),
+                         "traffic": NCU_TRAFFIC_BYTES.get((args.workload, top[0])) if world == 1 else None,
                          "peak_source": f"{src} (sustained bf16; burst {burst})",
                          "ms_per_launch": round(per_launch_ms, 4)},
             "kernels": kinds,

@@ -457,7 +457,12 @@ bool gemm_bf16_ex(const void* x, int ldx, const void* w, const void* w2, void* y
     g.scale = scale;
     g.err = device_error_word();
     g.num_m = (M + BM - 1) / BM;
-    g.group_m = 32;
+    // Row tiles are visited in groups whose activation slab (group_m x 128 rows x K) stays L2-resident
+    // (about 48 MB of the 126 MB) while the weights stream past it.
+    {
+        long gm = (48l << 20) / ((long)BM * K * 2);
+        g.group_m = (int)(gm < 4 ? 4 : (gm > 32 ? 32 : gm));
+    }
     g.o_cb = o_cb; g.o_cb_stride = o_cb_stride;
     g.a_kblk = a_kblk; g.a_rows = a_rows;
 
