@@ -13,9 +13,12 @@
 //   warp 0     : TMA producer (two Q tiles once, then K tiles (2 stages) and V tiles (3 stages))
 //   warp 1     : tcgen05.mma issuer: S_g = Q_g K_j^T into TMEM, O_g += P_g V_j with P_g read from
 //                tensor memory and V as an MN-major operand, alternating between the groups
-//   warps 2..9 : two softmax groups of four warps, one per query tile, one thread per query row
-//                (TMEM lane == row): fp32 scores -> running max / sum in the exp2 domain ->
-//                bf16 P written back into tensor memory over the scores.
+//   warps 2..17: two softmax groups of eight warps, one group per query tile, two threads per query
+//                row (TMEM lane == row; the warps w and w+4 of a group own the same 32 lanes and
+//                take 64 score columns each): fp32 scores -> running max (halves exchanged through
+//                shared memory) / sum in the exp2 domain -> bf16 P written back into tensor memory
+//                over the scores.  The softmax -> PV -> next-scores round trip of a group is the
+//                critical path of the kernel, which is why a row is split over two threads.
 // An accumulator is only rescaled when its running max grows by more than 2^8 (sum and
 // accumulator share the same stale max, so the final division is still exact).
 #include "common.cuh"
@@ -32,9 +35,10 @@ static constexpr int TILE_BYTES = 128 * 128 * 2;   // 32 KB: two 64-column panel
 static constexpr int PANEL_BYTES = 128 * 64 * 2;
 static constexpr int K_STAGES = 2;
 static constexpr int V_STAGES = 3;
-static constexpr int ATTN_THREADS = 320;   // TMA warp, MMA warp, two softmax groups of four warps
-// Q x2 | K x2 | V x3 (P lives in tensor memory) + 192 B of barriers / slots
-static constexpr int ATTN_SMEM = TILE_BYTES * (2 + K_STAGES + V_STAGES) + 192;
+static constexpr int ATTN_THREADS = 576;   // TMA warp, MMA warp, two softmax groups of eight warps
+// Q x2 | K x2 | V x3 (P lives in tensor memory) + 192 B of barriers / slots + row-max exchange
+static constexpr int ATTN_XCH = 2 * 2 * 128 * 4;   // [group][column half][row] floats
+static constexpr int ATTN_SMEM = TILE_BYTES * (2 + K_STAGES + V_STAGES) + 192 + ATTN_XCH;
 
 struct AttnArgs {
     uint16_t* out;
@@ -79,6 +83,7 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     uint64_t* o_done = p_ready + 2;         // 1
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 1);
     int* s_abort = reinterpret_cast<int*>(tmem_slot + 1);
+    float* xch = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + 192);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -105,7 +110,7 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         mbar_init(q_full, 1);
         for (int s = 0; s < K_STAGES; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
         for (int s = 0; s < V_STAGES; ++s) { mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
-        for (int s = 0; s < 2; ++s) { mbar_init(&s_full[s], 1); mbar_init(&p_ready[s], 4); }
+        for (int s = 0; s < 2; ++s) { mbar_init(&s_full[s], 1); mbar_init(&p_ready[s], 8); }
         mbar_init(o_done, 1);
         fence_mbar_init();
     }
@@ -219,8 +224,9 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         }
     } else {
         // -------------------------------------------------------- softmax groups + output
-        const int grp = (warp - 2) >> 2;         // which of the CTA's two query tiles
-        const int qd = warp & 3;                 // TMEM lane quadrant of this warp
+        const int grp = (warp - 2) >> 3;         // which of the CTA's two query tiles
+        const int half = ((warp - 2) >> 2) & 1;  // which 64 score / output columns of the row
+        const int qd = warp & 3;                 // TMEM lane quadrant this warp may access
         const int row = qd * 32 + lane;          // row within the query tile
         const int qg0 = q0 + grp * AQ;           // first row of this group's tile
         const int row_g = qg0 + row;             // global query index
@@ -228,25 +234,26 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         const bool tile_has_causal = qg0 < a.ar_len;
         const bool row_causal = row_g < a.ar_len;
         const uint32_t t_s = tmem_S + grp * 128 + lane_off;
-        const uint32_t t_o = tmem_O + grp * 128 + lane_off;
+        const uint32_t t_o = tmem_O + grp * 128 + half * 64 + lane_off;
+        float* x_mine = xch + (grp * 2 + half) * 128 + row;
+        const float* x_other = xch + (grp * 2 + (half ^ 1)) * 128 + row;
+        const int bar_id = 1 + grp;              // named barrier of the group's 256 threads
         float m_used = -INFINITY;                // max the stored P / l / O of this row are relative to
-        float l = 0.f;
+        float l = 0.f;                           // this thread's share of the row sum
         bool ok = true;
         for (int j = 0; j < n_tiles && ok; ++j) {
-            const int kv0 = j * AKV;
+            const int kv0 = j * AKV + half * 64;
             if (!mbar_wait(&s_full[grp], j & 1)) { atomicExch(a.err, 17); ok = false; break; }
             tc_fence_after();
-            const bool need_mask = (kv0 + AKV > a.S) || (tile_has_causal && kv0 + AKV - 1 > qg0);
-            // the whole score row (128 fp32) goes to registers with one wait
-            uint32_t r[4][32];
-            tmem_ld32(t_s + 0, r[0]);
-            tmem_ld32(t_s + 32, r[1]);
-            tmem_ld32(t_s + 64, r[2]);
-            tmem_ld32(t_s + 96, r[3]);
+            const bool need_mask = (kv0 + 64 > a.S) || (tile_has_causal && kv0 + 63 > qg0);
+            // this thread's 64 fp32 scores go to registers with one wait
+            uint32_t r[2][32];
+            tmem_ld32(t_s + half * 64, r[0]);
+            tmem_ld32(t_s + half * 64 + 32, r[1]);
             tmem_ld_wait();
             if (need_mask) {
 #pragma unroll
-                for (int c = 0; c < 4; ++c)
+                for (int c = 0; c < 2; ++c)
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
                         const int key = kv0 + c * 32 + i;
@@ -258,14 +265,20 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             {
                 float mxa = -INFINITY, mxb = -INFINITY, mxc = -INFINITY, mxd = -INFINITY;
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
+                for (int i = 0; i < 16; ++i) {
                     mxa = fmaxf(mxa, __uint_as_float(r[0][i]));
-                    mxb = fmaxf(mxb, __uint_as_float(r[1][i]));
-                    mxc = fmaxf(mxc, __uint_as_float(r[2][i]));
-                    mxd = fmaxf(mxd, __uint_as_float(r[3][i]));
+                    mxb = fmaxf(mxb, __uint_as_float(r[0][16 + i]));
+                    mxc = fmaxf(mxc, __uint_as_float(r[1][i]));
+                    mxd = fmaxf(mxd, __uint_as_float(r[1][16 + i]));
                 }
                 mx = fmaxf(fmaxf(mxa, mxb), fmaxf(mxc, mxd));
             }
+            // row max over both halves: the partner thread's value comes through shared memory.  The slot
+            // is rewritten one tile later, after the partner has arrived on p_ready and a new s_full
+            // has come round, so one barrier per tile is enough.
+            *x_mine = mx;
+            asm volatile("bar.sync %0, 256;" ::"r"(bar_id) : "memory");
+            mx = fmaxf(mx, *x_other);
             const float m_tile = mx * a.scale_log2;
             const bool grow = (m_tile - m_used) > 8.0f;      // also true while m_used == -inf
             if (__any_sync(0xffffffffu, grow)) {
@@ -277,27 +290,29 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 }
                 if (j >= 1) {
                     // PV_g(j-1) was issued before QK_g(j), whose completion s_full just reported: O is
-                    // complete and idle until PV_g(j), which waits for p_ready
+                    // complete and idle until PV_g(j), which waits for p_ready.  Each thread scales its
+                    // own 64 output columns.
 #pragma unroll 1
                     for (int c = 0; c < 4; ++c) {
-                        uint32_t o[32];
-                        tmem_ld32(t_o + c * 32, o);
+                        uint32_t o[16];
+                        tmem_ld16(t_o + c * 16, o);
                         tmem_ld_wait();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                        tmem_st32(t_o + c * 32, o);
+                        for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tmem_st16(t_o + c * 16, o);
                     }
                     tmem_st_wait();
                 }
             }
             // P = exp2(s * scale_log2 - m_used) as packed bf16 pairs, written over the score columns
-            // (all of them are in registers by now): 128 scores become 64 columns.
+            // (this half's 64 scores are in registers by now, and the partner only writes after the
+            // barrier above, i.e. after both loads): 64 scores become 32 columns at [half*32, +32).
             // A causal row may have no visible key in this tile and none before: m_used is still -inf
             // then and every score is masked; 0 keeps exp2(-inf + 0) = 0 instead of exp2(-inf + inf)
             const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
             float ls0 = 0.f, ls1 = 0.f;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < 2; ++c) {
                 uint32_t pk[16];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
@@ -307,7 +322,7 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                     ls1 += p1;
                     pk[i] = cvt_bf16x2(p0, p1);
                 }
-                tmem_st16(t_s + c * 16, pk);
+                tmem_st16(t_s + half * 32 + c * 16, pk);
             }
             tmem_st_wait();
             l += ls0 + ls1;
@@ -315,16 +330,21 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             __syncwarp();
             if (lane == 0) mbar_arrive(&p_ready[grp]);
         }
-        // ---- output: O / l -> bf16 -> out[row_g, h*128 ..]
+        // ---- output: O / l -> bf16 -> out[row_g, h*128 + half*64 ..]
         if (ok && n_tiles > 0) {
             if (!mbar_wait(o_done, 0)) { atomicExch(a.err, 19); ok = false; }
             tc_fence_after();
         }
+        // the row sum is the two threads' shares together (same exchange slots; every thread of the
+        // group reaches this barrier: a failed wait above fails for the whole group alike)
+        *x_mine = l;
+        asm volatile("bar.sync %0, 256;" ::"r"(bar_id) : "memory");
+        l += *x_other;
         if (ok) {
             const float inv_l = 1.0f / l;
-            uint16_t* dst = a.out + (size_t)row_g * a.ldo + (size_t)h * a.out_hoff;
+            uint16_t* dst = a.out + (size_t)row_g * a.ldo + (size_t)h * a.out_hoff + half * 64;
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < 2; ++c) {
                 uint32_t o[32];
                 tmem_ld32(t_o + c * 32, o);
                 tmem_ld_wait();
