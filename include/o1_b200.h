@@ -428,6 +428,20 @@ int o1_sigmas_default(int steps, float shift, float *sigmas /* [steps+1] */);
 /* src/model/scheduler.c:197-208; src/runtime/generate.c:1423-1438 */
 float o1_noise_scale(int n_sigmas, int step_index, float start, float end);
 void o1_noise_clamp_host(float *noise, size_t n, float clip_std);
+/* Same draws as o1_torch_rng_randn with the Box-Muller transform spread over host threads. */
+void o1_torch_rng_randn_mt(void *rng, float *out_host, int64_t n, int threads);
+/* Per-step noise of the flash scheduler (src/runtime/generate.c:1296, :1419-1439) as a pipeline.  The
+ * reference draws n normals on the host, computes mean / unbiased std in fp64, clamps at clip_std * std
+ * and copies to the device, all inside the step.  Here a host thread draws step i+1 into pinned memory
+ * while the device runs step i; o1_noise_pipe_next enqueues the copy of the current step's draw and the
+ * statistics + clamp kernels on `stream` (NULL = current stream) and returns without synchronising.
+ * The draws are bit-identical to the reference's; mean and std are fp64 sums in a different (fixed) order,
+ * so the clip value can differ from the host's only if that changes the fp32 rounding of std.
+ * create allocates 2 x n floats of pinned memory and 8 KB on the device; clip_std <= 0 disables the clamp. */
+typedef struct o1_noise_pipe o1_noise_pipe;
+int o1_noise_pipe_create(o1_noise_pipe **out, uint64_t seed, size_t n, float clip_std, int host_threads);
+hd_status o1_noise_pipe_next(o1_noise_pipe *pipe, float *noise_dev, void *stream);
+void o1_noise_pipe_free(o1_noise_pipe *pipe);
 /* src/runtime/decode.c:5-27 fused with the NaN / range scan of src/runtime/generate.c:1474-1496, on the device */
 hd_status o1_decode_to_rgb(const void *z_dev, int grid_h, int grid_w, int patch, int channels, void *rgb_dev,
                            void *stats_dev /* 12 bytes */, int *n_bad, float *vmin, float *vmax);

@@ -168,6 +168,10 @@ _sig("o1_sigmas_flash", c_int, c_int, c_float, _P)
 _sig("o1_sigmas_default", c_int, c_int, c_float, _P)
 _sig("o1_noise_scale", c_float, c_int, c_int, c_float, c_float)
 _sig("o1_noise_clamp_host", None, _P, c_size_t, c_float)
+_sig("o1_torch_rng_randn_mt", None, _P, _P, c_int64, c_int)
+_sig("o1_noise_pipe_create", c_int, C.POINTER(_P), c_uint64, c_size_t, c_float, c_int)
+_sig("o1_noise_pipe_next", c_int, _P, _P, _P)
+_sig("o1_noise_pipe_free", None, _P)
 _sig("o1_decode_to_rgb", c_int, _P, c_int, c_int, c_int, c_int, _P, _P, C.POINTER(c_int), C.POINTER(c_float),
      C.POINTER(c_float))
 _sig("hd_weights_to_device_gguf", c_int, C.c_char_p, c_int, C.POINTER(WeightStore))

@@ -6,12 +6,20 @@
 //  * sigma schedules (src/model/scheduler.c:26-64, 117-195), noise scale ramp (:197-208) and the
 //    per-step noise clamp of the flash path (generate.c:1423-1438)
 //  * decode (src/runtime/decode.c:5-27) fused with the NaN / range gate (generate.c:1474-1496)
+//  * the per-step noise of the flash scheduler as a pipeline: a host thread draws step i+1 into
+//    pinned memory while the device runs step i; mean / unbiased std / clamp run on the device
+//    (generate.c:1419-1439 does all of it on the host, serially, inside the step)
 #include "common.cuh"
 #include "../../include/o1_b200.h"
 
 #include <math.h>
 #include <stdlib.h>
 #include <string.h>
+
+#include <condition_variable>
+#include <mutex>
+#include <thread>
+#include <vector>
 
 namespace {
 
@@ -46,6 +54,28 @@ inline uint32_t mt_u32(Mt* r) {
     return y;
 }
 inline float mt_uniform(Mt* r) { return (float)((mt_u32(r) & 0xFFFFFFu) * (1.0f / 16777216.0f)); }
+// n uniforms at once: same draws as n calls of mt_uniform, tempered straight out of the state
+// array in loops the compiler can vectorise.  left + next == 625 holds after every scalar draw
+// (624 + 1 after a refill), so left - 1 entries are ready at state[next].
+void mt_uniform_fill(Mt* r, float* out, int64_t n) {
+    while (n > 0) {
+        if (r->left <= 1) { mt_refill(r); r->left = 625; }
+        const int64_t k = n < (int64_t)(r->left - 1) ? n : (int64_t)(r->left - 1);
+        const uint32_t* src = r->state + r->next;
+        for (int64_t i = 0; i < k; ++i) {
+            uint32_t y = src[i];
+            y ^= y >> 11;
+            y ^= (y << 7) & 0x9d2c5680u;
+            y ^= (y << 15) & 0xefc60000u;
+            y ^= y >> 18;
+            out[i] = (float)((y & 0xFFFFFFu) * (1.0f / 16777216.0f));
+        }
+        r->next += (int)k;
+        r->left -= (int)k;
+        out += k;
+        n -= k;
+    }
+}
 void box_muller_16(float* d) {
     for (int j = 0; j < 8; ++j) {
         const float u1 = 1.0f - d[j], u2 = d[j + 8];
@@ -55,13 +85,27 @@ void box_muller_16(float* d) {
         d[j + 8] = rad * sinf(th);
     }
 }
-void mt_randn(Mt* r, float* out, int64_t n) {
+// The uniform draws are one sequential stream; the Box-Muller transform of the groups of 16 is
+// independent per group and is spread over `threads` host threads.
+void mt_randn(Mt* r, float* out, int64_t n, int threads = 1) {
     if (n >= 16) {
-        for (int64_t i = 0; i < n; ++i) out[i] = mt_uniform(r);
-        for (int64_t i = 0; i < n - 15; i += 16) box_muller_16(out + i);
+        mt_uniform_fill(r, out, n);
+        const int64_t groups = (n - 15 + 15) / 16;     // groups starting at 0, 16, ... < n - 15
+        if (threads > 1 && groups >= 4096) {
+            std::vector<std::thread> pool;
+            const int64_t per = (groups + threads - 1) / threads;
+            for (int t = 0; t < threads; ++t) {
+                const int64_t g0 = t * per, g1 = g0 + per < groups ? g0 + per : groups;
+                if (g0 >= g1) break;
+                pool.emplace_back([=] { for (int64_t g = g0; g < g1; ++g) box_muller_16(out + g * 16); });
+            }
+            for (auto& th : pool) th.join();
+        } else {
+            for (int64_t i = 0; i < n - 15; i += 16) box_muller_16(out + i);
+        }
         if (n % 16 != 0) {
             float* d = out + (n - 16);
-            for (int j = 0; j < 16; ++j) d[j] = mt_uniform(r);
+            mt_uniform_fill(r, d, 16);
             box_muller_16(d);
         }
         return;
@@ -113,6 +157,83 @@ __global__ void decode_rgb_kernel(const uint16_t* __restrict__ z, int grid_h, in
     if (mn <= mx) { atomicMin(&stats[1], key(mn)); atomicMax(&stats[2], key(mx)); }
 }
 
+// ---- noise statistics on the device: deterministic fp64 sums (fixed grid, partials added in block order)
+constexpr int STAT_BLOCKS = 1024, STAT_THREADS = 256;
+// partial[b] = sum over this block's elements of (x - *shift)^pw, pw = 1 or 2; shift may be null (0)
+template <int PW>
+__global__ void noise_partial_kernel(const float* __restrict__ x, size_t n, const double* __restrict__ shift,
+                                     double* __restrict__ partial) {
+    __shared__ double sh[STAT_THREADS];
+    const double m = shift ? *shift : 0.0;
+    double acc = 0.0;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const double d = (double)x[i] - m;
+        acc += PW == 1 ? d : d * d;
+    }
+    sh[threadIdx.x] = acc;
+    __syncthreads();
+    for (int s = STAT_THREADS / 2; s > 0; s >>= 1) {
+        if ((int)threadIdx.x < s) sh[threadIdx.x] += sh[threadIdx.x + s];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) partial[blockIdx.x] = sh[0];
+}
+// stage 0: res[0] = mean.  stage 1: res[1] = clip = clip_std * (float)sqrt(ss / (n - 1))
+__global__ void noise_final_kernel(const double* __restrict__ partial, size_t n, float clip_std, int stage,
+                                   double* __restrict__ res) {
+    double s = 0.0;
+    for (int b = 0; b < STAT_BLOCKS; ++b) s += partial[b];
+    if (stage == 0) res[0] = s / (double)n;
+    else res[1] = (double)(clip_std * (float)sqrt(s / (double)(n - 1)));
+}
+__global__ void noise_clamp_kernel(float* __restrict__ x, size_t n, const double* __restrict__ res) {
+    const float clip = (float)res[1];
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const float v = x[i];
+        x[i] = v > clip ? clip : (v < -clip ? -clip : v);
+    }
+}
+
+struct NoisePipe {
+    Mt rng;
+    size_t n = 0;
+    float clip_std = 0.f;
+    int threads = 1;
+    float* pinned[2] = {nullptr, nullptr};
+    cudaEvent_t copied[2] = {nullptr, nullptr};   // H2D of the buffer has finished: the worker may overwrite it
+    bool copy_pending[2] = {false, false};
+    double* dev_scratch = nullptr;                // STAT_BLOCKS partials + 2 results
+    std::thread worker;
+    std::mutex mu;
+    std::condition_variable cv;
+    int produced = 0;       // steps fully drawn by the worker
+    int requested = 1;      // steps the worker may draw (one ahead of the consumer)
+    int consumed = 0;
+    bool stop = false;
+    int device = 0;
+};
+
+void noise_worker(NoisePipe* p) {
+    cudaSetDevice(p->device);
+    for (;;) {
+        int step;
+        {
+            std::unique_lock<std::mutex> lk(p->mu);
+            p->cv.wait(lk, [&] { return p->stop || p->produced < p->requested; });
+            if (p->stop) return;
+            step = p->produced;
+        }
+        const int b = step & 1;
+        if (p->copy_pending[b]) { cudaEventSynchronize(p->copied[b]); p->copy_pending[b] = false; }
+        mt_randn(&p->rng, p->pinned[b], (int64_t)p->n, p->threads);
+        {
+            std::lock_guard<std::mutex> lk(p->mu);
+            p->produced = step + 1;
+        }
+        p->cv.notify_all();
+    }
+}
+
 }  // namespace
 
 extern "C" {
@@ -124,6 +245,9 @@ void* o1_torch_rng_create(uint64_t seed) {
     return r;
 }
 void o1_torch_rng_randn(void* rng, float* out_host, int64_t n) { if (rng && out_host && n > 0) mt_randn((Mt*)rng, out_host, n); }
+void o1_torch_rng_randn_mt(void* rng, float* out_host, int64_t n, int threads) {
+    if (rng && out_host && n > 0) mt_randn((Mt*)rng, out_host, n, threads < 1 ? 1 : threads);
+}
 uint32_t o1_torch_rng_u32(void* rng) { return rng ? mt_u32((Mt*)rng) : 0; }
 void o1_torch_rng_free(void* rng) { free(rng); }
 
@@ -198,6 +322,93 @@ void o1_noise_clamp_host(float* noise, size_t n, float clip_std) {
     for (size_t i = 0; i < n; ++i) { const double d = (double)noise[i] - m; ss += d * d; }
     const float clip = clip_std * (float)sqrt(ss / (double)(n - 1));
     for (size_t i = 0; i < n; ++i) noise[i] = noise[i] > clip ? clip : (noise[i] < -clip ? -clip : noise[i]);
+}
+
+// ------------------------------------------------------------------ per-step noise pipeline (flash scheduler)
+// Stream of draws: the generator is seeded once (the reference seeds it with request seed + 1,
+// generate.c:1296) and every step takes the next n normals from it, so step i of the pipe equals the
+// i-th hd_torch_randn_f32(&step_rng, ., n) of the reference loop.
+int o1_noise_pipe_create(o1_noise_pipe** out, uint64_t seed, size_t n, float clip_std, int host_threads) {
+    if (!out || n < 2) { hd_set_error("noise pipe: bad arguments"); return -1; }
+    NoisePipe* p = new NoisePipe();
+    mt_seed(&p->rng, seed);
+    p->n = n;
+    p->clip_std = clip_std;
+    p->threads = host_threads < 1 ? 1 : host_threads;
+    cudaGetDevice(&p->device);
+    cudaError_t e = cudaSuccess;
+    for (int b = 0; b < 2 && e == cudaSuccess; ++b) {
+        e = cudaHostAlloc((void**)&p->pinned[b], n * sizeof(float), cudaHostAllocDefault);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&p->copied[b], cudaEventDisableTiming);
+    }
+    if (e == cudaSuccess) e = cudaMalloc((void**)&p->dev_scratch, (STAT_BLOCKS + 2) * sizeof(double));
+    if (e != cudaSuccess) {
+        hd_set_error("noise pipe: %s", cudaGetErrorString(e));
+        for (int b = 0; b < 2; ++b) { if (p->pinned[b]) cudaFreeHost(p->pinned[b]); if (p->copied[b]) cudaEventDestroy(p->copied[b]); }
+        if (p->dev_scratch) cudaFree(p->dev_scratch);
+        delete p;
+        return -1;
+    }
+    p->worker = std::thread(noise_worker, p);   // starts on step 0 at once
+    *out = reinterpret_cast<o1_noise_pipe*>(p);
+    return 0;
+}
+
+hd_status o1_noise_pipe_next(o1_noise_pipe* pipe, float* noise_dev, void* stream) {
+    NoisePipe* p = reinterpret_cast<NoisePipe*>(pipe);
+    if (!p || !noise_dev) { hd_set_error("noise pipe: bad arguments"); return HD_ERR_MISSING; }
+    cudaStream_t st = stream ? (cudaStream_t)stream : o1::current_stream();
+    int step;
+    {
+        std::unique_lock<std::mutex> lk(p->mu);
+        step = p->consumed;
+        p->cv.wait(lk, [&] { return p->produced > step; });
+    }
+    const int b = step & 1;
+    cudaError_t e = cudaMemcpyAsync(noise_dev, p->pinned[b], p->n * sizeof(float), cudaMemcpyHostToDevice, st);
+    if (e == cudaSuccess) e = cudaEventRecord(p->copied[b], st);
+    if (e != cudaSuccess) { hd_set_error("noise pipe: %s", cudaGetErrorString(e)); return HD_ERR_RUNTIME; }
+    {
+        // the worker touches copy_pending[b] again only after `requested` lets it reach step + 2
+        std::lock_guard<std::mutex> lk(p->mu);
+        p->copy_pending[b] = true;
+        p->consumed = step + 1;
+        p->requested = step + 2;     // draw the next step while the device works on this one
+    }
+    p->cv.notify_all();
+    if (p->clip_std > 0.0f) {
+        double* part = p->dev_scratch;
+        double* res = p->dev_scratch + STAT_BLOCKS;
+        noise_partial_kernel<1><<<STAT_BLOCKS, STAT_THREADS, 0, st>>>(noise_dev, p->n, nullptr, part);
+        noise_final_kernel<<<1, 1, 0, st>>>(part, p->n, p->clip_std, 0, res);
+        noise_partial_kernel<2><<<STAT_BLOCKS, STAT_THREADS, 0, st>>>(noise_dev, p->n, res, part);
+        noise_final_kernel<<<1, 1, 0, st>>>(part, p->n, p->clip_std, 1, res);
+        long blocks = (long)((p->n + 255) / 256);
+        if (blocks > (long)o1::sm_count() * 16) blocks = (long)o1::sm_count() * 16;
+        noise_clamp_kernel<<<(unsigned)blocks, 256, 0, st>>>(noise_dev, p->n, res);
+        o1_launch_count_add(5);
+        e = cudaGetLastError();
+        if (e != cudaSuccess) { hd_set_error("noise pipe: %s", cudaGetErrorString(e)); return HD_ERR_RUNTIME; }
+    }
+    return HD_OK;
+}
+
+void o1_noise_pipe_free(o1_noise_pipe* pipe) {
+    NoisePipe* p = reinterpret_cast<NoisePipe*>(pipe);
+    if (!p) return;
+    {
+        std::lock_guard<std::mutex> lk(p->mu);
+        p->stop = true;
+    }
+    p->cv.notify_all();
+    if (p->worker.joinable()) p->worker.join();
+    for (int b = 0; b < 2; ++b) {
+        if (p->copy_pending[b]) cudaEventSynchronize(p->copied[b]);
+        cudaFreeHost(p->pinned[b]);
+        cudaEventDestroy(p->copied[b]);
+    }
+    cudaFree(p->dev_scratch);
+    delete p;
 }
 
 // ------------------------------------------------------------------ decode + gate (device)

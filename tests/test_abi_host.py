@@ -204,3 +204,30 @@ def test_gguf_header_parse_without_gpu(pkg, tmp_path):
     trunc = tmp_path / "trunc.gguf"
     trunc.write_bytes(raw[:60])
     assert pkg.lib.o1_gguf_probe(str(trunc).encode(), -1, None, 0, None, None, None) == -1
+
+
+def test_bulk_and_threaded_rng_equals_the_scalar_stream(pkg):
+    """The block-wise uniform fill and the threaded Box-Muller give the same stream as draw-by-draw
+    generation (the oracle's generator, which is pinned to the reference's torch_rng.c), across state
+    refills and when scalar draws are mixed in between."""
+    import numpy as np
+    import parity
+    lib, orc = pkg.lib, parity.oracle()
+    h, o = lib.o1_torch_rng_create(987654321), orc.orc_rng_create(987654321)
+    try:
+        for n, threads in ((100003, 4), (5, 1), (70000, 3), (16, 2), (623, 1), (1 << 18, 8)):
+            a = np.empty(n, dtype=np.float32)
+            b = np.empty(n, dtype=np.float32)
+            lib.o1_torch_rng_randn_mt(h, a.ctypes.data_as(C.c_void_p), n, threads)
+            orc.orc_rng_randn(o, parity.np_ptr(b), n)
+            assert (a.view(np.uint32) == b.view(np.uint32)).all(), (n, threads)
+            lib.o1_torch_rng_u32(h)                      # one scalar draw in between keeps the states aligned
+            tmp = np.empty(1, dtype=np.float32)
+            # the oracle has no raw-u32 entry on a stateful generator: a 1-element randn uses 4 draws, so
+            # advance the library's generator by the 3 remaining ones
+            orc.orc_rng_randn(o, parity.np_ptr(tmp), 1)
+            for _ in range(3):
+                lib.o1_torch_rng_u32(h)
+    finally:
+        lib.o1_torch_rng_free(h)
+        orc.orc_rng_free(o)
