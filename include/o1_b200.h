@@ -477,6 +477,32 @@ hd_status o1_sp_forward_begin(const hd_forward_binding *bw, const o1_sp_ws *w, c
 hd_status o1_sp_forward_end(const hd_forward_binding *bw, const o1_sp_ws *w, const void *hidden,
                             void *norm_scratch, void *out_local);
 
+/* Direct form of the two exchanges: no collective call and no staging copy.  Each rank maps its peers' gath
+ * [S][C] and recv [P][rows][Hc] buffers and a small flag array (CUDA IPC: o1_peer_*; in a C host
+ * cudaIpcGetMemHandle / cudaIpcOpenMemHandle directly).  o1_sp_block_pre_direct's q/k/v GEMM epilogues store head
+ * group p straight into rank p's gath; o1_sp_block_attn_direct applies the per-head norm + rope on the received
+ * rows and its attention epilogue stores row block p straight into rank p's recv; o1_sp_block_post is unchanged.
+ * Results are bit-identical to the staged form.  Call order per block on every rank:
+ *   pre_direct, barrier(e), attn_direct, barrier(e+1), post      (e grows by 2 per block, never reused)
+ * The barrier is a kernel on the current stream that release-stores the epoch into every peer's flag array and
+ * polls its own; its wait is bounded (device error code 30 after about two seconds).  Ranks must be on different
+ * GPUs (two ranks' barrier kernels on one GPU would wait for each other without being co-scheduled). */
+typedef struct {
+    void *gath[8];      /* rank p's gath buffer as mapped in this process ([sp_rank] = the local one)   */
+    void *recv[8];      /* rank p's recv buffer                                                         */
+    void *flags[8];     /* rank p's flag array: 8 x uint32, zero-initialised                            */
+    void *rope_full;    /* local: cos|sin table of all S rows, fp32 [S,128]                             */
+} o1_sp_peers;
+int o1_peer_alloc(void **dev_ptr, size_t bytes);                 /* cudaMalloc + zero fill */
+int o1_peer_free(void *dev_ptr);
+int o1_peer_export(const void *dev_ptr, unsigned char handle[64]);
+int o1_peer_open(const unsigned char handle[64], void **peer_ptr);
+int o1_peer_close(void *peer_ptr);
+hd_status o1_sp_rope_table_full(const o1_sp_ws *w, const o1_sp_peers *pt, const float *pos_global);
+hd_status o1_sp_block_pre_direct(const hd_block_binding *bw, const o1_sp_ws *w, const o1_sp_peers *pt, const void *in);
+hd_status o1_sp_block_attn_direct(const hd_block_binding *bw, const o1_sp_ws *w, const o1_sp_peers *pt);
+hd_status o1_sp_barrier(const o1_sp_ws *w, const o1_sp_peers *pt, unsigned epoch);
+
 #ifdef __cplusplus
 }
 #endif

@@ -50,6 +50,10 @@ struct AttnArgs {
     int q_hc, q_hr, kv_hc, kv_hr;
     long out_hoff;      // element offset of head h in the output: h * out_hoff
     int* err;
+    // out_rows > 0: output rows [b*out_rows, (b+1)*out_rows) are written to out_tab[b] (possibly another
+    // GPU's memory) instead of out
+    int out_rows;
+    uint16_t* out_tab[8];
 };
 
 __device__ __forceinline__ float ex2_approx(float x) {
@@ -343,6 +347,10 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         if (ok) {
             const float inv_l = 1.0f / l;
             uint16_t* dst = a.out + (size_t)row_g * a.ldo + (size_t)h * a.out_hoff + half * 64;
+            if (a.out_rows > 0 && row_g < a.S) {
+                const int blk = row_g / a.out_rows;
+                dst = a.out_tab[blk] + (size_t)(row_g - blk * a.out_rows) * a.ldo + (size_t)h * a.out_hoff + half * 64;
+            }
 #pragma unroll 1
             for (int c = 0; c < 2; ++c) {
                 uint32_t o[32];
@@ -373,7 +381,13 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 static bool flash_attention_impl(const void* q, int ldq, const void* k, int ldk, const void* v,
                                  int ldv, void* out, int ldo, int S, int heads, int kv_heads,
                                  int ar_len, float scale, bool in_head_major, bool out_head_major,
-                                 cudaStream_t st) {
+                                 cudaStream_t st, void* const* out_tab = nullptr, int out_rows = 0) {
+    if (out_tab) {
+        if (out_rows <= 0 || (S + out_rows - 1) / out_rows > 8 || out_head_major) { set_error("attention: bad output table"); return false; }
+        for (int i = 0; i < (S + out_rows - 1) / out_rows; ++i)
+            if (!out_tab[i] || (((uintptr_t)out_tab[i]) & 15)) { set_error("attention: output table entry %d unusable", i); return false; }
+        out = out_tab[0];
+    }
     if (!q || !k || !v || !out || S <= 0 || heads <= 0 || kv_heads <= 0 || (heads % kv_heads) != 0) {
         set_error("attention: bad args");
         return false;
@@ -408,6 +422,9 @@ static bool flash_attention_impl(const void* q, int ldq, const void* k, int ldk,
     a.out_hoff = out_head_major ? (long)S * AD : AD;
     if (out_head_major) a.ldo = AD;
     a.err = device_error_word();
+    a.out_rows = out_tab ? out_rows : 0;
+    for (int i = 0; i < 8; ++i) a.out_tab[i] = nullptr;
+    if (out_tab) for (int i = 0; i < (S + out_rows - 1) / out_rows; ++i) a.out_tab[i] = (uint16_t*)out_tab[i];
     dim3 grid((S + AQ2 - 1) / AQ2, heads);
     {
         // QK^T + PV over the keys each row can see: 4*heads*128*(ar(ar+1)/2 + (S-ar)*S)
@@ -426,6 +443,12 @@ bool flash_attention(const void* q, int ldq, const void* k, int ldk, const void*
                      cudaStream_t st) {
     return flash_attention_impl(q, ldq, k, ldk, v, ldv, out, ldo, S, heads, kv_heads, ar_len, scale,
                                 false, false, st);
+}
+bool flash_attention_tab(const void* q, int ldq, const void* k, int ldk, const void* v, int ldv,
+                         void* const* out_tab, int out_rows, int ldo, int S, int heads, int kv_heads,
+                         int ar_len, float scale, cudaStream_t st) {
+    return flash_attention_impl(q, ldq, k, ldk, v, ldv, nullptr, ldo, S, heads, kv_heads, ar_len, scale,
+                                false, false, st, out_tab, out_rows);
 }
 // q [heads,S,128], k/v [kv_heads,S,128]; out head-major [heads,S,128] or seq-major [S, heads*128]
 bool flash_attention_hm(const void* q, const void* k, const void* v, void* out, int S, int heads,

@@ -42,6 +42,10 @@ struct GemmArgs {
     // slabs of an all-to-all send buffer.  o_cb must be a multiple of the tile width.
     int o_cb;
     long o_cb_stride;
+    // With o_tab_n > 0 block b starts at o_tab[b] instead of out + b * o_cb_stride: the blocks may then
+    // live in other GPUs' memory (peer-mapped), which turns the epilogue's stores into the transfer.
+    int o_tab_n;
+    uint16_t* o_tab[8];
     // Input K blocks: K columns [b*a_kblk, (b+1)*a_kblk) of row r live at x[(b*a_rows + r) * ldx + ...]
     // (a_kblk == 0: plain).  Lets a projection read the slabs an all-to-all received, one per source.
     int a_kblk, a_rows;
@@ -268,7 +272,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
                             for (int j = 0; j < 32; ++j) v[j] = b[j] + g.scale * v[j];
                         }
-                        store32_bf16(g.out + (size_t)row * g.ldo + ocol, v);
+                        uint16_t* obase = g.o_tab_n ? g.o_tab[col / g.o_cb] + (col % g.o_cb) : g.out + ocol;
+                        store32_bf16(obase + (size_t)row * g.ldo, v);
                     }
                 }
             }
@@ -424,8 +429,12 @@ bool gemm_bf16_ld(const void* x, int ldx, const void* w, const void* w2, void* y
 
 bool gemm_bf16_ex(const void* x, int ldx, const void* w, const void* w2, void* y, int ldy, int M, int N,
                   int K, int epi, const void* bias, const void* resid, int ldr, float scale, int force_bn,
-                  int o_cb, long o_cb_stride, int a_kblk, int a_rows, cudaStream_t st) {
-    if (!x || !w || !y || M <= 0 || N <= 0 || K <= 0) { set_error("gemm: bad args"); return false; }
+                  int o_cb, long o_cb_stride, int a_kblk, int a_rows, cudaStream_t st, void* const* o_tab) {
+    if (!x || !w || (!y && !o_tab) || M <= 0 || N <= 0 || K <= 0) { set_error("gemm: bad args"); return false; }
+    if (o_tab && (!o_cb || N / o_cb > 8 || epi != EPI_STORE)) {
+        set_error("gemm: an output table needs column blocks (at most 8) and the plain epilogue");
+        return false;
+    }
     if ((o_cb || a_kblk) && !gemm_tc_supported(M, N, K, epi)) {
         set_error("gemm: blocked operand layouts need a tensor-core shape");
         return false;
@@ -464,6 +473,15 @@ bool gemm_bf16_ex(const void* x, int ldx, const void* w, const void* w2, void* y
         g.group_m = (int)(gm < 4 ? 4 : (gm > 32 ? 32 : gm));
     }
     g.o_cb = o_cb; g.o_cb_stride = o_cb_stride;
+    g.o_tab_n = 0;
+    for (int i = 0; i < 8; ++i) g.o_tab[i] = nullptr;
+    if (o_tab) {
+        g.o_tab_n = N / o_cb;
+        for (int i = 0; i < g.o_tab_n; ++i) {
+            if (!o_tab[i] || (((uintptr_t)o_tab[i]) & 15)) { set_error("gemm: output table entry %d unusable", i); return false; }
+            g.o_tab[i] = (uint16_t*)o_tab[i];
+        }
+    }
     g.a_kblk = a_kblk; g.a_rows = a_rows;
 
     const CUtensorMap* tA = a_kblk ? cached_tmap(x, (uint64_t)(K / a_kblk) * a_rows, a_kblk, ldx, 128)

@@ -30,7 +30,7 @@ bool gemm_bf16_ld(const void* x, int ldx, const void* w, const void* w2, void* y
 //  a_kblk / a_rows   : input column k of row r is read from x[((k / a_kblk) * a_rows + r) * ldx + k % a_kblk]
 bool gemm_bf16_ex(const void* x, int ldx, const void* w, const void* w2, void* y, int ldy, int M, int N,
                   int K, int epi, const void* bias, const void* resid, int ldr, float scale, int force_bn,
-                  int o_cb, long o_cb_stride, int a_kblk, int a_rows, cudaStream_t st);
+                  int o_cb, long o_cb_stride, int a_kblk, int a_rows, cudaStream_t st, void* const* o_tab = nullptr);
 bool gemm_tc_supported(int M, int N, int K, int epi);
 const CUtensorMap* cached_tmap(const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
                                uint32_t box_rows);
@@ -44,6 +44,11 @@ bool flash_attention(const void* q, int ldq, const void* k, int ldk, const void*
 
 bool flash_attention_hm(const void* q, const void* k, const void* v, void* out, int S, int heads,
                         int kv_heads, int ar_len, float scale, bool out_head_major, cudaStream_t st);
+// seq-major operands; output rows [b*out_rows, (b+1)*out_rows) go to out_tab[b] (row-major, leading
+// dimension ldo), which may be peer-mapped memory of another GPU
+bool flash_attention_tab(const void* q, int ldq, const void* k, int ldk, const void* v, int ldv,
+                         void* const* out_tab, int out_rows, int ldo, int S, int heads, int kv_heads,
+                         int ar_len, float scale, cudaStream_t st);
 
 // ---- elementwise.cu
 bool rmsnorm(const void* x, const void* w, void* y, int rows, int cols, float eps, cudaStream_t st);

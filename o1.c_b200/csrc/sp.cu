@@ -9,11 +9,20 @@
 // writes its output as [S, Hc] whose row blocks are the second exchange's send slabs, and o_proj reads
 // the received slabs as K blocks of its A operand.  The exchanges themselves are the caller's
 // (NCCL all-to-all with equal splits, or peer copies).
+//
+// Direct form (o1_sp_*_direct): the exchange is part of the producing kernel.  Every rank maps its
+// peers' gath / recv buffers (CUDA IPC); the q/k/v GEMM epilogues store each destination's head group
+// straight into that rank's gath rows, and attention stores each destination's row block straight into
+// that rank's recv slab, so the NVLink transfer runs under the tensor-core work and no collective kernel
+// or staging copy exists.  Per-head norm + rope then run on the receiving side (same arithmetic on the
+// same values, so results are bit-identical to the staged form).  A flag barrier over peer memory
+// (o1_sp_barrier) orders producers and consumers; its wait is bounded.
 #include "common.cuh"
 #include "kernels.h"
 #include "../../include/o1_b200.h"
 
 #include <math.h>
+#include <string.h>
 
 using namespace o1;
 
@@ -32,7 +41,116 @@ static bool sp_ok(const o1_sp_ws* w) {
            ((w->heads / w->sp_size) * 128) % 128 == 0;
 }
 
+// One thread per peer: release-store this rank's epoch into the peer's flag array, then poll this rank's
+// own array for the peer's epoch.  Epochs only grow, so a late reader never misses one.  The wait is
+// bounded (about two seconds of SM clock); on expiry the device error word gets code 30.
+__global__ void sp_barrier_kernel(o1_sp_peers pt, int P, int rank, unsigned epoch, int* err) {
+    const int p = threadIdx.x;
+    if (p >= P || p == rank) return;
+    unsigned* remote = (unsigned*)pt.flags[p] + rank;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
+    const unsigned* mine = (const unsigned*)pt.flags[rank] + p;
+    const long long t0 = clock64();
+    for (;;) {
+        unsigned v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+        if ((int)(v - epoch) >= 0) break;
+        if (clock64() - t0 > 4000000000ll) { atomicExch(err, 30); break; }
+    }
+}
+
+static bool peers_ok(const o1_sp_ws* w, const o1_sp_peers* pt) {
+    if (!pt) return false;
+    for (int p = 0; p < w->sp_size; ++p)
+        if (!pt->gath[p] || !pt->recv[p] || !pt->flags[p]) return false;
+    return pt->rope_full != nullptr;
+}
+
 extern "C" {
+
+// ------------------------------------------------------------------ peer-visible memory (CUDA IPC)
+int o1_peer_alloc(void** dev_ptr, size_t bytes) {
+    if (!dev_ptr || !bytes) return -1;
+    cudaError_t e = cudaMalloc(dev_ptr, bytes);
+    if (e == cudaSuccess) e = cudaMemset(*dev_ptr, 0, bytes);
+    if (e != cudaSuccess) { hd_set_error("peer alloc: %s", cudaGetErrorString(e)); return -1; }
+    return 0;
+}
+int o1_peer_free(void* dev_ptr) { return cudaFree(dev_ptr) == cudaSuccess ? 0 : -1; }
+int o1_peer_export(const void* dev_ptr, unsigned char handle[64]) {
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    cudaIpcMemHandle_t h;
+    cudaError_t e = cudaIpcGetMemHandle(&h, const_cast<void*>(dev_ptr));
+    if (e != cudaSuccess) { hd_set_error("peer export: %s", cudaGetErrorString(e)); return -1; }
+    memcpy(handle, &h, 64);
+    return 0;
+}
+int o1_peer_open(const unsigned char handle[64], void** peer_ptr) {
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, 64);
+    cudaError_t e = cudaIpcOpenMemHandle(peer_ptr, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) { hd_set_error("peer open: %s", cudaGetErrorString(e)); return -1; }
+    return 0;
+}
+int o1_peer_close(void* peer_ptr) { return cudaIpcCloseMemHandle(peer_ptr) == cudaSuccess ? 0 : -1; }
+
+hd_status o1_sp_barrier(const o1_sp_ws* w, const o1_sp_peers* pt, unsigned epoch) {
+    if (!sp_ok(w) || !peers_ok(w, pt)) { hd_set_error("sp: bad peer table"); return HD_ERR_MISSING; }
+    if (w->sp_size == 1) return HD_OK;
+    sp_barrier_kernel<<<1, 32, 0, current_stream()>>>(*pt, w->sp_size, w->sp_rank, epoch, device_error_word());
+    o1_launch_count_add(1);
+    if (cudaGetLastError() != cudaSuccess) { hd_set_error("sp: barrier launch failed"); return HD_ERR_RUNTIME; }
+    return HD_OK;
+}
+
+// cos|sin table of ALL S rows (the direct form applies rope on the receiving side)
+hd_status o1_sp_rope_table_full(const o1_sp_ws* w, const o1_sp_peers* pt, const float* pos_global) {
+    if (!sp_ok(w) || !pt || !pt->rope_full || !pos_global) { hd_set_error("sp: bad workspace"); return HD_ERR_MISSING; }
+    SP_TRY(mrope_table64_rows(pos_global, w->S, 0, w->S, 5000000.0f, (float*)pt->rope_full, current_stream()),
+           "rope table");
+    return HD_OK;
+}
+
+// in [rows, hidden] -> every rank's gath rows [rank*rows, (rank+1)*rows): RMSNorm, then q/k/v projections whose
+// epilogues store head group p of the output into rank p's gath (raw values: norm + rope follow after the barrier)
+hd_status o1_sp_block_pre_direct(const hd_block_binding* bw, const o1_sp_ws* w, const o1_sp_peers* pt, const void* in) {
+    if (!sp_ok(w) || !peers_ok(w, pt) || !bw || !in) { hd_set_error("sp: bad arguments"); return HD_ERR_MISSING; }
+    cudaStream_t st = current_stream();
+    const int P = w->sp_size, R = w->rows, H = w->hidden;
+    const int qc = w->heads * 128, kc = w->kv_heads * 128;
+    const int qcp = qc / P, kcp = kc / P, C = qcp + 2 * kcp;
+    void* tq[8]; void* tk[8]; void* tv[8];
+    for (int p = 0; p < P; ++p) {
+        uint16_t* base = (uint16_t*)pt->gath[p] + (size_t)w->sp_rank * R * C;
+        tq[p] = base; tk[p] = base + qcp; tv[p] = base + qcp + kcp;
+    }
+    SP_TRY(rmsnorm(in, bw->input_ln, w->ln, R, H, 1e-6f, st), "input_norm");
+    SP_TRY(gemm_bf16_ex(w->ln, H, bw->q_proj, nullptr, nullptr, C, R, qc, H, EPI_STORE, nullptr, nullptr, 0, 0.f, 0,
+                        qcp, 0, 0, 0, st, tq), "q_proj");
+    SP_TRY(gemm_bf16_ex(w->ln, H, bw->k_proj, nullptr, nullptr, C, R, kc, H, EPI_STORE, nullptr, nullptr, 0, 0.f, 0,
+                        kcp, 0, 0, 0, st, tk), "k_proj");
+    SP_TRY(gemm_bf16_ex(w->ln, H, bw->v_proj, nullptr, nullptr, C, R, kc, H, EPI_STORE, nullptr, nullptr, 0, 0.f, 0,
+                        kcp, 0, 0, 0, st, tv), "v_proj");
+    return HD_OK;
+}
+
+// own gath [S][C] (all rows, this rank's heads; complete after the barrier) -> per-head norm + rope in place ->
+// attention whose epilogue stores row block p into rank p's recv slab [rank]
+hd_status o1_sp_block_attn_direct(const hd_block_binding* bw, const o1_sp_ws* w, const o1_sp_peers* pt) {
+    if (!sp_ok(w) || !peers_ok(w, pt) || !bw) { hd_set_error("sp: bad arguments"); return HD_ERR_MISSING; }
+    cudaStream_t st = current_stream();
+    const int P = w->sp_size, R = w->rows;
+    const int qcp = w->heads * 128 / P, kcp = w->kv_heads * 128 / P, C = qcp + 2 * kcp;
+    uint16_t* g = (uint16_t*)pt->gath[w->sp_rank];
+    const float* rope = (const float*)pt->rope_full;
+    SP_TRY(qk_norm_rope(g, C, w->S, w->heads / P, bw->q_norm, rope, 1e-6f, st), "q_norm_rope");
+    SP_TRY(qk_norm_rope(g + qcp, C, w->S, w->kv_heads / P, bw->k_norm, rope, 1e-6f, st), "k_norm_rope");
+    void* to[8];
+    for (int p = 0; p < P; ++p) to[p] = (uint16_t*)pt->recv[p] + (size_t)w->sp_rank * R * qcp;
+    SP_TRY(flash_attention_tab(g, C, g + qcp, C, g + qcp + kcp, C, to, R, qcp, w->S, w->heads / P, w->kv_heads / P,
+                               w->ar_len, (float)(1.0 / sqrt(128.0)), st), "attention");
+    return HD_OK;
+}
 
 hd_status o1_sp_rope_table(const o1_sp_ws* w, const float* pos_global) {
     if (!sp_ok(w) || !pos_global || !w->rope) { hd_set_error("sp: bad workspace"); return HD_ERR_MISSING; }

@@ -22,7 +22,25 @@ class SpWs(C.Structure):
                [(n, c_void_p) for n in ("send", "gath", "attn", "recv", "ln", "ar", "post", "swi", "rope")]
 
 
+class SpPeers(C.Structure):
+    """o1_sp_peers (include/o1_b200.h): every SP rank's gath / recv / flag buffers as mapped here."""
+    _fields_ = [("gath", c_void_p * 8), ("recv", c_void_p * 8), ("flags", c_void_p * 8), ("rope_full", c_void_p)]
+
+
+for _name, _res, _args in (("o1_peer_alloc", c_int, (C.POINTER(c_void_p), C.c_size_t)),
+                           ("o1_peer_free", c_int, (c_void_p,)),
+                           ("o1_peer_export", c_int, (c_void_p, C.POINTER(C.c_ubyte))),
+                           ("o1_peer_open", c_int, (C.POINTER(C.c_ubyte), C.POINTER(c_void_p))),
+                           ("o1_peer_close", c_int, (c_void_p,))):
+    _f = getattr(lib, _name)
+    _f.restype, _f.argtypes = _res, list(_args)
+
 for _name, _args in (("o1_sp_rope_table", (C.POINTER(SpWs), c_void_p)),
+                     ("o1_sp_rope_table_full", (C.POINTER(SpWs), C.POINTER(SpPeers), c_void_p)),
+                     ("o1_sp_block_pre_direct", (C.POINTER(BlockBinding), C.POINTER(SpWs), C.POINTER(SpPeers),
+                                                 c_void_p)),
+                     ("o1_sp_block_attn_direct", (C.POINTER(BlockBinding), C.POINTER(SpWs), C.POINTER(SpPeers))),
+                     ("o1_sp_barrier", (C.POINTER(SpWs), C.POINTER(SpPeers), C.c_uint)),
                      ("o1_sp_block_pre", (C.POINTER(BlockBinding), C.POINTER(SpWs), c_void_p)),
                      ("o1_sp_block_attn", (C.POINTER(SpWs),)),
                      ("o1_sp_block_post", (C.POINTER(BlockBinding), C.POINTER(SpWs), c_void_p, c_void_p)),
@@ -57,12 +75,19 @@ def shard_rows(S, T, P, r):
 
 
 class EngineSP:
-    """One SP rank of one forward.  `exchange(src, dst)` performs the equal-split all-to-all of the
-    contiguous tensor `src` into `dst` (same shape): torch.distributed.all_to_all_single in a real
-    job, a peer-copy emulation in single-process tests."""
+    """One SP rank of one forward.
 
-    def __init__(self, weights, text_len, img_tokens, sp_size, sp_rank, exchange, ar_len=None):
+    Staged form: `exchange(src, dst)` performs the equal-split all-to-all of the contiguous tensor `src`
+    into `dst` (same shape): torch.distributed.all_to_all_single in a real job, a peer-copy emulation in
+    single-process tests.
+
+    Direct form (`direct=True`, exchange unused): gath / recv / flags live in one peer-visible region
+    (`self.region`); after `connect()` has been given every rank's region base, the q/k/v GEMM and
+    attention epilogues store straight into the peers' buffers and `barrier()` orders the ranks."""
+
+    def __init__(self, weights, text_len, img_tokens, sp_size, sp_rank, exchange=None, ar_len=None, direct=False):
         self.w, self.P, self.r, self.exchange = weights, sp_size, sp_rank, exchange
+        self.direct, self.peers, self.region, self.epoch, self._opened = direct, None, None, 0, []
         d = weights.dims
         self.T, self.I, self.S = text_len, img_tokens, text_len + img_tokens
         (self.row0, _), (self.t0, self.t1), (self.i0, self.i1) = shard_rows(self.S, self.T, sp_size, sp_rank)
@@ -75,10 +100,26 @@ class EngineSP:
         dev = weights.device
         bf = dict(dtype=torch.bfloat16, device=dev)
         R, S = self.rows, self.S
-        self.send = torch.empty(sp_size, R, self.C, **bf)
-        self.gath = self.send.view(S, self.C) if sp_size == 1 else torch.empty(S, self.C, **bf)
-        self.attn = torch.empty(S, self.Hc, **bf)
-        self.recv = self.attn.view(sp_size, R, self.Hc) if sp_size == 1 else torch.empty(sp_size, R, self.Hc, **bf)
+        if direct:
+            # one cudaMalloc'd region (exportable through CUDA IPC): gath | recv | flags
+            self.gath_bytes = S * self.C * 2
+            self.recv_bytes = S * self.Hc * 2
+            self.region_bytes = self.gath_bytes + self.recv_bytes + 256
+            reg = c_void_p()
+            if lib.o1_peer_alloc(C.byref(reg), self.region_bytes) != 0:
+                raise RuntimeError("peer region allocation failed")
+            self.region = reg.value
+            self.rope_full = torch.empty(S, 128, dtype=torch.float32, device=dev)
+            gath_ptr, recv_ptr = self.region, self.region + self.gath_bytes
+            send_ptr = attn_ptr = 0
+        else:
+            self.send = torch.empty(sp_size, R, self.C, **bf)
+            self.gath = self.send.view(S, self.C) if sp_size == 1 else torch.empty(S, self.C, **bf)
+            self.attn = torch.empty(S, self.Hc, **bf)
+            self.recv = (self.attn.view(sp_size, R, self.Hc) if sp_size == 1
+                         else torch.empty(sp_size, R, self.Hc, **bf))
+            gath_ptr, recv_ptr = self.gath.data_ptr(), self.recv.data_ptr()
+            send_ptr, attn_ptr = self.send.data_ptr(), self.attn.data_ptr()
         self.ln, self.ar, self.post = (torch.empty(R, H, **bf) for _ in range(3))
         self.swi = torch.empty(R, ff, **bf)
         self.hid = [torch.empty(R, H, **bf) for _ in range(2)]
@@ -89,15 +130,40 @@ class EngineSP:
         self.ws = SpWs(sp_size=sp_size, sp_rank=sp_rank, S=S, T=self.T, row0=self.row0, rows=R, heads=d["heads"],
                        kv_heads=d["kv_heads"], hidden=H, ff=ff, head_dim=hd,
                        ar_len=(text_len - 1 if ar_len is None else ar_len),
-                       send=self.send.data_ptr(), gath=self.gath.data_ptr(), attn=self.attn.data_ptr(),
-                       recv=self.recv.data_ptr(), ln=self.ln.data_ptr(), ar=self.ar.data_ptr(),
+                       send=send_ptr, gath=gath_ptr, attn=attn_ptr,
+                       recv=recv_ptr, ln=self.ln.data_ptr(), ar=self.ar.data_ptr(),
                        post=self.post.data_ptr(), swi=self.swi.data_ptr(), rope=self.rope.data_ptr())
+
+    def connect(self, region_bases, opened=()):
+        """region_bases[p]: base of SP rank p's region as mapped in this process (own region for p == r)."""
+        pt = SpPeers()
+        for p, base in enumerate(region_bases):
+            pt.gath[p] = base
+            pt.recv[p] = base + self.gath_bytes
+            pt.flags[p] = base + self.gath_bytes + self.recv_bytes
+        pt.rope_full = self.rope_full.data_ptr()
+        self.peers, self._opened = pt, list(opened)
+
+    def barrier(self):
+        self.epoch += 1
+        check(lib.o1_sp_barrier(C.byref(self.ws), C.byref(self.peers), self.epoch), "sp_barrier")
+
+    def close(self):
+        for q in self._opened:
+            lib.o1_peer_close(q)
+        self._opened = []
+        if self.region:
+            lib.o1_peer_free(self.region)
+            self.region = None
 
     # the forward is split into generator-style stages so that a single process can interleave several
     # emulated ranks; `forward()` runs them back to back for a real rank
     def stages(self, ids, pos, vin_local, t, out_local):
         ws, w = C.byref(self.ws), self.w
         self.timestep.fill_(float(t))
+        if self.direct:
+            yield from self._stages_direct(ids, pos, vin_local, out_local)
+            return
         check(lib.o1_sp_rope_table(ws, ptr(pos)), "sp_rope_table")
         check(lib.o1_sp_forward_begin(C.byref(w.binding), ws, ptr(ids), ptr(vin_local), ptr(self.timestep),
                                       ptr(self.small), ptr(self.xe_stage), TMS_ID, ptr(self.hid[0])), "sp_begin")
@@ -112,12 +178,32 @@ class EngineSP:
             cur, nxt = nxt, cur
         check(lib.o1_sp_forward_end(C.byref(w.binding), ws, ptr(cur), ptr(self.ln), ptr(out_local)), "sp_end")
 
+    def _stages_direct(self, ids, pos, vin_local, out_local):
+        ws, w, pt = C.byref(self.ws), self.w, C.byref(self.peers)
+        check(lib.o1_sp_rope_table_full(ws, pt, ptr(pos)), "sp_rope_table_full")
+        check(lib.o1_sp_forward_begin(C.byref(w.binding), ws, ptr(ids), ptr(vin_local), ptr(self.timestep),
+                                      ptr(self.small), ptr(self.xe_stage), TMS_ID, ptr(self.hid[0])), "sp_begin")
+        cur, nxt = self.hid
+        for l in range(w.n_layers):
+            bb = C.byref(w.block_binding(l))
+            check(lib.o1_sp_block_pre_direct(bb, ws, pt, ptr(cur)), "sp_block_pre_direct")
+            yield ("barrier", None, None)
+            check(lib.o1_sp_block_attn_direct(bb, ws, pt), "sp_block_attn_direct")
+            yield ("barrier", None, None)
+            check(lib.o1_sp_block_post(bb, ws, ptr(cur), ptr(nxt)), "sp_block_post")
+            cur, nxt = nxt, cur
+        check(lib.o1_sp_forward_end(C.byref(w.binding), ws, ptr(cur), ptr(self.ln), ptr(out_local)), "sp_end")
+
     def forward(self, ids, pos, vin_local, t, out_local=None):
         """x_pred rows of this rank, [rows, 3072] bf16."""
         if out_local is None:
             out_local = torch.empty(self.rows, PATCH_DIM, dtype=torch.bfloat16, device=self.w.device)
-        for _, src, dst in self.stages(ids, pos, vin_local, t, out_local):
-            if self.P > 1:
+        for kind, src, dst in self.stages(ids, pos, vin_local, t, out_local):
+            if self.P == 1:
+                continue
+            if kind == "barrier":
+                self.barrier()
+            else:
                 self.exchange(src, dst)
         return out_local
 
@@ -129,6 +215,30 @@ def nccl_exchange(group):
     def ex(src, dst):
         dist.all_to_all_single(dst.view(-1), src.view(-1), group=group)
     return ex
+
+
+def connect_direct(engine, group):
+    """Exchange CUDA IPC handles of the peer regions inside the SP process group (ranks in sp_rank order)
+    and map them; every rank of the group must call this."""
+    import torch.distributed as dist
+    h = (C.c_ubyte * 64)()
+    if lib.o1_peer_export(engine.region, h) != 0:
+        raise RuntimeError("peer export failed")
+    handles = [None] * engine.P
+    dist.all_gather_object(handles, bytes(h), group=group)
+    bases, opened = [], []
+    for p in range(engine.P):
+        if p == engine.r:
+            bases.append(engine.region)
+            continue
+        q = c_void_p()
+        if lib.o1_peer_open((C.c_ubyte * 64).from_buffer_copy(handles[p]), C.byref(q)) != 0:
+            raise RuntimeError(f"cannot map the region of SP rank {p}")
+        bases.append(q.value)
+        opened.append(q.value)
+    engine.connect(bases, opened)
+    torch.cuda.synchronize()
+    dist.barrier(group=group)      # every region is zeroed and mapped before the first store into it
 
 
 def run_emulated(engines, ids, pos, vin, t):
@@ -146,6 +256,8 @@ def run_emulated(engines, ids, pos, vin, t):
                 steps.append(None)
         if all(s is None for s in steps):
             break
+        if steps[0][0] == "barrier":      # direct form: the lock-step order of one stream is the barrier
+            continue
         for s in range(P):
             for d in range(P):
                 steps[d][2][s].copy_(steps[s][1][d])
