@@ -194,7 +194,12 @@ def run_ours(args):
     if sp_size > 1:
         del eng
         torch.cuda.empty_cache()
-        eng = spmod.EngineSP(w, T, I, sp_size, sp_rank, spmod.nccl_exchange(sp_group))
+        if args.exchange == "direct":
+            # exchanges done by the producing kernels' epilogues (peer stores) + flag barriers
+            eng = spmod.EngineSP(w, T, I, sp_size, sp_rank, direct=True)
+            spmod.connect_direct(eng, sp_group)
+        else:
+            eng = spmod.EngineSP(w, T, I, sp_size, sp_rank, spmod.nccl_exchange(sp_group))
         i0, i1, n_text_local = eng.i0, eng.i1, eng.t1 - eng.t0
         z, z_next = z[i0:i1].contiguous(), z_next[i0:i1].contiguous()
         z_host = z.cpu().pin_memory()
@@ -324,6 +329,9 @@ def run_ours(args):
                        "parallelism": "1 GPU" if world == 1 else
                                       (f"dp{images} (one image per GPU)" if is_lora else f"cfg pair x ulysses sp{sp_size}"
                                        + (f" x dp{images}" if images > 1 else "")),
+                       "sp_exchange": (None if sp_size == 1 else
+                                       ("peer stores from the GEMM / attention epilogues + flag barriers"
+                                        if args.exchange == "direct" else "NCCL all-to-all")),
                        "weights": "random-init N(0,0.02) bf16, seed 1234",
                        "l2": "no flush needed: every step streams 2 x %.1f GB of weights (L2 is 126 MB)"
                              % (w.nbytes() / 1e9)},
@@ -533,6 +541,9 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--layers", type=int, default=36)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--exchange", choices=("direct", "nccl"), default="direct",
+                    help="Ulysses exchanges at 4 / 8 GPUs: stores into the peers' buffers from the producing "
+                         "kernels (default) or NCCL all-to-all between the stage kernels")
     ap.add_argument("--short", action="store_true",
                     help="profiler runs only: take --warmup literally, skip the end-to-end and CPU legs "
                          "(a number from such a run is not a benchmark value)")

@@ -344,13 +344,45 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         *x_mine = l;
         asm volatile("bar.sync %0, 256;" ::"r"(bar_id) : "memory");
         l += *x_other;
-        if (ok) {
+        if (ok && a.out_rows > 0) {
+            // Row blocks of the output live in other GPUs' memory: leave as full 128-byte row segments (4 rows
+            // per store instruction) instead of 16-byte pieces of 32 rows.  The staging slice is this warp's
+            // 4 KB of the Q tiles, which no MMA reads any more once o_done has completed.
+            const float inv_l = 1.0f / l;
+            uint8_t* stg = q_s + (warp - 2) * (32 * 128);
+#pragma unroll 1
+            for (int c = 0; c < 2; ++c) {
+                uint32_t o[32];
+                tmem_ld32(t_o + c * 32, o);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    uint4 pk;
+                    pk.x = cvt_bf16x2(__uint_as_float(o[i * 8 + 0]) * inv_l, __uint_as_float(o[i * 8 + 1]) * inv_l);
+                    pk.y = cvt_bf16x2(__uint_as_float(o[i * 8 + 2]) * inv_l, __uint_as_float(o[i * 8 + 3]) * inv_l);
+                    pk.z = cvt_bf16x2(__uint_as_float(o[i * 8 + 4]) * inv_l, __uint_as_float(o[i * 8 + 5]) * inv_l);
+                    pk.w = cvt_bf16x2(__uint_as_float(o[i * 8 + 6]) * inv_l, __uint_as_float(o[i * 8 + 7]) * inv_l);
+                    const int j = c * 4 + i;
+                    *reinterpret_cast<uint4*>(stg + lane * 128 + ((j ^ (lane & 7)) * 16)) = pk;
+                }
+            }
+            __syncwarp();
+            const int ch = lane & 7;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const int rr = k * 4 + (lane >> 3);
+                const uint4 v = *reinterpret_cast<const uint4*>(stg + rr * 128 + ((ch ^ (rr & 7)) * 16));
+                const int rg = qg0 + qd * 32 + rr;
+                if (rg < a.S) {
+                    const int blk = rg / a.out_rows;
+                    uint16_t* dst = a.out_tab[blk] + (size_t)(rg - blk * a.out_rows) * a.ldo + (size_t)h * a.out_hoff +
+                                    half * 64 + ch * 8;
+                    *reinterpret_cast<uint4*>(dst) = v;
+                }
+            }
+        } else if (ok) {
             const float inv_l = 1.0f / l;
             uint16_t* dst = a.out + (size_t)row_g * a.ldo + (size_t)h * a.out_hoff + half * 64;
-            if (a.out_rows > 0 && row_g < a.S) {
-                const int blk = row_g / a.out_rows;
-                dst = a.out_tab[blk] + (size_t)(row_g - blk * a.out_rows) * a.ldo + (size_t)h * a.out_hoff + half * 64;
-            }
 #pragma unroll 1
             for (int c = 0; c < 2; ++c) {
                 uint32_t o[32];

@@ -58,7 +58,8 @@ struct GemmCfg {
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int STAGES = (BN == 256) ? 4 : 6;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+    static constexpr int STORE_STAGE_BYTES = 4 * 32 * 128;   // per epilogue warp 32 rows x 128 B (peer stores)
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/ + STORE_STAGE_BYTES;
     static constexpr int TMEM_COLS = 2 * BN;
 };
 
@@ -111,6 +112,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     uint64_t* tfull = empty + STAGES;
     uint64_t* tempty = tfull + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+    uint8_t* store_stage = smem + STAGES * Cfg::STAGE_BYTES + 256;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -243,6 +245,41 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         store32_bf16(g.out + (size_t)row * g.ldo + nb * 128 + c * 32, v);
                     }
                 }
+            } else if (EPI == EPI_STORE && g.o_tab_n) {
+                // Blocks of the output live in other GPUs' memory.  One thread per row would put 16-byte
+                // pieces of 32 different rows into every store instruction; over NVLink each piece is a
+                // packet of its own.  So 64 columns at a time go through a swizzled shared-memory slice of
+                // this warp and leave as full 128-byte row segments (4 rows per instruction).
+                uint8_t* stg = store_stage + q * (32 * 128);
+#pragma unroll 1
+                for (int c2 = 0; c2 < BN / 64; ++c2) {
+                    uint32_t r0[32], r1[32];
+                    tmem_ld32(t_row + c2 * 64, r0);
+                    tmem_ld32(t_row + c2 * 64 + 32, r1);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const uint32_t* src = j < 4 ? &r0[(j & 3) * 8] : &r1[(j & 3) * 8];
+                        uint4 o;
+                        o.x = pack_bf16x2(__uint_as_float(src[0]), __uint_as_float(src[1]));
+                        o.y = pack_bf16x2(__uint_as_float(src[2]), __uint_as_float(src[3]));
+                        o.z = pack_bf16x2(__uint_as_float(src[4]), __uint_as_float(src[5]));
+                        o.w = pack_bf16x2(__uint_as_float(src[6]), __uint_as_float(src[7]));
+                        *reinterpret_cast<uint4*>(stg + lane * 128 + ((j ^ (lane & 7)) * 16)) = o;
+                    }
+                    __syncwarp();
+                    const int col = nb * BN + c2 * 64;      // a 64-column group never straddles a block (o_cb % 128 == 0)
+                    uint16_t* obase = g.o_tab[col / g.o_cb] + (col % g.o_cb);
+                    const int ch = lane & 7;
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) {
+                        const int rr = k * 4 + (lane >> 3);
+                        const uint4 o = *reinterpret_cast<const uint4*>(stg + rr * 128 + ((ch ^ (rr & 7)) * 16));
+                        const int grow = mb * BM + q * 32 + rr;
+                        if (grow < g.M) *reinterpret_cast<uint4*>(obase + (size_t)grow * g.ldo + ch * 8) = o;
+                    }
+                    __syncwarp();
+                }
             } else {
 #pragma unroll 1
                 for (int c = 0; c < BN / 32; ++c) {
@@ -272,8 +309,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
                             for (int j = 0; j < 32; ++j) v[j] = b[j] + g.scale * v[j];
                         }
-                        uint16_t* obase = g.o_tab_n ? g.o_tab[col / g.o_cb] + (col % g.o_cb) : g.out + ocol;
-                        store32_bf16(obase + (size_t)row * g.ldo, v);
+                        store32_bf16(g.out + (size_t)row * g.ldo + ocol, v);
                     }
                 }
             }

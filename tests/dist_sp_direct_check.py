@@ -1,0 +1,102 @@
+"""Multi-process check of the direct (peer-store) Ulysses exchange on real GPUs, one rank per GPU:
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node P --master-addr 127.0.0.1 \
+        --master-port 29531 tests/dist_sp_direct_check.py [--S 2048 --layers 2 --time]
+
+Every rank runs the same sharded forward twice, once with NCCL all-to-all exchanges and once with the
+direct form; rank 0 also runs the unsharded forward.  Prints one JSON line; exit code 0 only if the direct
+form equals the staged form bit for bit and the sharded forward matches the unsharded one."""
+import argparse
+import json
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from __graft_entry__ import load_package  # noqa: E402
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--text", type=int, default=64)
+    ap.add_argument("--grid", type=int, default=32)          # image tokens = grid * grid
+    ap.add_argument("--layers", type=int, default=2)
+    ap.add_argument("--time", action="store_true")
+    args = ap.parse_args()
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    pkg = load_package()
+    from o1c_b200 import sp
+    pkg.use_torch_stream()
+    T, I = args.text, args.grid * args.grid
+    S = T + I
+    assert S % world == 0, "choose --text / --grid so that the sequence divides by the ranks"
+    w = pkg.Weights(n_layers=args.layers, seed=1234, weight_set="B", device=dev)
+    pos, _ = pkg.seq_t2i(T, args.grid, args.grid)
+    rng = np.random.default_rng(1)
+    ids = rng.integers(0, 151000, size=T).astype(np.int64)
+    ids[-1] = pkg.TMS_ID
+    idsd, posd = torch.from_numpy(ids).to(dev), pos.to(dev)
+    g = torch.Generator(device="cpu").manual_seed(5)
+    vin = torch.randn(I, 3072, generator=g).to(torch.bfloat16).to(dev)
+
+    def run(engine):
+        mine = vin[engine.i0:engine.i1] if engine.i1 > engine.i0 else None
+        out = engine.forward(idsd, posd, mine, 0.5)
+        full = torch.empty(world, engine.rows, 3072, dtype=torch.bfloat16, device=dev)
+        dist.all_gather_into_tensor(full.view(-1), out.view(-1))
+        return full.view(S, 3072)
+
+    def timed(engine, reps=5):
+        mine = vin[engine.i0:engine.i1] if engine.i1 > engine.i0 else None
+        for _ in range(2):
+            engine.forward(idsd, posd, mine, 0.5)
+        dist.barrier(); torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            engine.forward(idsd, posd, mine, 0.5)
+        e1.record(); torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / reps], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    staged_eng = sp.EngineSP(w, T, I, world, rank, sp.nccl_exchange(dist.group.WORLD))
+    staged = run(staged_eng)
+    ms_staged = timed(staged_eng) if args.time else None
+    del staged_eng
+    direct_eng = sp.EngineSP(w, T, I, world, rank, direct=True)
+    sp.connect_direct(direct_eng, dist.group.WORLD)
+    direct = run(direct_eng)
+    direct2 = run(direct_eng)
+    ms_direct = timed(direct_eng) if args.time else None
+    torch.cuda.synchronize()
+    err = pkg.lib.o1_device_error()
+    same = bool(torch.equal(direct.view(torch.int16), staged.view(torch.int16)) and
+                torch.equal(direct2.view(torch.int16), staged.view(torch.int16)))
+    ok = torch.tensor([int(same and err == 0)], device=dev)
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    rel = None
+    if rank == 0:
+        ref = pkg.Engine(w, T, I).forward(idsd, posd, vin, 0.5).float()
+        rel = float((direct.float() - ref).norm() / ref.norm())
+    dist.barrier()
+    direct_eng.close()
+    if rank == 0:
+        good = bool(ok.item()) and rel < 5e-3
+        print(json.dumps({"world": world, "S": S, "layers": args.layers, "direct_equals_staged": bool(ok.item()),
+                          "rel_l2_vs_unsharded": rel, "device_error": err, "ms_forward_staged": ms_staged,
+                          "ms_forward_direct": ms_direct, "ok": good}))
+        dist.destroy_process_group()
+        sys.exit(0 if good else 1)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -73,3 +73,25 @@ def test_sp_direct_form_is_bit_identical_to_staged_form(pkg, dev, P):
             e.close()
     assert torch.equal(direct.view(torch.int16), staged.view(torch.int16))
     assert torch.equal(again.view(torch.int16), staged.view(torch.int16))
+
+
+def test_sp_direct_form_on_real_gpus(pkg):
+    """The same comparison with one process per GPU (CUDA IPC mappings, peer stores over NVLink, the flag
+    barrier): needs at least two GPUs."""
+    import json
+    import os
+    import subprocess
+    import sys
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs two GPUs")
+    world = 4 if n >= 4 else 2
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", "29531",
+           os.path.join(root, "tests", "dist_sp_direct_check.py"), "--text", "64", "--grid", "32", "--layers", "2"]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=root)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+    line = [l for l in res.stdout.splitlines() if l.startswith("{")][-1]
+    rep = json.loads(line)
+    assert rep["ok"] and rep["direct_equals_staged"] and rep["device_error"] == 0
