@@ -354,6 +354,15 @@ int o1_gemm(const void *x, int ldx, const void *w, const void *w2, void *y, int 
  * v [S, ldv], out [S, ldo]; head h at columns [128h, 128h+128). */
 int o1_flash_attention(const void *q, int ldq, const void *k, int ldk, const void *v, int ldv,
                        void *out, int ldo, int S, int heads, int kv_heads, int ar_len, float scale);
+/* Same with device scratch (16-byte aligned) for key-split tail items: when the number of (256 query rows,
+ * head) items is not a multiple of the SM count, the items of the last, partly filled wave are cut along the
+ * keys into several CTAs whose fp32 partial results (133,120 bytes each) a merge kernel combines.  The forward
+ * and the SP stages pass the idle SwiGLU buffer.  Too little scratch only reduces or disables the split. */
+int o1_flash_attention_ws(const void *q, int ldq, const void *k, int ldk, const void *v, int ldv, void *out,
+                          int ldo, int S, int heads, int kv_heads, int ar_len, float scale, void *scratch,
+                          size_t scratch_bytes);
+/* Policy of that split: 0 = automatic (default), 1 = never, n > 1 = n parts whenever scratch and key count allow. */
+void o1_attention_tail_ways(int ways);
 /* cos|sin table [S,128] fp32 for section [24,20,20], theta 5e6 (built once per forward). */
 int o1_mrope_table(const float *pos_dev, int seq, float theta, float *cs_dev);
 /* Per-head RMSNorm + rotary, in place on [S, ld] holding `heads` heads. */

@@ -194,6 +194,9 @@ _sig("o1_gemm", c_int, _P, c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int,
      c_float, c_int)
 _sig("o1_flash_attention", c_int, _P, c_int, _P, c_int, _P, c_int, _P, c_int, c_int, c_int, c_int,
      c_int, c_float)
+_sig("o1_attention_tail_ways", None, c_int)
+_sig("o1_flash_attention_ws", c_int, _P, c_int, _P, c_int, _P, c_int, _P, c_int, c_int, c_int, c_int,
+     c_int, c_float, _P, c_size_t)
 _sig("o1_mrope_table", c_int, _P, c_int, c_float, _P)
 _sig("o1_qk_norm_rope", c_int, _P, c_int, c_int, c_int, _P, _P, c_float)
 _sig("o1_sched_cfg_flow_step", c_int, _P, _P, _P, c_float, c_float, c_float, _P, c_size_t)

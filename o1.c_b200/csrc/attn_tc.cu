@@ -54,6 +54,13 @@ struct AttnArgs {
     // GPU's memory) instead of out
     int out_rows;
     uint16_t* out_tab[8];
+    // Work items: item = head * nqb + query block.  The first n_plain items are one CTA each.  Each of the
+    // remaining (tail) items is cut along the keys into `ways` CTAs that leave unnormalised partial results
+    // (accumulator, running max, row sum) in part_o / part_ml for attn_merge_kernel, so that the last,
+    // partly filled wave of CTAs is short.  ways == 1: no tail.
+    int nqb, n_plain, ways;
+    float* part_o;      // [slot][256 rows][128] fp32, slot = (item - n_plain) * ways + part
+    float* part_ml;     // [slot][256 rows][2]: max (exp2 domain) the partial is relative to, row sum
 };
 
 __device__ __forceinline__ float ex2_approx(float x) {
@@ -91,15 +98,24 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int q0 = blockIdx.x * AQ2;
-    const int h = blockIdx.y;
+    int item = blockIdx.x, part = 0, ways = 1;
+    if (item >= a.n_plain) {
+        const int t = item - a.n_plain;
+        item = a.n_plain + t / a.ways;
+        part = t - (t / a.ways) * a.ways;
+        ways = a.ways;
+    }
+    const int h = item / a.nqb;
+    const int q0 = (item - h * a.nqb) * AQ2;
     const int kh = h / (a.heads / a.kv_heads);
 
     // keys this pair of query tiles can see (the second tile's range covers the first's)
     int kv_end = a.S;
     if (q0 + AQ2 - 1 < a.ar_len) kv_end = q0 + AQ2;   // all rows causal: keys <= last row
     if (kv_end > a.S) kv_end = a.S;
-    const int n_tiles = (kv_end + AKV - 1) / AKV;
+    const int tiles_all = (kv_end + AKV - 1) / AKV;
+    const int j0 = (int)((long)part * tiles_all / ways);                  // first key tile of this CTA
+    const int n_tiles = (int)((long)(part + 1) * tiles_all / ways) - j0;  // and how many it covers
 
     // a kernel that already failed on this device leaves its code in *err: do nothing then
     if (threadIdx.x == 0) {
@@ -146,18 +162,18 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 const int st = j % K_STAGES;
                 if (!mbar_wait(&k_empty[st], ((j / K_STAGES) & 1) ^ 1)) { atomicExch(a.err, 11); return false; }
                 mbar_expect_tx(&k_full[st], TILE_BYTES);
-                tma_load_2d(k_s + st * TILE_BYTES, &tmK, &k_full[st], kh * a.kv_hc, kh * a.kv_hr + j * AKV);
+                tma_load_2d(k_s + st * TILE_BYTES, &tmK, &k_full[st], kh * a.kv_hc, kh * a.kv_hr + (j0 + j) * AKV);
                 tma_load_2d(k_s + st * TILE_BYTES + PANEL_BYTES, &tmK, &k_full[st], kh * a.kv_hc + 64,
-                            kh * a.kv_hr + j * AKV);
+                            kh * a.kv_hr + (j0 + j) * AKV);
                 return true;
             };
             auto load_v = [&](int j) -> bool {
                 const int st = j % V_STAGES;
                 if (!mbar_wait(&v_empty[st], ((j / V_STAGES) & 1) ^ 1)) { atomicExch(a.err, 12); return false; }
                 mbar_expect_tx(&v_full[st], TILE_BYTES);
-                tma_load_2d(v_s + st * TILE_BYTES, &tmV, &v_full[st], kh * a.kv_hc, kh * a.kv_hr + j * AKV);
+                tma_load_2d(v_s + st * TILE_BYTES, &tmV, &v_full[st], kh * a.kv_hc, kh * a.kv_hr + (j0 + j) * AKV);
                 tma_load_2d(v_s + st * TILE_BYTES + PANEL_BYTES, &tmV, &v_full[st], kh * a.kv_hc + 64,
-                            kh * a.kv_hr + j * AKV);
+                            kh * a.kv_hr + (j0 + j) * AKV);
                 return true;
             };
             // load order follows the consumer: K0, then per tile V(j), K(j+1)
@@ -246,7 +262,7 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         float l = 0.f;                           // this thread's share of the row sum
         bool ok = true;
         for (int j = 0; j < n_tiles && ok; ++j) {
-            const int kv0 = j * AKV + half * 64;
+            const int kv0 = (j0 + j) * AKV + half * 64;
             if (!mbar_wait(&s_full[grp], j & 1)) { atomicExch(a.err, 17); ok = false; break; }
             tc_fence_after();
             const bool need_mask = (kv0 + 64 > a.S) || (tile_has_causal && kv0 + 63 > qg0);
@@ -344,7 +360,25 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         *x_mine = l;
         asm volatile("bar.sync %0, 256;" ::"r"(bar_id) : "memory");
         l += *x_other;
-        if (ok && a.out_rows > 0) {
+        if (ok && ways > 1) {
+            // partial result of a key range: accumulator as it is (relative to m_used), max and row sum
+            const int slot = (item - a.n_plain) * ways + part;
+            const int prow = grp * AQ + row;
+            float* po = a.part_o + ((size_t)slot * AQ2 + prow) * AD + half * 64;
+            if (half == 0) {
+                float2 ml = make_float2(m_used, l);
+                *reinterpret_cast<float2*>(a.part_ml + ((size_t)slot * AQ2 + prow) * 2) = ml;
+            }
+#pragma unroll 1
+            for (int c = 0; c < 2; ++c) {
+                uint32_t o[32];
+                tmem_ld32(t_o + c * 32, o);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    *reinterpret_cast<uint4*>(po + c * 32 + i * 4) = make_uint4(o[i * 4], o[i * 4 + 1], o[i * 4 + 2], o[i * 4 + 3]);
+            }
+        } else if (ok && a.out_rows > 0) {
             // Row blocks of the output live in other GPUs' memory: leave as full 128-byte row segments (4 rows
             // per store instruction) instead of 16-byte pieces of 32 rows.  The staging slice is this warp's
             // 4 KB of the Q tiles, which no MMA reads any more once o_done has completed.
@@ -410,10 +444,70 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     if (warp == 1) tmem_dealloc(tmem_base, 512);
 }
 
+// Combines the partial results of the tail items: out = sum_i O_i 2^(m_i - M) / sum_i l_i 2^(m_i - M).
+// One block per query row, one thread per output column.
+__global__ void __launch_bounds__(AD) attn_merge_kernel(const AttnArgs a, int n_tail) {
+    const int ti = blockIdx.x / AQ2, r = blockIdx.x - ti * AQ2;
+    if (ti >= n_tail) return;
+    const int item = a.n_plain + ti;
+    const int h = item / a.nqb;
+    const int row_g = (item - h * a.nqb) * AQ2 + r;
+    if (row_g >= a.S) return;
+    const int col = threadIdx.x;
+    float M = -INFINITY;
+    for (int i = 0; i < a.ways; ++i) M = fmaxf(M, a.part_ml[((size_t)(ti * a.ways + i) * AQ2 + r) * 2]);
+    float num = 0.f, den = 0.f;
+    for (int i = 0; i < a.ways; ++i) {
+        const size_t pr = (size_t)(ti * a.ways + i) * AQ2 + r;
+        const float m = a.part_ml[pr * 2];
+        if (m == -INFINITY) continue;           // this key range held no visible key for the row
+        const float wgt = exp2f(m - M);
+        num = fmaf(a.part_o[pr * AD + col], wgt, num);
+        den = fmaf(a.part_ml[pr * 2 + 1], wgt, den);
+    }
+    const float v = num * (1.0f / den);
+    uint16_t* dst = a.out + (size_t)row_g * a.ldo + (size_t)h * a.out_hoff;
+    if (a.out_rows > 0) {
+        const int blk = row_g / a.out_rows;
+        dst = a.out_tab[blk] + (size_t)(row_g - blk * a.out_rows) * a.ldo + (size_t)h * a.out_hoff;
+    }
+    dst[col] = f32_to_bf16(v);
+}
+
+// Number of key-range parts for the tail items: the last (total % SMs) items would otherwise occupy a wave
+// of CTAs alone.  Cost of the tail in item durations: rounds of CTAs it needs, ceil(rem * w / SMs), times the
+// duration of a part, 1/w plus a fixed share for its prologue, Q load and fp32 epilogue (about four key
+// tiles' worth).  After many full waves the SMs have drifted apart by a good fraction of an item's duration
+// and a small tail costs little, so the split must save more than that drift to be used.  Every part keeps
+// at least two key tiles.
+static int g_tail_ways = 0;   // 0: choose; 1: never split; n > 1: n parts whenever they fit
+void attention_tail_ways(int ways) { g_tail_ways = ways < 0 ? 0 : ways; }
+
+static int choose_tail_ways(int total, int nsm, int min_tiles, size_t scratch_bytes) {
+    const int rem = total % nsm;
+    if (rem == 0) return 1;
+    const size_t part_bytes = (size_t)AQ2 * AD * 4 + (size_t)AQ2 * 2 * 4;
+    if (g_tail_ways >= 1) {
+        const bool fits = g_tail_ways * 2 <= min_tiles && (size_t)rem * g_tail_ways * part_bytes <= scratch_bytes;
+        return fits ? g_tail_ways : 1;
+    }
+    const double fixed = 4.0 / min_tiles;
+    int best = 1;
+    double best_cost = 1.0;
+    for (int w = 2; w <= 32 && w * 2 <= min_tiles; ++w) {
+        if ((size_t)rem * w * part_bytes > scratch_bytes) break;
+        const double cost = (double)((rem * w + nsm - 1) / nsm) * (1.0 / w + fixed) + 0.02;
+        if (cost < best_cost - 1e-9) { best_cost = cost; best = w; }
+    }
+    const double drift = 0.1 * (total / nsm) + 0.05;
+    return (1.0 - best_cost) > drift ? best : 1;
+}
+
 static bool flash_attention_impl(const void* q, int ldq, const void* k, int ldk, const void* v,
                                  int ldv, void* out, int ldo, int S, int heads, int kv_heads,
                                  int ar_len, float scale, bool in_head_major, bool out_head_major,
-                                 cudaStream_t st, void* const* out_tab = nullptr, int out_rows = 0) {
+                                 cudaStream_t st, void* const* out_tab = nullptr, int out_rows = 0,
+                                 void* scratch = nullptr, size_t scratch_bytes = 0) {
     if (out_tab) {
         if (out_rows <= 0 || (S + out_rows - 1) / out_rows > 8 || out_head_major) { set_error("attention: bad output table"); return false; }
         for (int i = 0; i < (S + out_rows - 1) / out_rows; ++i)
@@ -457,13 +551,39 @@ static bool flash_attention_impl(const void* q, int ldq, const void* k, int ldk,
     a.out_rows = out_tab ? out_rows : 0;
     for (int i = 0; i < 8; ++i) a.out_tab[i] = nullptr;
     if (out_tab) for (int i = 0; i < (S + out_rows - 1) / out_rows; ++i) a.out_tab[i] = (uint16_t*)out_tab[i];
-    dim3 grid((S + AQ2 - 1) / AQ2, heads);
+    a.nqb = (S + AQ2 - 1) / AQ2;
+    const int total = a.nqb * heads;
+    a.n_plain = total; a.ways = 1; a.part_o = nullptr; a.part_ml = nullptr;
+    int n_tail = 0;
+    if (scratch && scratch_bytes && (((uintptr_t)scratch) & 15) == 0) {
+        const int nsm = sm_count();
+        const int rem = total % nsm;
+        // fewest key tiles among the tail items (all-causal query blocks stop at the diagonal)
+        int min_tiles = 1 << 30;
+        for (int it = total - rem; it < total; ++it) {
+            const int q0 = (it % a.nqb) * AQ2;
+            int kv_end = (q0 + AQ2 - 1 < ar_len) ? q0 + AQ2 : S;
+            if (kv_end > S) kv_end = S;
+            const int t = (kv_end + AKV - 1) / AKV;
+            if (t < min_tiles) min_tiles = t;
+        }
+        const int w = rem ? choose_tail_ways(total, nsm, min_tiles, scratch_bytes) : 1;
+        if (w > 1) {
+            n_tail = rem;
+            a.n_plain = total - rem;
+            a.ways = w;
+            a.part_o = (float*)scratch;
+            a.part_ml = a.part_o + (size_t)rem * w * AQ2 * AD;
+        }
+    }
+    dim3 grid(a.n_plain + n_tail * a.ways);
     {
         // QK^T + PV over the keys each row can see: 4*heads*128*(ar(ar+1)/2 + (S-ar)*S)
         const double keys = 0.5 * ar_len * (ar_len + 1.0) + (double)(S - ar_len) * S;
         prof_before(PROF_ATTN, 4.0 * heads * 128.0 * keys, st);
     }
     flash_attn_kernel<<<grid, ATTN_THREADS, ATTN_SMEM, st>>>(*tq, *tk, *tv, a);
+    if (n_tail) attn_merge_kernel<<<n_tail * AQ2, AD, 0, st>>>(a, n_tail);
     prof_after(st);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) { set_error("attention: launch: %s", cudaGetErrorString(e)); return false; }
@@ -472,15 +592,15 @@ static bool flash_attention_impl(const void* q, int ldq, const void* k, int ldk,
 
 bool flash_attention(const void* q, int ldq, const void* k, int ldk, const void* v, int ldv,
                      void* out, int ldo, int S, int heads, int kv_heads, int ar_len, float scale,
-                     cudaStream_t st) {
+                     cudaStream_t st, void* scratch, size_t scratch_bytes) {
     return flash_attention_impl(q, ldq, k, ldk, v, ldv, out, ldo, S, heads, kv_heads, ar_len, scale,
-                                false, false, st);
+                                false, false, st, nullptr, 0, scratch, scratch_bytes);
 }
 bool flash_attention_tab(const void* q, int ldq, const void* k, int ldk, const void* v, int ldv,
                          void* const* out_tab, int out_rows, int ldo, int S, int heads, int kv_heads,
-                         int ar_len, float scale, cudaStream_t st) {
+                         int ar_len, float scale, cudaStream_t st, void* scratch, size_t scratch_bytes) {
     return flash_attention_impl(q, ldq, k, ldk, v, ldv, nullptr, ldo, S, heads, kv_heads, ar_len, scale,
-                                false, false, st, out_tab, out_rows);
+                                false, false, st, out_tab, out_rows, scratch, scratch_bytes);
 }
 // q [heads,S,128], k/v [kv_heads,S,128]; out head-major [heads,S,128] or seq-major [S, heads*128]
 bool flash_attention_hm(const void* q, const void* k, const void* v, void* out, int S, int heads,

@@ -489,8 +489,9 @@ static hd_status block_forward(const void* in, const float* cs, int ar_len, cons
     BLK_TRY(qk_norm_rope(b.qkv, ld, S, heads, bw->q_norm, cs, eps, st), "q_norm_rope");
     BLK_TRY(qk_norm_rope(b.qkv + qc, ld, S, kv_heads, bw->k_norm, cs, eps, st), "k_norm_rope");
     // 7. attention, output already seq-major [S, heads*hd]
+    // (the SwiGLU buffer is idle until step 11: it holds the partial results of key-split tail items)
     BLK_TRY(flash_attention(b.qkv, ld, b.qkv + qc, ld, b.qkv + qc + kc, ld, b.attn, qc, S, heads,
-                            kv_heads, ar_len, scaling, st), "attention");
+                            kv_heads, ar_len, scaling, st, b.swi, (size_t)S * ff * 2), "attention");
     // 8-9. o_proj (+ residual)
     if (ints && ints->attn_hidden) {
         BLK_TRY(gemm_bf16(b.attn, bw->o_proj, nullptr, b.tmp, S, hidden, qc, EPI_STORE, nullptr,
@@ -785,6 +786,16 @@ int o1_flash_attention(const void* q, int ldq, const void* k, int ldk, const voi
     count();
     return 0;
 }
+int o1_flash_attention_ws(const void* q, int ldq, const void* k, int ldk, const void* v, int ldv, void* out,
+                          int ldo, int S, int heads, int kv_heads, int ar_len, float scale, void* scratch,
+                          size_t scratch_bytes) {
+    if (!flash_attention(q, ldq, k, ldk, v, ldv, out, ldo, S, heads, kv_heads, ar_len, scale, g_stream, scratch,
+                         scratch_bytes))
+        return 1;
+    count();
+    return 0;
+}
+void o1_attention_tail_ways(int ways) { attention_tail_ways(ways); }
 int o1_mrope_table(const float* pos, int seq, float theta, float* cs) {
     if (!mrope_table64(pos, seq, theta, cs, g_stream)) return 1;
     count();

@@ -38,17 +38,21 @@ const CUtensorMap* cached_tmap(const void* base, uint64_t rows, uint64_t cols, u
 // ---- attn_tc.cu
 // q [S, ldq] (heads*128 columns used), k/v [S, ldk]/[S, ldv] (kv_heads*128),
 // out [S, ldo] seq-major; rows < ar_len are causal, rows >= ar_len see all keys.
+// scratch (optional, 16-byte aligned): room for the partial results of key-split tail items; without it
+// every (256 query rows, head) item is one CTA and the last wave of CTAs may be mostly empty
 bool flash_attention(const void* q, int ldq, const void* k, int ldk, const void* v, int ldv,
                      void* out, int ldo, int S, int heads, int kv_heads, int ar_len, float scale,
-                     cudaStream_t st);
+                     cudaStream_t st, void* scratch = nullptr, size_t scratch_bytes = 0);
 
 bool flash_attention_hm(const void* q, const void* k, const void* v, void* out, int S, int heads,
                         int kv_heads, int ar_len, float scale, bool out_head_major, cudaStream_t st);
+// tail split policy of flash_attention*: 0 = automatic, 1 = never, n = n key-range parts when they fit
+void attention_tail_ways(int ways);
 // seq-major operands; output rows [b*out_rows, (b+1)*out_rows) go to out_tab[b] (row-major, leading
 // dimension ldo), which may be peer-mapped memory of another GPU
 bool flash_attention_tab(const void* q, int ldq, const void* k, int ldk, const void* v, int ldv,
                          void* const* out_tab, int out_rows, int ldo, int S, int heads, int kv_heads,
-                         int ar_len, float scale, cudaStream_t st);
+                         int ar_len, float scale, cudaStream_t st, void* scratch = nullptr, size_t scratch_bytes = 0);
 
 // ---- elementwise.cu
 bool rmsnorm(const void* x, const void* w, void* y, int rows, int cols, float eps, cudaStream_t st);

@@ -148,7 +148,8 @@ hd_status o1_sp_block_attn_direct(const hd_block_binding* bw, const o1_sp_ws* w,
     void* to[8];
     for (int p = 0; p < P; ++p) to[p] = (uint16_t*)pt->recv[p] + (size_t)w->sp_rank * R * qcp;
     SP_TRY(flash_attention_tab(g, C, g + qcp, C, g + qcp + kcp, C, to, R, qcp, w->S, w->heads / P, w->kv_heads / P,
-                               w->ar_len, (float)(1.0 / sqrt(128.0)), st), "attention");
+                               w->ar_len, (float)(1.0 / sqrt(128.0)), st, w->swi, (size_t)w->rows * w->ff * 2),
+           "attention");
     return HD_OK;
 }
 
@@ -188,7 +189,8 @@ hd_status o1_sp_block_attn(const o1_sp_ws* w) {
     const int qcp = w->heads * 128 / P, kcp = w->kv_heads * 128 / P, C = qcp + 2 * kcp;
     const uint16_t* g = (const uint16_t*)w->gath;
     SP_TRY(flash_attention(g, C, g + qcp, C, g + qcp + kcp, C, w->attn, qcp, w->S, w->heads / P, w->kv_heads / P,
-                           w->ar_len, (float)(1.0 / sqrt(128.0)), current_stream()), "attention");
+                           w->ar_len, (float)(1.0 / sqrt(128.0)), current_stream(), w->swi,
+                           (size_t)w->rows * w->ff * 2), "attention");
     return HD_OK;
 }
 

@@ -136,3 +136,41 @@ def test_flash_attention_full_size_sampled_rows(pkg, orc, dev):
     hi = vmax.reshape(KV, 128)[kvh] * 1.01 + 0.02
     lo = vmin.reshape(KV, 128)[kvh] * 1.01 - 0.02
     assert bool(((o <= hi) & (o >= lo)).all()) and bool(torch.isfinite(o).all())
+
+
+@pytest.mark.parametrize("S,H,KV,ar,ways", [(1280, 32, 8, 255, 0), (2304, 20, 4, 18, 0), (2304, 20, 4, 18, 9),
+                                            (2304, 20, 4, 2304, 0), (1037, 40, 8, 600, 0), (3000, 8, 2, 0, 3),
+                                            (3000, 8, 2, 0, 12), (3000, 36, 4, 200, 2), (3000, 36, 4, 2900, 0), (1500, 150, 50, 1, 5)])
+def test_flash_attention_key_split_tail(pkg, orc, dev, S, H, KV, ar, ways):
+    """With scratch the items of the last, partly filled wave are cut along the keys and merged: same result as
+    the oracle (class D) and close to the unsplit kernel; item counts here leave tails of different sizes, one
+    case is fully causal (tail items with different key ranges), one has fewer items than SMs."""
+    ld = (H + 2 * KV) * 128
+    qkv = seeded_bf16((S, ld), 77, 0.0, 1.5)
+    d = u16_to_torch(qkv, dev)
+    args = (C.c_void_p(d.data_ptr()), ld, C.c_void_p(d.data_ptr() + H * 256), ld,
+            C.c_void_p(d.data_ptr() + (H + KV) * 256), ld)
+    plain = torch.zeros(S, H * 128, dtype=torch.bfloat16, device=dev)
+    split = torch.zeros_like(plain)
+    scratch = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    assert pkg.lib.o1_flash_attention(*args, pkg.ptr(plain), H * 128, S, H, KV, ar, 128 ** -0.5) == 0
+    pkg.lib.o1_attention_tail_ways(ways)            # 0: the library's own choice; n: forced
+    try:
+        assert pkg.lib.o1_flash_attention_ws(*args, pkg.ptr(split), H * 128, S, H, KV, ar, 128 ** -0.5,
+                                             pkg.ptr(scratch), scratch.numel()) == 0, pkg.last_error()
+        torch.cuda.synchronize()
+    finally:
+        pkg.lib.o1_attention_tail_ways(0)
+    ref = np.zeros((S, H * 128), dtype=np.uint16)
+    orc.orc_attention_rows(np_ptr(qkv), ld, np_ptr(qkv[:, H * 128:]), ld, np_ptr(qkv[:, (H + KV) * 128:]), ld,
+                           np_ptr(ref), H * 128, H, KV, S, 128, 128 ** -0.5, ar, None, 0)
+    assert_close(torch_to_u16(split), ref, "D", "key-split attention vs oracle")
+    assert_close(torch_to_u16(split), torch_to_u16(plain), "C", "key-split vs unsplit")
+    if ways > 1:
+        assert not torch.equal(split.view(torch.int16), plain.view(torch.int16)), "the split path did not run"
+    # too little scratch: falls back to the unsplit form, bit for bit
+    small = torch.zeros_like(plain)
+    assert pkg.lib.o1_flash_attention_ws(*args, pkg.ptr(small), H * 128, S, H, KV, ar, 128 ** -0.5, pkg.ptr(scratch),
+                                         1024) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(small.view(torch.int16), plain.view(torch.int16))
