@@ -28,7 +28,7 @@ WORKLOADS = {
     "c2": (256, 128, 128),   # "2048^2" of BASELINE.json: 16384 image tokens
     "c1": (256, 64, 64),     # 4096 image tokens
     "c0": (256, 32, 32),     # 1024 image tokens
-    "c3": (512, 128, 128),   # multi-reference edit: + 4 reference images of 64x64 tokens (1 GPU only here)
+    "c3": (512, 128, 128),   # multi-reference edit: + 4 reference images of 64x64 tokens
     "c4": (256, 64, 64),     # c1 geometry after a rank-64 LoRA merge, one image per GPU (data parallel)
 }
 C3_REFS = [(4096, 64, 64, 8, 8)] * 4     # (tokens, grid_h, grid_w, cond_h, cond_w) per reference
@@ -130,8 +130,6 @@ def run_ours(args):
     T, gh, gw = WORKLOADS[args.workload]
     I_tgt = gh * gw
     is_ref, is_lora = args.workload == "c3", args.workload == "c4"
-    if is_ref and world > 1:
-        raise SystemExit("workload c3 is measured on one GPU here")
     I = I_tgt + (sum(r[0] for r in C3_REFS) if is_ref else 0)      # rows that go through x_embedder
     S = T + I
     layers = args.layers
@@ -196,10 +194,10 @@ def run_ours(args):
         torch.cuda.empty_cache()
         if args.exchange == "direct":
             # exchanges done by the producing kernels' epilogues (peer stores) + flag barriers
-            eng = spmod.EngineSP(w, T, I, sp_size, sp_rank, direct=True)
+            eng = spmod.EngineSP(w, T, I, sp_size, sp_rank, ar_len=ar, direct=True)
             spmod.connect_direct(eng, sp_group)
         else:
-            eng = spmod.EngineSP(w, T, I, sp_size, sp_rank, spmod.nccl_exchange(sp_group))
+            eng = spmod.EngineSP(w, T, I, sp_size, sp_rank, spmod.nccl_exchange(sp_group), ar_len=ar)
         i0, i1, n_text_local = eng.i0, eng.i1, eng.t1 - eng.t0
         z, z_next = z[i0:i1].contiguous(), z_next[i0:i1].contiguous()
         z_host = z.cpu().pin_memory()
@@ -207,11 +205,12 @@ def run_ours(args):
         z_stage = torch.empty_like(z)
         xp_local = torch.empty(eng.rows, 3072, dtype=torch.bfloat16, device=dev)
         xp_pair = torch.empty(2, i1 - i0, 3072, dtype=torch.bfloat16, device=dev)
+        n_step_local = max(0, min(I_tgt, i1) - i0)      # local image rows that are target (stepped) rows
     xp_both = torch.empty(2, S, 3072, dtype=torch.bfloat16, device=dev) if (pair and sp_size == 1) else None
 
     def step_device(i, zin, zout):
         s0, s1 = sig[i % STEPS_PER_IMAGE], sig[i % STEPS_PER_IMAGE + 1]
-        if is_ref:
+        if is_ref and not pair:
             eng.denoise_step_cfg_ref(ids_c, ids_u, posd, zin, I_tgt, s0, s1, GUIDANCE, zout)
             return
         if not pair:
@@ -222,14 +221,15 @@ def run_ours(args):
             mine = xp_both[branch]
             eng.forward(ids_b, posd, zin, 1.0 - s0, out=mine)
             dist.all_gather_into_tensor(xp_both.view(-1), mine.view(-1), group=cfg_group)
+            # reference rows (c3) are static: only the target rows are stepped
             rc = lib.o1_sched_cfg_flow_step(pkg.ptr(zin), pkg.ptr(xp_both[0, T:]), pkg.ptr(xp_both[1, T:]), s0, s1,
-                                            GUIDANCE, pkg.ptr(zout), I * 3072)
+                                            GUIDANCE, pkg.ptr(zout), I_tgt * 3072)
         else:
             eng.forward(ids_b, posd, zin if zin.numel() else None, 1.0 - s0, out_local=xp_local)
             mine = xp_local[n_text_local:]
             dist.all_gather_into_tensor(xp_pair.view(-1), mine.reshape(-1), group=cfg_group)
             rc = lib.o1_sched_cfg_flow_step(pkg.ptr(zin), pkg.ptr(xp_pair[0]), pkg.ptr(xp_pair[1]), s0, s1,
-                                            GUIDANCE, pkg.ptr(zout), zin.numel()) if zin.numel() else 0
+                                            GUIDANCE, pkg.ptr(zout), n_step_local * 3072) if n_step_local else 0
         assert rc == 0
 
     def step_host(i):

@@ -485,6 +485,13 @@ hd_status o1_sp_forward_begin(const hd_forward_binding *bw, const o1_sp_ws *w, c
                               int tms_token_id, void *hidden_out);
 hd_status o1_sp_forward_end(const hd_forward_binding *bw, const o1_sp_ws *w, const void *hidden,
                             void *norm_scratch, void *out_local);
+/* Visual conditioning of a sharded forward (src/model/forward.c:277-285 masked scatter of image_embeds into the
+ * <image_pad> rows after the embedding, :363-369 DeepStack add after blocks 0..2), on this rank's rows.
+ * mask_global [S] uint8 on the device; embed_row0 = marked rows before this rank's first row. */
+hd_status o1_sp_visual_scatter(const o1_sp_ws *w, const uint8_t *mask_global, const void *image_embeds, int embed_row0,
+                               const void *in, void *out);
+hd_status o1_sp_deepstack(const o1_sp_ws *w, const uint8_t *mask_global, const void *deepstack_l, int embed_row0,
+                          const void *in, void *out);
 
 /* Direct form of the two exchanges: no collective call and no staging copy.  Each rank maps its peers' gath
  * [S][C] and recv [P][rows][Hc] buffers and a small flag array (CUDA IPC: o1_peer_*; in a C host

@@ -250,6 +250,24 @@ hd_status o1_sp_forward_begin(const hd_forward_binding* bw, const o1_sp_ws* w, c
     return HD_OK;
 }
 
+// Visual conditioning on this rank's rows (src/model/forward.c:277-285, :363-369).  mask_global [S] uint8 marks the
+// <image_pad> rows; embed_row0 = number of marked rows before this rank's first row (the caller counts them once
+// per request), so that the k-th marked row of the whole sequence still receives row k.  Out of place: in -> out.
+hd_status o1_sp_visual_scatter(const o1_sp_ws* w, const uint8_t* mask_global, const void* image_embeds, int embed_row0,
+                               const void* in, void* out) {
+    if (!sp_ok(w) || !mask_global || !image_embeds || !in || !out || embed_row0 < 0) { hd_set_error("sp: bad arguments"); return HD_ERR_MISSING; }
+    SP_TRY(masked_scatter(in, mask_global + w->row0, (const uint16_t*)image_embeds + (size_t)embed_row0 * w->hidden, out,
+                          w->rows, w->hidden, current_stream()), "masked_scatter");
+    return HD_OK;
+}
+hd_status o1_sp_deepstack(const o1_sp_ws* w, const uint8_t* mask_global, const void* deepstack_l, int embed_row0,
+                          const void* in, void* out) {
+    if (!sp_ok(w) || !mask_global || !deepstack_l || !in || !out || embed_row0 < 0) { hd_set_error("sp: bad arguments"); return HD_ERR_MISSING; }
+    SP_TRY(deepstack_inject(in, mask_global + w->row0, (const uint16_t*)deepstack_l + (size_t)embed_row0 * w->hidden, out,
+                            w->rows, w->hidden, current_stream()), "deepstack");
+    return HD_OK;
+}
+
 // final RMSNorm + head on this rank's rows: hidden [rows, hidden] -> out_local [rows, 3072]
 hd_status o1_sp_forward_end(const hd_forward_binding* bw, const o1_sp_ws* w, const void* hidden, void* norm_scratch,
                             void* out_local) {

@@ -41,6 +41,8 @@ for _name, _args in (("o1_sp_rope_table", (C.POINTER(SpWs), c_void_p)),
                                                  c_void_p)),
                      ("o1_sp_block_attn_direct", (C.POINTER(BlockBinding), C.POINTER(SpWs), C.POINTER(SpPeers))),
                      ("o1_sp_barrier", (C.POINTER(SpWs), C.POINTER(SpPeers), C.c_uint)),
+                     ("o1_sp_visual_scatter", (C.POINTER(SpWs), c_void_p, c_void_p, c_int, c_void_p, c_void_p)),
+                     ("o1_sp_deepstack", (C.POINTER(SpWs), c_void_p, c_void_p, c_int, c_void_p, c_void_p)),
                      ("o1_sp_block_pre", (C.POINTER(BlockBinding), C.POINTER(SpWs), c_void_p)),
                      ("o1_sp_block_attn", (C.POINTER(SpWs),)),
                      ("o1_sp_block_post", (C.POINTER(BlockBinding), C.POINTER(SpWs), c_void_p, c_void_p)),
@@ -88,6 +90,7 @@ class EngineSP:
     def __init__(self, weights, text_len, img_tokens, sp_size, sp_rank, exchange=None, ar_len=None, direct=False):
         self.w, self.P, self.r, self.exchange = weights, sp_size, sp_rank, exchange
         self.direct, self.peers, self.region, self.epoch, self._opened = direct, None, None, 0, []
+        self.visual = None
         d = weights.dims
         self.T, self.I, self.S = text_len, img_tokens, text_len + img_tokens
         (self.row0, _), (self.t0, self.t1), (self.i0, self.i1) = shard_rows(self.S, self.T, sp_size, sp_rank)
@@ -134,6 +137,33 @@ class EngineSP:
                        recv=recv_ptr, ln=self.ln.data_ptr(), ar=self.ar.data_ptr(),
                        post=self.post.data_ptr(), swi=self.swi.data_ptr(), rope=self.rope.data_ptr())
 
+    def set_visual(self, mask, image_embeds, deepstack):
+        """Visual conditioning of the following forwards: mask uint8 [S] (device) marks the <image_pad> rows,
+        image_embeds [V, hidden], deepstack = three [V, hidden] tensors; None switches it off.  Only ranks whose
+        rows hold marked rows do any work; the count of marked rows before this rank's rows is taken once here."""
+        if mask is None:
+            self.visual = None
+            return
+        m = mask.to("cpu")
+        first = int(m[:self.row0].sum())
+        mine = int(m[self.row0:self.row0 + self.rows].sum())
+        self.visual = (mask, image_embeds, list(deepstack), first) if mine else None
+
+    def _visual_after_embed(self, cur, nxt):
+        if self.visual is None:
+            return cur, nxt
+        mask, emb, _, first = self.visual
+        check(lib.o1_sp_visual_scatter(C.byref(self.ws), ptr(mask), ptr(emb), first, ptr(cur), ptr(nxt)), "sp_scatter")
+        return nxt, cur
+
+    def _visual_after_block(self, l, cur, nxt):
+        """cur holds the block's output; DeepStack writes the sum into the other buffer."""
+        if self.visual is None or l >= 3:
+            return cur, nxt
+        mask, _, dss, first = self.visual
+        check(lib.o1_sp_deepstack(C.byref(self.ws), ptr(mask), ptr(dss[l]), first, ptr(cur), ptr(nxt)), "sp_deepstack")
+        return nxt, cur
+
     def connect(self, region_bases, opened=()):
         """region_bases[p]: base of SP rank p's region as mapped in this process (own region for p == r)."""
         pt = SpPeers()
@@ -167,7 +197,7 @@ class EngineSP:
         check(lib.o1_sp_rope_table(ws, ptr(pos)), "sp_rope_table")
         check(lib.o1_sp_forward_begin(C.byref(w.binding), ws, ptr(ids), ptr(vin_local), ptr(self.timestep),
                                       ptr(self.small), ptr(self.xe_stage), TMS_ID, ptr(self.hid[0])), "sp_begin")
-        cur, nxt = self.hid
+        cur, nxt = self._visual_after_embed(*self.hid)
         for l in range(w.n_layers):
             bb = C.byref(w.block_binding(l))
             check(lib.o1_sp_block_pre(bb, ws, ptr(cur)), "sp_block_pre")
@@ -175,7 +205,7 @@ class EngineSP:
             check(lib.o1_sp_block_attn(ws), "sp_block_attn")
             yield ("a2a", self.attn.view(self.P, self.rows, self.Hc), self.recv)
             check(lib.o1_sp_block_post(bb, ws, ptr(cur), ptr(nxt)), "sp_block_post")
-            cur, nxt = nxt, cur
+            cur, nxt = self._visual_after_block(l, nxt, cur)
         check(lib.o1_sp_forward_end(C.byref(w.binding), ws, ptr(cur), ptr(self.ln), ptr(out_local)), "sp_end")
 
     def _stages_direct(self, ids, pos, vin_local, out_local):
@@ -183,7 +213,7 @@ class EngineSP:
         check(lib.o1_sp_rope_table_full(ws, pt, ptr(pos)), "sp_rope_table_full")
         check(lib.o1_sp_forward_begin(C.byref(w.binding), ws, ptr(ids), ptr(vin_local), ptr(self.timestep),
                                       ptr(self.small), ptr(self.xe_stage), TMS_ID, ptr(self.hid[0])), "sp_begin")
-        cur, nxt = self.hid
+        cur, nxt = self._visual_after_embed(*self.hid)
         for l in range(w.n_layers):
             bb = C.byref(w.block_binding(l))
             check(lib.o1_sp_block_pre_direct(bb, ws, pt, ptr(cur)), "sp_block_pre_direct")
@@ -191,7 +221,7 @@ class EngineSP:
             check(lib.o1_sp_block_attn_direct(bb, ws, pt), "sp_block_attn_direct")
             yield ("barrier", None, None)
             check(lib.o1_sp_block_post(bb, ws, ptr(cur), ptr(nxt)), "sp_block_post")
-            cur, nxt = nxt, cur
+            cur, nxt = self._visual_after_block(l, nxt, cur)
         check(lib.o1_sp_forward_end(C.byref(w.binding), ws, ptr(cur), ptr(self.ln), ptr(out_local)), "sp_end")
 
     def forward(self, ids, pos, vin_local, t, out_local=None):

@@ -95,3 +95,51 @@ def test_sp_direct_form_on_real_gpus(pkg):
     line = [l for l in res.stdout.splitlines() if l.startswith("{")][-1]
     rep = json.loads(line)
     assert rep["ok"] and rep["direct_equals_staged"] and rep["device_error"] == 0
+
+
+@pytest.mark.parametrize("P,direct", [(2, False), (4, True)])
+def test_sp_multi_reference_forward_with_visual_conditioning(pkg, dev, P, direct):
+    """Edit / personalise layout on sharded rows: K = 4 reference grids behind the target grid, <image_pad> rows
+    receive image_embeds and the three DeepStack adds on whichever rank holds them.  Against the unsharded
+    hd_forward with the same visual inputs."""
+    from o1c_b200 import sp
+    refs = [(64, 8, 8, 4, 4), (64, 8, 8, 4, 6), (16, 4, 4, 2, 2), (96, 8, 12, 3, 5)]   # tokens, grid, cond grid
+    T, gh, gw = 88, 16, 16
+    ids = np.random.default_rng(3).integers(0, 151000, size=T).astype(np.int64)
+    o = 8
+    for (_, _, _, ch, cw) in refs:                     # <|vision_start|> + one <|image_pad|> run per reference
+        ids[o] = 151652
+        ids[o + 1:o + 1 + ch * cw] = 151655
+        o += 1 + ch * cw + 3
+    ids[-2], ids[-1] = 151669, pkg.TMS_ID
+    _, pos_t, ar = pkg.seq_ref(ids.tolist(), refs, gh, gw)
+    pos = pos_t.numpy()
+    I = gh * gw + sum(r[0] for r in refs)
+    S = T + I
+    assert S % P == 0 and pos.shape[1] == S
+    text = ids
+    L = 4
+    w = pkg.Weights(n_layers=L, seed=1234, weight_set="B", device=dev)
+    vmask = np.zeros(S, dtype=np.uint8)
+    vmask[:T] = (text == 151655)
+    V = int(vmask.sum())
+    emb = u16_to_torch(seeded_bf16((V, 4096), 81), dev)
+    dss = [u16_to_torch(seeded_bf16((V, 4096), 82 + k, 0.0, 0.5), dev) for k in range(3)]
+    vin = u16_to_torch(seeded_bf16((I, 3072), 90), dev)
+    idsd, posd, maskd = torch.from_numpy(text).to(dev), torch.from_numpy(pos).to(dev), torch.from_numpy(vmask).to(dev)
+    ref = pkg.Engine(w, T, I, ar_len=ar).forward(idsd, posd, vin, 0.3, visual=(maskd, emb, dss))
+    engines = [sp.EngineSP(w, T, I, P, r, None, ar_len=ar, direct=direct) for r in range(P)]
+    try:
+        for e in engines:
+            if direct:
+                e.connect([x.region for x in engines])
+            e.set_visual(maskd, emb, dss)
+        assert sum(e.visual is not None for e in engines) >= 1
+        out = sp.run_emulated(engines, idsd, posd, vin, 0.3)
+        torch.cuda.synchronize()
+    finally:
+        for e in engines:
+            e.close()
+    assert_close(out, ref, "B", f"SP{P} multi-reference forward vs unsharded")
+    plain = pkg.Engine(w, T, I, ar_len=ar).forward(idsd, posd, vin, 0.3)
+    assert parity.metrics(plain, out)[0] > 1e-2           # the visual inputs were applied
