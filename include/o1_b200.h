@@ -285,6 +285,11 @@ typedef struct {
 } hd_weight_store;
 /* src/model/weights.h:125-131.  GGUF v3, tensors F32 / F16 / BF16 (io/gguf.c:196-206), all stored bf16. */
 hd_status hd_weights_to_device_gguf(const char *gguf_path, int device_id, hd_weight_store *out);
+/* Header only: the same store (arena allocated, tensor addresses fixed) with the payload left unwritten, for ranks
+ * that receive the arena bytes from the rank that read the file (e.g. ncclBroadcast of arena_ptr / arena_bytes).
+ * The layout depends only on the header and is identical on every rank.  (src/model/weights.c:519-669 reads the
+ * whole file on every process.) */
+hd_status o1_weights_gguf_layout(const char *gguf_path, int device_id, hd_weight_store *out);
 void hd_weight_store_free(hd_weight_store *s);
 const char *hd_weights_last_error(void);
 /* header-only parse, no GPU needed: returns the tensor count (or -1) and describes tensor `index` */

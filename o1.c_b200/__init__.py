@@ -175,6 +175,7 @@ _sig("o1_noise_pipe_free", None, _P)
 _sig("o1_decode_to_rgb", c_int, _P, c_int, c_int, c_int, c_int, _P, _P, C.POINTER(c_int), C.POINTER(c_float),
      C.POINTER(c_float))
 _sig("hd_weights_to_device_gguf", c_int, C.c_char_p, c_int, C.POINTER(WeightStore))
+_sig("o1_weights_gguf_layout", c_int, C.c_char_p, c_int, C.POINTER(WeightStore))
 _sig("hd_weight_store_free", None, C.POINTER(WeightStore))
 _sig("hd_weights_last_error", C.c_char_p)
 _sig("o1_gguf_probe", c_int64, C.c_char_p, c_int64, C.c_char_p, c_size_t, C.POINTER(c_int64), C.POINTER(c_int),
@@ -251,5 +252,5 @@ def use_torch_stream():
 
 
 from .model import (  # noqa: E402
-    Weights, Engine, seq_t2i, seq_ref, dev_sigmas, write_gguf, gguf_tensor_name, weight_seed, SLOT_NAMES, GLOBAL_NAMES, tensor_shape,
+    Weights, GgufWeights, Engine, seq_t2i, seq_ref, dev_sigmas, write_gguf, gguf_tensor_name, weight_seed, SLOT_NAMES, GLOBAL_NAMES, tensor_shape,
 )

@@ -160,7 +160,19 @@ int64_t o1_gguf_probe(const char* path, int64_t index, char* name_out, size_t na
     return (int64_t)idx.tensors.size();
 }
 
+static hd_status load_gguf(const char* gguf_path, int device_id, hd_weight_store* out, bool payload);
+
 hd_status hd_weights_to_device_gguf(const char* gguf_path, int device_id, hd_weight_store* out) {
+    return load_gguf(gguf_path, device_id, out, true);
+}
+// Same store (arena allocated, every tensor's address fixed by the header) without reading the payload: the
+// caller fills the arena from another rank's copy (one disk read + a broadcast over NVLink instead of one
+// disk read per GPU).  The arena layout depends only on the header, so it is identical on every rank.
+hd_status o1_weights_gguf_layout(const char* gguf_path, int device_id, hd_weight_store* out) {
+    return load_gguf(gguf_path, device_id, out, false);
+}
+
+static hd_status load_gguf(const char* gguf_path, int device_id, hd_weight_store* out, bool payload) {
     if (!gguf_path || !out) { werr("weights: null argument"); return HD_ERR_MISSING; }
     memset(out, 0, sizeof(*out));
     GgufIndex idx;
@@ -223,6 +235,7 @@ hd_status hd_weights_to_device_gguf(const char* gguf_path, int device_id, hd_wei
             snprintf(out->largest_name, sizeof(out->largest_name), "%s", t.name.c_str());
         }
         const size_t esz = t.type == 0 ? 4 : 2;
+        if (!payload) continue;
         if (fseeko(f, (off_t)(idx.data_start + t.offset), SEEK_SET) != 0) { werr("weights: seek failed for %s", a.name); rc = HD_ERR_IO; break; }
         uint64_t done_el = 0;
         while (done_el < t.numel && rc == HD_OK) {

@@ -7,6 +7,7 @@ weight arena + bindings (src/model/weights.c, forward.c:61-105), position ids
 the step loop (src/runtime/generate.c:1314-1455).
 """
 import ctypes as C
+import os
 
 import torch
 
@@ -354,3 +355,52 @@ def write_gguf(path, tensors, metadata=None, alignment=256):
             f.seek(start + o)
             f.write(np.ascontiguousarray(a).tobytes())
         f.truncate(start + off)
+
+
+class _DevBytes:
+    """Zero-copy torch view of raw device memory through the CUDA array interface."""
+
+    def __init__(self, ptr_, nbytes):
+        self.__cuda_array_interface__ = {"shape": (int(nbytes),), "typestr": "|u1", "data": (int(ptr_), False),
+                                         "version": 2}
+
+
+class GgufWeights:
+    """A GGUF pack on the device (hd_weights_to_device_gguf + hd_forward_resolve).  With a process group only
+    rank `src` reads the payload; the other ranks allocate the identical arena from the header and receive
+    the bytes by one broadcast (o1.c src/model/weights.c:519-669 would read the file once per process)."""
+
+    def __init__(self, path, n_layers, device, group=None, src=0):
+        from . import WeightStore, ForwardBinding
+        self.device = torch.device(device)
+        idx = self.device.index if self.device.index is not None else torch.cuda.current_device()
+        self.store, self.binding, self.n_layers = WeightStore(), ForwardBinding(), n_layers
+        # the architecture is fixed on this path (o1.c src/model/block.h:48-62); a pack with other shapes
+        # fails in the kernels' shape checks
+        self.dims = dict(hidden=HIDDEN, heads=HEADS, kv_heads=KV_HEADS, head_dim=HEAD_DIM, ff=FF, vocab=VOCAB)
+        reader = True
+        if group is not None:
+            import torch.distributed as dist
+            reader = dist.get_rank() == src
+        fn = lib.hd_weights_to_device_gguf if reader else lib.o1_weights_gguf_layout
+        if fn(os.fsencode(path), idx, C.byref(self.store)) != 0:
+            raise RuntimeError(lib.hd_weights_last_error().decode())
+        if group is not None:
+            import torch.distributed as dist
+            arena = torch.as_tensor(_DevBytes(self.store.arena_ptr, self.store.arena_bytes), device=self.device)
+            dist.broadcast(arena, src=src, group=group)
+            torch.cuda.synchronize()
+        if lib.hd_forward_resolve(C.byref(self.store), n_layers, C.byref(self.binding)) != 0:
+            err = lib.hd_last_error().decode()
+            lib.hd_weight_store_free(C.byref(self.store))
+            raise RuntimeError(err)
+
+    def block_binding(self, layer):
+        return self.binding.blocks[layer]
+
+    def nbytes(self):
+        return int(self.store.arena_bytes)
+
+    def close(self):
+        lib.hd_forward_binding_free(C.byref(self.binding))
+        lib.hd_weight_store_free(C.byref(self.store))

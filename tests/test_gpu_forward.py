@@ -244,3 +244,50 @@ def test_gguf_pack_to_device_and_resolve(pkg, dev, tmp_path):
     pkg.lib.hd_weight_store_free(C.byref(store))
     assert not store.arena_ptr
     assert pkg.lib.hd_weights_to_device_gguf(b"/nonexistent.gguf", 0, C.byref(store)) != 0
+
+
+def test_forward_from_a_gguf_pack_and_header_only_layout(pkg, dev, tmp_path):
+    """A pack of the real architecture (1 block) written from the seeded arena: loading it back gives the same
+    forward bit for bit; the header-only store has the identical layout, and once its arena holds a copy of the
+    loaded bytes (what a broadcast from the reading rank delivers) it gives the same forward too."""
+    L, T, gh, gw = 1, 16, 4, 8
+    I = gh * gw
+    w = pkg.Weights(n_layers=L, seed=1234, weight_set="B", device=dev)
+    tensors = []
+    for layer, names in [(-1, pkg.GLOBAL_NAMES)] + [(l, pkg.SLOT_NAMES) for l in range(L)]:
+        for name in names:
+            bits = w.tensor(layer, name).contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+            tensors.append((pkg.gguf_tensor_name(layer, name), bits))
+    path = str(tmp_path / "model.gguf")
+    pkg.write_gguf(path, tensors, {"general.architecture": "hidream_o1", "hidream.num_layers": str(L)})
+    pos, _ = pkg.seq_t2i(T, gh, gw)
+    ids = np.arange(T, dtype=np.int64) + 7
+    ids[-1] = pkg.TMS_ID
+    idsd, posd = torch.from_numpy(ids).to(dev), pos.to(dev)
+    vin = u16_to_torch(seeded_bf16((I, 3072), 43), dev)
+    want = pkg.Engine(w, T, I).forward(idsd, posd, vin, 0.5)
+    gw_ = pkg.GgufWeights(path, L, dev)
+    try:
+        got = pkg.Engine(gw_, T, I).forward(idsd, posd, vin, 0.5)
+        torch.cuda.synchronize()
+        assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+        lay = pkg.WeightStore()
+        assert pkg.lib.o1_weights_gguf_layout(path.encode(), 0, C.byref(lay)) == 0, pkg.lib.hd_weights_last_error()
+        try:
+            assert lay.arena_bytes == gw_.store.arena_bytes and lay.n_allocs == gw_.store.n_allocs
+            assert lay.host_bytes_loaded == 0
+            for i in range(lay.n_allocs):
+                assert lay.allocs[i].name == gw_.store.allocs[i].name
+                assert lay.allocs[i].dev_ptr - lay.arena_ptr == gw_.store.allocs[i].dev_ptr - gw_.store.arena_ptr
+            a = torch.as_tensor(pkg.model._DevBytes(gw_.store.arena_ptr, lay.arena_bytes), device=dev)
+            b = torch.as_tensor(pkg.model._DevBytes(lay.arena_ptr, lay.arena_bytes), device=dev)
+            b.copy_(a)                                        # stands in for the broadcast
+            fb = pkg.ForwardBinding()
+            assert pkg.lib.hd_forward_resolve(C.byref(lay), L, C.byref(fb)) == 0
+            assert fb.blocks[0].q_proj - lay.arena_ptr == gw_.binding.blocks[0].q_proj - gw_.store.arena_ptr
+            pkg.lib.hd_forward_binding_free(C.byref(fb))
+            assert torch.equal(a, b)
+        finally:
+            pkg.lib.hd_weight_store_free(C.byref(lay))
+    finally:
+        gw_.close()
