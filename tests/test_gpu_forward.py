@@ -291,3 +291,44 @@ def test_forward_from_a_gguf_pack_and_header_only_layout(pkg, dev, tmp_path):
             pkg.lib.hd_weight_store_free(C.byref(lay))
     finally:
         gw_.close()
+
+
+def test_cfg_step_replays_from_a_cuda_graph(pkg, dev):
+    """One CFG denoise step (2 forwards + fused scheduler update) issues no allocation and no host
+    synchronisation, so it can be captured once and replayed: the replay equals the eager step bit for bit,
+    also after the latent buffer has been refilled."""
+    T, gh, gw, L = 24, 8, 12, 2
+    I = gh * gw
+    w = pkg.Weights(n_layers=L, seed=1234, weight_set="B", device=dev)
+    eng = pkg.Engine(w, T, I)
+    pos, _ = pkg.seq_t2i(T, gh, gw)
+    rng = np.random.default_rng(5)
+    ids_c = rng.integers(0, 151000, size=T).astype(np.int64)
+    ids_u = rng.integers(0, 151000, size=T).astype(np.int64)
+    ids_c[-1] = ids_u[-1] = pkg.TMS_ID
+    ic, iu, posd = torch.from_numpy(ids_c).to(dev), torch.from_numpy(ids_u).to(dev), pos.to(dev)
+    z = u16_to_torch(seeded_bf16((I, 3072), 11, 0.0, 8.0), dev)
+    eager = torch.empty_like(z)
+    eng.denoise_step_cfg(ic, iu, posd, z, 0.8, 0.7, 5.0, eager)          # also the warm-up (tensor maps, attributes)
+    torch.cuda.synchronize()
+    out = torch.empty_like(z)
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    try:
+        with torch.cuda.stream(side):
+            pkg.use_torch_stream()
+            with torch.cuda.graph(graph, stream=side):
+                eng.denoise_step_cfg(ic, iu, posd, z, 0.8, 0.7, 5.0, out)
+        out.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out.view(torch.int16), eager.view(torch.int16))
+        z2 = u16_to_torch(seeded_bf16((I, 3072), 12, 0.0, 8.0), dev)
+        z.copy_(z2)
+        graph.replay()
+        torch.cuda.synchronize()
+    finally:
+        pkg.use_torch_stream()                                            # back to the default stream
+    eng.denoise_step_cfg(ic, iu, posd, z2, 0.8, 0.7, 5.0, eager)
+    torch.cuda.synchronize()
+    assert torch.equal(out.view(torch.int16), eager.view(torch.int16))
