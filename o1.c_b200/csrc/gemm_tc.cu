@@ -280,6 +280,44 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     }
                     __syncwarp();
                 }
+            } else if (EPI == EPI_LORA) {
+                // In-place update of W.  The contraction is short (9 x rank), so this epilogue's read-modify-
+                // write of W bounds the kernel: all of the row's W values of four 32-column groups are requested
+                // before the first is used, which keeps about 32 KB per SM in flight instead of one load per thread.
+#pragma unroll 1
+                for (int c4 = 0; c4 < BN / 128; ++c4) {
+                    uint4 wv[4][4];
+                    const uint16_t* wrow = g.out + (size_t)row * g.ldo + nb * BN + c4 * 128;
+                    if (row_ok) {
+#pragma unroll
+                        for (int c = 0; c < 4; ++c)
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) wv[c][i] = reinterpret_cast<const uint4*>(wrow + c * 32)[i];
+                    }
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t r[32];
+                        tmem_ld32(t_row + c4 * 128 + c * 32, r);
+                        tmem_ld_wait();
+                        if (row_ok) {
+                            uint4* dst = reinterpret_cast<uint4*>(g.out + (size_t)row * g.ldo + nb * BN + c4 * 128 + c * 32);
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const uint4 o = wv[c][i];
+                                uint4 n;
+                                n.x = pack_bf16x2(bf16lo(o.x) + g.scale * __uint_as_float(r[i * 8 + 0]),
+                                                  bf16hi(o.x) + g.scale * __uint_as_float(r[i * 8 + 1]));
+                                n.y = pack_bf16x2(bf16lo(o.y) + g.scale * __uint_as_float(r[i * 8 + 2]),
+                                                  bf16hi(o.y) + g.scale * __uint_as_float(r[i * 8 + 3]));
+                                n.z = pack_bf16x2(bf16lo(o.z) + g.scale * __uint_as_float(r[i * 8 + 4]),
+                                                  bf16hi(o.z) + g.scale * __uint_as_float(r[i * 8 + 5]));
+                                n.w = pack_bf16x2(bf16lo(o.w) + g.scale * __uint_as_float(r[i * 8 + 6]),
+                                                  bf16hi(o.w) + g.scale * __uint_as_float(r[i * 8 + 7]));
+                                dst[i] = n;
+                            }
+                        }
+                    }
+                }
             } else {
 #pragma unroll 1
                 for (int c = 0; c < BN / 32; ++c) {

@@ -38,18 +38,28 @@ __global__ void lora_split_up_kernel(const float* __restrict__ up, uint16_t* __r
 #pragma unroll
     for (int t = 0; t < 9; ++t) row[t * Rp + r] = h[t / 3];
 }
-// down [R,K] fp32 -> B' [K, 9*Rp]
-__global__ void lora_split_down_kernel(const float* __restrict__ down, uint16_t* __restrict__ b, int K,
-                                       int R, int Rp) {
-    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= (long)K * Rp) return;
-    const int k = (int)(i % K);     // k fastest: coalesced reads of down
-    const int r = (int)(i / K);
-    uint16_t h[3] = {0, 0, 0};
-    if (r < R) split3(down[(long)r * K + k], h[0], h[1], h[2]);
-    uint16_t* row = b + (long)k * 9 * Rp;
+// down [R,K] fp32 -> B' [K, 9*Rp].  down is read along k (its contiguous axis), B' is written along its
+// rows (9*Rp contiguous values per k): a tile of 32 k x Rp ranks goes through shared memory as split terms.
+__global__ void __launch_bounds__(256) lora_split_down_kernel(const float* __restrict__ down,
+                                                              uint16_t* __restrict__ b, int K, int R, int Rp) {
+    extern __shared__ uint16_t sm[];            // [3][32][Rp + 2]: term, k within the tile, rank (padded)
+    const int k0 = blockIdx.x * 32;
+    const int ldp = Rp + 2;
+    for (int i = threadIdx.x; i < 32 * Rp; i += blockDim.x) {
+        const int kk = i & 31, r = i >> 5;      // kk fastest: coalesced reads of down
+        uint16_t h[3] = {0, 0, 0};
+        if (r < R && k0 + kk < K) split3(down[(long)r * K + k0 + kk], h[0], h[1], h[2]);
 #pragma unroll
-    for (int t = 0; t < 9; ++t) row[t * Rp + r] = h[t % 3];
+        for (int t = 0; t < 3; ++t) sm[(t * 32 + kk) * ldp + r] = h[t];
+    }
+    __syncthreads();
+    const int row_len = 9 * Rp;
+    for (int i = threadIdx.x; i < 32 * row_len; i += blockDim.x) {
+        const int kk = i / row_len, c = i - kk * row_len;   // c fastest: coalesced writes of B'
+        if (k0 + kk >= K) break;
+        const int t = c / Rp, r = c - t * Rp;
+        b[(long)(k0 + kk) * row_len + c] = sm[((t % 3) * 32 + kk) * ldp + r];
+    }
 }
 // shapes the tensor-core tiles do not cover
 __global__ void lora_simt_kernel(uint16_t* __restrict__ w, const float* __restrict__ up,
@@ -86,7 +96,8 @@ hd_status hd_lora_merge_gpu(hd_lora_entry* entries, size_t count, void* stream) 
         }
         const float scale = e->multiplier * e->alpha / (float)e->rank;
         const int Rp = (R + 63) & ~63;
-        if (!gemm_tc_supported(N, K, 9 * Rp, EPI_LORA)) {
+        const size_t split_smem = (size_t)3 * 32 * (Rp + 2) * sizeof(uint16_t);   // lora_split_down_kernel's tile
+        if (!gemm_tc_supported(N, K, 9 * Rp, EPI_LORA) || split_smem > 200 * 1024) {
             const long tot = (long)N * K;
             lora_simt_kernel<<<(unsigned)((tot + 255) / 256), 256, 0, st>>>(
                 (uint16_t*)e->base_dev, (const float*)e->up_dev, (const float*)e->down_dev, N, K, R, scale);
@@ -105,9 +116,16 @@ hd_status hd_lora_merge_gpu(hd_lora_entry* entries, size_t count, void* stream) 
         }
         uint16_t* a = stage;
         uint16_t* b = stage + (((size_t)N * 9 * Rp + 127) & ~(size_t)127);
-        const long na = (long)N * Rp, nb = (long)K * Rp;
+        const long na = (long)N * Rp;
         lora_split_up_kernel<<<(unsigned)((na + 255) / 256), 256, 0, st>>>((const float*)e->up_dev, a, N, R, Rp);
-        lora_split_down_kernel<<<(unsigned)((nb + 255) / 256), 256, 0, st>>>((const float*)e->down_dev, b, K, R, Rp);
+        if (split_smem > 48 * 1024 &&
+            cudaFuncSetAttribute(lora_split_down_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)split_smem) !=
+                cudaSuccess) {
+            set_error("lora: shared-memory attribute for rank %d failed", R);
+            rc = HD_ERR_RUNTIME;
+            break;
+        }
+        lora_split_down_kernel<<<(unsigned)((K + 31) / 32), 256, split_smem, st>>>((const float*)e->down_dev, b, K, R, Rp);
         if (cudaGetLastError() != cudaSuccess) { set_error("lora: split launch failed"); rc = HD_ERR_RUNTIME; break; }
         // W[N,K] += scale * A'[N,9Rp] . B'[K,9Rp]^T, in place
         if (!gemm_bf16_ld(a, 9 * Rp, b, nullptr, e->base_dev, K, N, K, 9 * Rp, EPI_LORA, nullptr, nullptr,

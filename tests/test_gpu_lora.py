@@ -36,7 +36,7 @@ def entry(pkg, w, up, down, R, K, N, alpha, mult):
     return e
 
 
-@pytest.mark.parametrize("N,K,R", [(1024, 4096, 64), (4096, 1024, 16), (384, 256, 8), (100, 72, 4)])
+@pytest.mark.parametrize("N,K,R", [(1024, 4096, 64), (4096, 1024, 16), (384, 256, 8), (100, 72, 4), (512, 1280, 200)])
 def test_lora_merge(pkg, orc, dev, N, K, R):
     w0 = seeded_bf16((N, K), 51, 0.0, 0.02)
     up = np.empty((N, R), dtype=np.float32)
