@@ -56,7 +56,8 @@ def test_lora_merge(pkg, orc, dev, N, K, R):
     orc.orc_lora_merge(np_ptr(ref), np_ptr(up), np_ptr(down), N, K, R, mult * alpha / R)
     got = torch_to_u16(wd)
     assert (got != w0).mean() > 0.01, "merge changed nothing"
-    check_merged(got, ref, w0)
+    # 9 x 256 exact products per element are summed by the tensor core in its own order: more tie flips than at rank 64
+    check_merged(got, ref, w0, max_frac=2e-4 if R <= 64 else 2e-3)
 
 
 def test_lora_sequential_adapters_and_errors(pkg, orc, dev):
