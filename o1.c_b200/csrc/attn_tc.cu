@@ -477,9 +477,10 @@ __global__ void __launch_bounds__(AD) attn_merge_kernel(const AttnArgs a, int n_
 // Number of key-range parts for the tail items: the last (total % SMs) items would otherwise occupy a wave
 // of CTAs alone.  Cost of the tail in item durations: rounds of CTAs it needs, ceil(rem * w / SMs), times the
 // duration of a part, 1/w plus a fixed share for its prologue, Q load and fp32 epilogue (about four key
-// tiles' worth).  After many full waves the SMs have drifted apart by a good fraction of an item's duration
-// and a small tail costs little, so the split must save more than that drift to be used.  Every part keeps
-// at least two key tiles.
+// tiles' worth).  Measured on B200: the split pays when the tail is a sizeable part of a wave (76 of 148 SMs
+// at 8 heads and S = 16640: -13 %) or when at most one full wave precedes it (S = 1280: -20 %); after many
+// full waves the SMs have drifted apart and a tail of a few items costs next to nothing (no gain measured
+// with 4 or 8 tail items after 7 or 14 waves), so it is left alone.  Every part keeps at least two key tiles.
 static int g_tail_ways = 0;   // 0: choose; 1: never split; n > 1: n parts whenever they fit
 void attention_tail_ways(int ways) { g_tail_ways = ways < 0 ? 0 : ways; }
 
@@ -499,8 +500,8 @@ static int choose_tail_ways(int total, int nsm, int min_tiles, size_t scratch_by
         const double cost = (double)((rem * w + nsm - 1) / nsm) * (1.0 / w + fixed) + 0.02;
         if (cost < best_cost - 1e-9) { best_cost = cost; best = w; }
     }
-    const double drift = 0.1 * (total / nsm) + 0.05;
-    return (1.0 - best_cost) > drift ? best : 1;
+    const bool worth = rem * 4 >= nsm || total / nsm <= 1;
+    return (worth && best_cost < 0.9) ? best : 1;
 }
 
 static bool flash_attention_impl(const void* q, int ldq, const void* k, int ldk, const void* v,
