@@ -1,13 +1,18 @@
 #!/usr/bin/env python
 """Benchmark of the HiDream-O1 denoising hot path on B200.
 
-Metric (BASELINE.json): seconds per image for 28-step CFG text-to-image at 16384 image tokens
+Metric: seconds per image for 28-step CFG text-to-image at 16384 image tokens
 (+256 text tokens, 36 decoder blocks).  A "step" here is one denoise step: cond forward, uncond
 forward, fused CFG + flow-match scheduler update.  sec/image = 28 x mean step time.
 
-  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c1|c0]
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c0|c1|c2|c3|c4]
+                  [--exchange direct|nccl]
 
-Prints ONE JSON line (rank 0).  See DESIGN.md for what every key means.
+Prints ONE JSON line (rank 0): value = s/image from CUDA-event step times with the latent resident on the
+device (max over ranks); e2e = the same through pinned host latents (H2D + D2H inside the timed region);
+kernels = per tensor-core kernel family launches / total ms / TFLOP/s from events the library records
+around its own launches; roofline = the family with the largest event time against the measured cuBLAS
+bf16 peak; cpu_baseline = the C/OpenMP oracle timed on one decoder block and extrapolated by FLOPs.
 """
 import argparse
 import ctypes as C

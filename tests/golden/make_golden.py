@@ -1,5 +1,5 @@
-"""Regenerates the fixtures in this folder.  Needs the reference tree (default
-/root/reference) and oracle/_ref/libo1ref.so (make -C oracle ref); neither is
+"""Regenerates the fixtures in this folder.  Needs a checkout of the reference (o1.c; its location comes
+from the environment variable O1_REFERENCE) and oracle/_ref/libo1ref.so (make -C oracle ref); neither is
 needed to RUN the tests, which only read the files written here.
 
   scheduler_dump.json : the reference's own scheduler oracle dumps
