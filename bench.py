@@ -30,7 +30,7 @@ sys.path.insert(0, os.path.join(ROOT, "tests"))
 
 WORKLOADS = {
     # name: (text tokens, grid_h, grid_w)
-    "c2": (256, 128, 128),   # "2048^2" of BASELINE.json: 16384 image tokens
+    "c2": (256, 128, 128),   # the 2048 x 2048 image of the headline metric: 16384 image tokens
     "c1": (256, 64, 64),     # 4096 image tokens
     "c0": (256, 32, 32),     # 1024 image tokens
     "c3": (512, 128, 128),   # multi-reference edit: + 4 reference images of 64x64 tokens
@@ -369,7 +369,7 @@ def run_ours(args):
 
 
 def merge_synthetic_lora(pkg, w, layers, dev):
-    """BASELINE config 4: rank-64 adapters (A, B ~ N(0, 0.01), alpha = 64, multiplier 1) merged at load into
+    """Workload c4: rank-64 adapters (A, B ~ N(0, 0.01), alpha = 64, multiplier 1) merged at load into
     every linear of every block through hd_lora_merge_gpu.  Returns the merge time in ms (CUDA events)."""
     import torch
     targets = ["q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj"]

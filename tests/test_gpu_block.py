@@ -101,7 +101,7 @@ def test_block_vs_reference_cuda_build(pkg, dev, production):
 
 
 def test_block_c0_shape_vs_reference_production(pkg, dev):
-    """BASELINE config 0: 256 text + 32x32 image tokens, both weight sets, vs the reference's production
+    """Workload c0 (one decoder block): 256 text + 32x32 image tokens, both weight sets, vs the reference's production
     path (cuBLASLt + cuDNN two-pass SDPA) when available, else vs the CPU oracle on weight set B."""
     T, gh, gw = 256, 32, 32
     r = parity.reflib()

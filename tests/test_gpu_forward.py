@@ -159,7 +159,7 @@ def test_decode_to_rgb_and_gate(pkg, dev):
 
 
 def test_multi_reference_forward_with_visual_conditioning(pkg, orc, dev, golden):
-    """Edit / personalise layout (BASELINE config 3 in miniature): text with <image_pad> runs, target grid,
+    """Edit / personalise layout (workload c3 in miniature): text with <image_pad> runs, target grid,
     K = 4 reference grids with their own 3-axis positions from the hd_seq_build fixture; vision-tower outputs
     (image_embeds, DeepStack x3) scattered / added on the pad rows; reference rows taken from the x_embedder
     cache.  Against the oracle, and cache path == recompute path bit for bit."""
