@@ -347,7 +347,8 @@ qk_norm_rope_kernel(uint16_t* __restrict__ x, int ld, int S, int heads, int hpb,
         unpack8(*reinterpret_cast<const uint4*>(base + 8 * t), lo);
         unpack8(*reinterpret_cast<const uint4*>(base + 64 + 8 * t), hi);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) sq += lo[j] * lo[j] + hi[j] * hi[j];
+        // explicit roundings: the fused GEMM epilogue (EPI_QKNORM) sums in exactly this order
+        for (int j = 0; j < 8; ++j) sq = __fadd_rn(sq, __fmaf_rn(hi[j], hi[j], __fmul_rn(lo[j], lo[j])));
     }
     sq += __shfl_xor_sync(0xffffffffu, sq, 1);
     sq += __shfl_xor_sync(0xffffffffu, sq, 2);

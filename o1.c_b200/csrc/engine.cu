@@ -478,16 +478,26 @@ static hd_status block_forward(const void* in, const float* cs, int ar_len, cons
 
     // 1. input RMSNorm
     BLK_TRY(rmsnorm(in, bw->input_ln, b.ln, S, hidden, eps, st), "input_norm");
-    // 2. q/k/v projections into one seq-major buffer [S, qc | kc | kc]
-    BLK_TRY(gemm_bf16_ld(b.ln, hidden, bw->q_proj, nullptr, b.qkv, ld, S, qc, hidden, EPI_STORE,
-                         nullptr, nullptr, 0, 0.f, 0, st), "q_proj");
-    BLK_TRY(gemm_bf16_ld(b.ln, hidden, bw->k_proj, nullptr, b.qkv + qc, ld, S, kc, hidden, EPI_STORE,
-                         nullptr, nullptr, 0, 0.f, 0, st), "k_proj");
-    BLK_TRY(gemm_bf16_ld(b.ln, hidden, bw->v_proj, nullptr, b.qkv + qc + kc, ld, S, kc, hidden,
-                         EPI_STORE, nullptr, nullptr, 0, 0.f, 0, st), "v_proj");
-    // 3-6. per-head RMSNorm + MRoPE on q and k, in place (no head split)
-    BLK_TRY(qk_norm_rope(b.qkv, ld, S, heads, bw->q_norm, cs, eps, st), "q_norm_rope");
-    BLK_TRY(qk_norm_rope(b.qkv + qc, ld, S, kv_heads, bw->k_norm, cs, eps, st), "k_norm_rope");
+    // 2-6. q/k/v projections into one seq-major buffer [S, qc | kc | kc]; the per-head RMSNorm + MRoPE of q and k
+    // (block.c:266-289) run inside the projections' epilogues where the tensor-core tiles cover the shape,
+    // otherwise as one in-place kernel per tensor (no head split either way)
+    if (gemm_tc_supported(S, qc, hidden, EPI_QKNORM) && gemm_tc_supported(S, kc, hidden, EPI_QKNORM)) {
+        BLK_TRY(gemm_bf16_ld(b.ln, hidden, bw->q_proj, nullptr, b.qkv, ld, S, qc, hidden, EPI_QKNORM,
+                             bw->q_norm, cs, 0, eps, 0, st), "q_proj+norm+rope");
+        BLK_TRY(gemm_bf16_ld(b.ln, hidden, bw->k_proj, nullptr, b.qkv + qc, ld, S, kc, hidden, EPI_QKNORM,
+                             bw->k_norm, cs, 0, eps, 0, st), "k_proj+norm+rope");
+        BLK_TRY(gemm_bf16_ld(b.ln, hidden, bw->v_proj, nullptr, b.qkv + qc + kc, ld, S, kc, hidden,
+                             EPI_STORE, nullptr, nullptr, 0, 0.f, 0, st), "v_proj");
+    } else {
+        BLK_TRY(gemm_bf16_ld(b.ln, hidden, bw->q_proj, nullptr, b.qkv, ld, S, qc, hidden, EPI_STORE,
+                             nullptr, nullptr, 0, 0.f, 0, st), "q_proj");
+        BLK_TRY(gemm_bf16_ld(b.ln, hidden, bw->k_proj, nullptr, b.qkv + qc, ld, S, kc, hidden, EPI_STORE,
+                             nullptr, nullptr, 0, 0.f, 0, st), "k_proj");
+        BLK_TRY(gemm_bf16_ld(b.ln, hidden, bw->v_proj, nullptr, b.qkv + qc + kc, ld, S, kc, hidden,
+                             EPI_STORE, nullptr, nullptr, 0, 0.f, 0, st), "v_proj");
+        BLK_TRY(qk_norm_rope(b.qkv, ld, S, heads, bw->q_norm, cs, eps, st), "q_norm_rope");
+        BLK_TRY(qk_norm_rope(b.qkv + qc, ld, S, kv_heads, bw->k_norm, cs, eps, st), "k_norm_rope");
+    }
     // 7. attention, output already seq-major [S, heads*hd]
     // (the SwiGLU buffer is idle until step 11: it holds the partial results of key-split tail items)
     BLK_TRY(flash_attention(b.qkv, ld, b.qkv + qc, ld, b.qkv + qc + kc, ld, b.attn, qc, S, heads,

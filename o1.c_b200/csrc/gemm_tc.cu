@@ -35,6 +35,7 @@ struct GemmArgs {
     const uint16_t* bias;
     const uint16_t* resid;
     int ldr;
+    const float* rope;     // EPI_QKNORM: cos|sin table [M,128] fp32
     float scale;
     int num_m, num_n, group_m;
     // Output column blocks: column c lives at out + (c / o_cb) * o_cb_stride + row * ldo + c % o_cb
@@ -280,6 +281,77 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     }
                     __syncwarp();
                 }
+            } else if (EPI == EPI_QKNORM) {
+                // Per-head RMSNorm + rotary on the projection's output row (o1.c src/model/block.c:266-289 runs
+                // head split, hd_rmsnorm, hd_apply_rotary as separate passes).  This thread owns the whole row of
+                // the tile, i.e. BN/128 complete heads: the 128 values of a head are rounded to bf16 (the
+                // projection's stored result), summed in the order of qk_norm_rope_kernel (eight partial sums of
+                // 8 + 8 elements, pairwise tree) so that both paths agree bit for bit, normalised, rotated with the
+                // partner 64 columns away, and written once.
+#pragma unroll 1
+                for (int hb = 0; hb < BN / 128; ++hb) {
+                    uint32_t r[4][32];
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) tmem_ld32(t_row + hb * 128 + c * 32, r[c]);
+                    tmem_ld_wait();
+                    if (row_ok) {
+                        float part[8];
+#pragma unroll
+                        for (int t = 0; t < 8; ++t) {
+                            float acc = 0.f;
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                const int e = 8 * t + j;
+                                const float lo = bf16_round(__uint_as_float(r[e >> 5][e & 31]));
+                                const float hi = bf16_round(__uint_as_float(r[2 + (e >> 5)][e & 31]));
+                                r[e >> 5][e & 31] = __float_as_uint(lo);
+                                r[2 + (e >> 5)][e & 31] = __float_as_uint(hi);
+                                acc = __fadd_rn(acc, __fmaf_rn(hi, hi, __fmul_rn(lo, lo)));
+                            }
+                            part[t] = acc;
+                        }
+                        const float sq = __fadd_rn(__fadd_rn(__fadd_rn(part[0], part[1]), __fadd_rn(part[2], part[3])),
+                                                   __fadd_rn(__fadd_rn(part[4], part[5]), __fadd_rn(part[6], part[7])));
+                        const float inv = rsqrtf(sq / 128.0f + g.scale);
+                        const int col = nb * BN + hb * 128;
+                        const size_t ocol = g.o_cb ? (size_t)(col / g.o_cb) * g.o_cb_stride + (col % g.o_cb) : (size_t)col;
+                        uint16_t* orow = g.out + (size_t)row * g.ldo + ocol;
+                        const float* cs = g.rope + (size_t)row * 128;
+#pragma unroll
+                        for (int t = 0; t < 8; ++t) {
+                            const uint4 wl4 = *reinterpret_cast<const uint4*>(g.bias + 8 * t);
+                            const uint4 wh4 = *reinterpret_cast<const uint4*>(g.bias + 64 + 8 * t);
+                            const float wl[8] = {bf16lo(wl4.x), bf16hi(wl4.x), bf16lo(wl4.y), bf16hi(wl4.y),
+                                                 bf16lo(wl4.z), bf16hi(wl4.z), bf16lo(wl4.w), bf16hi(wl4.w)};
+                            const float wh[8] = {bf16lo(wh4.x), bf16hi(wh4.x), bf16lo(wh4.y), bf16hi(wh4.y),
+                                                 bf16lo(wh4.z), bf16hi(wh4.z), bf16lo(wh4.w), bf16hi(wh4.w)};
+                            const float4 ca = *reinterpret_cast<const float4*>(cs + 8 * t);
+                            const float4 cb = *reinterpret_cast<const float4*>(cs + 8 * t + 4);
+                            const float4 sa = *reinterpret_cast<const float4*>(cs + 64 + 8 * t);
+                            const float4 sb = *reinterpret_cast<const float4*>(cs + 64 + 8 * t + 4);
+                            const float cc[8] = {ca.x, ca.y, ca.z, ca.w, cb.x, cb.y, cb.z, cb.w};
+                            const float ss[8] = {sa.x, sa.y, sa.z, sa.w, sb.x, sb.y, sb.z, sb.w};
+                            float ol[8], oh[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                const int e = 8 * t + j;
+                                const float lo = __uint_as_float(r[e >> 5][e & 31]);
+                                const float hi = __uint_as_float(r[2 + (e >> 5)][e & 31]);
+                                const float a = bf16_round(wl[j] * lo * inv);
+                                const float b = bf16_round(wh[j] * hi * inv);
+                                ol[j] = bf16_round(a * cc[j]) - bf16_round(b * ss[j]);
+                                oh[j] = bf16_round(b * cc[j]) + bf16_round(a * ss[j]);
+                            }
+                            uint4 po, ph;
+                            po.x = pack_bf16x2(ol[0], ol[1]); po.y = pack_bf16x2(ol[2], ol[3]);
+                            po.z = pack_bf16x2(ol[4], ol[5]); po.w = pack_bf16x2(ol[6], ol[7]);
+                            ph.x = pack_bf16x2(oh[0], oh[1]); ph.y = pack_bf16x2(oh[2], oh[3]);
+                            ph.z = pack_bf16x2(oh[4], oh[5]); ph.w = pack_bf16x2(oh[6], oh[7]);
+                            *reinterpret_cast<uint4*>(orow + 8 * t) = po;
+                            *reinterpret_cast<uint4*>(orow + 64 + 8 * t) = ph;
+                        }
+                    }
+                }
             } else if (EPI == EPI_LORA) {
                 // In-place update of W.  The contraction is short (9 x rank), so this epilogue's read-modify-
                 // write of W bounds the kernel: all of the row's W values of four 32-column groups are requested
@@ -475,7 +547,7 @@ static bool launch_tc(const CUtensorMap* tA, const CUtensorMap* tB, const CUtens
     const int tiles = g.num_m * g.num_n;
     int grid = sm_count();
     if (grid > tiles) grid = tiles;
-    prof_before(EPI, 2.0 * g.M * (double)g.N * g.K * (EPI == EPI_SWIGLU ? 2.0 : 1.0), st);
+    prof_before(EPI == EPI_QKNORM ? (int)EPI_STORE : EPI, 2.0 * g.M * (double)g.N * g.K * (EPI == EPI_SWIGLU ? 2.0 : 1.0), st);
     kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, st>>>(*tA, *tB, *tB2, g);
     prof_after(st);
     cudaError_t e = cudaGetLastError();
@@ -538,6 +610,17 @@ bool gemm_bf16_ex(const void* x, int ldx, const void* w, const void* w2, void* y
     g.bias = (const uint16_t*)bias;
     g.resid = (const uint16_t*)resid; g.ldr = ldr;
     g.scale = scale;
+    g.rope = nullptr;
+    if (epi == EPI_QKNORM) {
+        // resid carries the cos|sin table, bias the norm weight; every 128 output columns are one head
+        if (!bias || !resid || (N % 128) != 0 || (o_cb && (o_cb % 128) != 0) || o_tab || (((uintptr_t)bias) & 15) ||
+            (((uintptr_t)resid) & 15)) {
+            set_error("gemm: per-head norm epilogue needs norm weight, cos|sin table and whole heads");
+            return false;
+        }
+        g.rope = (const float*)resid;
+        g.resid = nullptr;
+    }
     g.err = device_error_word();
     g.num_m = (M + BM - 1) / BM;
     // Row tiles are visited in groups whose activation slab (group_m x 128 rows x K) stays L2-resident
@@ -589,6 +672,7 @@ bool gemm_bf16_ex(const void* x, int ldx, const void* w, const void* w2, void* y
             case EPI_BIAS:  return launch_tc<EPI_BIAS, 256>(tA, tB, tB2, g, st);
             case EPI_RESID: return launch_tc<EPI_RESID, 256>(tA, tB, tB2, g, st);
             case EPI_LORA:  return launch_tc<EPI_LORA, 256>(tA, tB, tB2, g, st);
+            case EPI_QKNORM: return launch_tc<EPI_QKNORM, 256>(tA, tB, tB2, g, st);
         }
     } else {
         switch (epi) {
@@ -596,6 +680,7 @@ bool gemm_bf16_ex(const void* x, int ldx, const void* w, const void* w2, void* y
             case EPI_BIAS:  return launch_tc<EPI_BIAS, 128>(tA, tB, tB2, g, st);
             case EPI_RESID: return launch_tc<EPI_RESID, 128>(tA, tB, tB2, g, st);
             case EPI_LORA:  return launch_tc<EPI_LORA, 128>(tA, tB, tB2, g, st);
+            case EPI_QKNORM: return launch_tc<EPI_QKNORM, 128>(tA, tB, tB2, g, st);
         }
     }
     set_error("gemm: unknown epilogue %d", epi);

@@ -376,3 +376,31 @@ def test_seeded_fill_is_bit_identical_on_host_and_device(pkg, orc, dev):
     orc.orc_fill_normal_f32(np_ptr(h32), n, 99, 0.0, 1.0)
     assert (torch_to_u16(d16) == h16).all()
     assert (d32.cpu().numpy().view(np.uint32) == h32.view(np.uint32)).all()
+
+
+@pytest.mark.parametrize("M,N,K,ldy,bn", [(300, 512, 256, 512 + 384, 0), (1024, 1024, 512, 1024, 256), (130, 256, 128, 256, 128)])
+def test_projection_with_norm_and_rope_in_the_epilogue(pkg, dev, M, N, K, ldy, bn):
+    """GEMM whose epilogue applies the per-head RMSNorm + rotary (epilogue 6) == plain GEMM followed by the
+    in-place norm + rope kernel, bit for bit; columns of the output row beyond the projection stay untouched."""
+    heads = N // 128
+    x = dv(seeded_bf16((M, K), 71), dev)
+    w = dv(seeded_bf16((N, K), 72, 0.0, 0.05), dev)
+    nw = dv(seeded_bf16(128, 73, 1.0, 0.1), dev)
+    pos, _ = pkg.seq_t2i(20, 10, (M - 20 + 9) // 10)
+    tab = torch.empty(pos.shape[1], 128, device=dev)
+    pkg.lib.o1_mrope_table(pkg.ptr(pos.to(dev)), pos.shape[1], 5e6, pkg.ptr(tab))
+    assert pos.shape[1] >= M
+    fill = seeded_bf16((M, ldy), 74)
+    y_fused, y_plain = dv(fill, dev), dv(fill, dev)
+    rc = pkg.lib.o1_gemm(pkg.ptr(x), K, pkg.ptr(w), None, pkg.ptr(y_fused), ldy, M, N, K, 6, pkg.ptr(nw), pkg.ptr(tab),
+                         0, 1e-6, bn)
+    assert rc == 0, pkg.last_error()
+    rc = pkg.lib.o1_gemm(pkg.ptr(x), K, pkg.ptr(w), None, pkg.ptr(y_plain), ldy, M, N, K, 0, None, None, 0, 0.0, bn)
+    assert rc == 0, pkg.last_error()
+    assert pkg.lib.o1_qk_norm_rope(pkg.ptr(y_plain), ldy, M, heads, pkg.ptr(nw), pkg.ptr(tab), 1e-6) == 0
+    done(pkg, "gemm + norm + rope")
+    assert torch.equal(y_fused.view(torch.int16), y_plain.view(torch.int16))
+    assert (torch_to_u16(y_fused)[:, N:] == fill[:, N:]).all()
+    # shapes the tensor-core tiles do not cover refuse the fused epilogue instead of falling back silently
+    assert pkg.lib.o1_gemm(pkg.ptr(x), K, pkg.ptr(w), None, pkg.ptr(y_fused), ldy, 4, N, K, 6, pkg.ptr(nw), pkg.ptr(tab),
+                           0, 1e-6, 0) != 0
