@@ -1,6 +1,11 @@
 // Shared helpers: bf16 conversion with the reference's rounding
 // (src/cuda/cuda_internal.h:21-40 in o1.c: RNE by integer add, no NaN
 // special case), 128-bit vector types, error slot, stream handling.
+// On the device the rounding is the hardware conversion (cvt.rn.bf16.f32 /
+// cvt.rn.bf16x2.f32: one instruction instead of five per value; the epilogues
+// and elementwise kernels round several times per element).  It gives the
+// same result as the integer form for every finite input and infinity; only
+// NaN payloads differ (canonical NaN instead of a shifted payload).
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -19,20 +24,24 @@ __host__ __device__ __forceinline__ float bf16_to_f32(uint16_t b) {
 #endif
 }
 __host__ __device__ __forceinline__ uint16_t f32_to_bf16(float f) {
-    uint32_t u;
 #ifdef __CUDA_ARCH__
-    u = __float_as_uint(f);
+    uint16_t r;
+    asm("cvt.rn.bf16.f32 %0, %1;" : "=h"(r) : "f"(f));
+    return r;
 #else
+    uint32_t u;
     __builtin_memcpy(&u, &f, 4);
-#endif
     u += 0x7FFFu + ((u >> 16) & 1u);
     return (uint16_t)(u >> 16);
+#endif
 }
 __host__ __device__ __forceinline__ float bf16_round(float f) {
     return bf16_to_f32(f32_to_bf16(f));
 }
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
-    return (uint32_t)f32_to_bf16(lo) | ((uint32_t)f32_to_bf16(hi) << 16);
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
 }
 __device__ __forceinline__ float bf16lo(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16hi(uint32_t v) { return __uint_as_float(v & 0xFFFF0000u); }

@@ -334,45 +334,49 @@ bool apply_rotary(const void* x, const float* cosd, const float* sind, void* y, 
 __global__ void __launch_bounds__(256)
 qk_norm_rope_kernel(uint16_t* __restrict__ x, int ld, int S, int heads, int hpb, long blk_stride,
                     const uint16_t* __restrict__ w, const float* __restrict__ cs, float eps) {
-    const int gid = blockIdx.x * 32 + (threadIdx.x >> 3);  // (token, head) pair index
+    // 8 threads per token walk over its heads: the token's cos|sin values and the norm weights are loaded once
+    // and reused for every head (the table row is twice the size of a head, so loading it per head doubled the
+    // traffic of this kernel)
+    const int s = blockIdx.x * 32 + (threadIdx.x >> 3);
     const int t = threadIdx.x & 7;
-    const long total = (long)S * heads;
-    const bool active = gid < total;
-    const int s = active ? gid / heads : 0;
-    const int h = active ? gid % heads : 0;
-    uint16_t* base = x + (size_t)(h / hpb) * blk_stride + (size_t)s * ld + (h % hpb) * 128;
-    float lo[8], hi[8];
-    float sq = 0.f;
+    const bool active = s < S;
+    float wl[8], wh[8], cc[8], ss[8];
     if (active) {
-        unpack8(*reinterpret_cast<const uint4*>(base + 8 * t), lo);
-        unpack8(*reinterpret_cast<const uint4*>(base + 64 + 8 * t), hi);
-#pragma unroll
-        // explicit roundings: the fused GEMM epilogue (EPI_QKNORM) sums in exactly this order
-        for (int j = 0; j < 8; ++j) sq = __fadd_rn(sq, __fmaf_rn(hi[j], hi[j], __fmul_rn(lo[j], lo[j])));
+        unpack8(*reinterpret_cast<const uint4*>(w + 8 * t), wl);
+        unpack8(*reinterpret_cast<const uint4*>(w + 64 + 8 * t), wh);
+        const float4* c4 = reinterpret_cast<const float4*>(cs + (size_t)s * 128 + 8 * t);
+        const float4* s4 = reinterpret_cast<const float4*>(cs + (size_t)s * 128 + 64 + 8 * t);
+        const float4 ca = c4[0], cb = c4[1], sa = s4[0], sb = s4[1];
+        cc[0] = ca.x; cc[1] = ca.y; cc[2] = ca.z; cc[3] = ca.w; cc[4] = cb.x; cc[5] = cb.y; cc[6] = cb.z; cc[7] = cb.w;
+        ss[0] = sa.x; ss[1] = sa.y; ss[2] = sa.z; ss[3] = sa.w; ss[4] = sb.x; ss[5] = sb.y; ss[6] = sb.z; ss[7] = sb.w;
     }
-    sq += __shfl_xor_sync(0xffffffffu, sq, 1);
-    sq += __shfl_xor_sync(0xffffffffu, sq, 2);
-    sq += __shfl_xor_sync(0xffffffffu, sq, 4);
-    if (!active) return;
-    const float inv = rsqrtf(sq / 128.0f + eps);
-    float wl[8], wh[8];
-    unpack8(*reinterpret_cast<const uint4*>(w + 8 * t), wl);
-    unpack8(*reinterpret_cast<const uint4*>(w + 64 + 8 * t), wh);
-    const float4* c4 = reinterpret_cast<const float4*>(cs + (size_t)s * 128 + 8 * t);
-    const float4* s4 = reinterpret_cast<const float4*>(cs + (size_t)s * 128 + 64 + 8 * t);
-    const float4 ca = c4[0], cb = c4[1], sa = s4[0], sb = s4[1];
-    const float cc[8] = {ca.x, ca.y, ca.z, ca.w, cb.x, cb.y, cb.z, cb.w};
-    const float ss[8] = {sa.x, sa.y, sa.z, sa.w, sb.x, sb.y, sb.z, sb.w};
-    float ol[8], oh[8];
+    for (int h = 0; h < heads; ++h) {
+        uint16_t* base = x + (size_t)(h / hpb) * blk_stride + (size_t)(active ? s : 0) * ld + (h % hpb) * 128;
+        float lo[8], hi[8];
+        float sq = 0.f;
+        if (active) {
+            unpack8(*reinterpret_cast<const uint4*>(base + 8 * t), lo);
+            unpack8(*reinterpret_cast<const uint4*>(base + 64 + 8 * t), hi);
+            // explicit roundings: the fused GEMM epilogue (EPI_QKNORM) sums in exactly this order
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        const float a = bf16_round(wl[j] * lo[j] * inv);
-        const float b = bf16_round(wh[j] * hi[j] * inv);
-        ol[j] = bf16_round(a * cc[j]) - bf16_round(b * ss[j]);
-        oh[j] = bf16_round(b * cc[j]) + bf16_round(a * ss[j]);
+            for (int j = 0; j < 8; ++j) sq = __fadd_rn(sq, __fmaf_rn(hi[j], hi[j], __fmul_rn(lo[j], lo[j])));
+        }
+        sq += __shfl_xor_sync(0xffffffffu, sq, 1);
+        sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+        sq += __shfl_xor_sync(0xffffffffu, sq, 4);
+        if (!active) continue;
+        const float inv = rsqrtf(sq / 128.0f + eps);
+        float ol[8], oh[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float a = bf16_round(wl[j] * lo[j] * inv);
+            const float b = bf16_round(wh[j] * hi[j] * inv);
+            ol[j] = bf16_round(a * cc[j]) - bf16_round(b * ss[j]);
+            oh[j] = bf16_round(b * cc[j]) + bf16_round(a * ss[j]);
+        }
+        *reinterpret_cast<uint4*>(base + 8 * t) = pack8(ol);
+        *reinterpret_cast<uint4*>(base + 64 + 8 * t) = pack8(oh);
     }
-    *reinterpret_cast<uint4*>(base + 8 * t) = pack8(ol);
-    *reinterpret_cast<uint4*>(base + 64 + 8 * t) = pack8(oh);
 }
 bool qk_norm_rope(void* x, int ld, int S, int heads, const void* w, const float* cs_table, float eps,
                   cudaStream_t st) {
@@ -389,8 +393,7 @@ bool qk_norm_rope_blocked(void* x, int ld, int S, int heads, int hpb, long blk_s
         set_error("qk_norm_rope: bad args");
         return false;
     }
-    const long total = (long)S * heads;
-    qk_norm_rope_kernel<<<(unsigned)((total + 31) / 32), 256, 0, st>>>(
+    qk_norm_rope_kernel<<<(unsigned)((S + 31) / 32), 256, 0, st>>>(
         (uint16_t*)x, ld, S, heads, hpb, blk_stride, (const uint16_t*)w, cs_table, eps);
     O1_LAUNCH_CHECK("qk_norm_rope");
     return true;
