@@ -143,3 +143,34 @@ def test_sp_multi_reference_forward_with_visual_conditioning(pkg, dev, P, direct
     assert_close(out, ref, "B", f"SP{P} multi-reference forward vs unsharded")
     plain = pkg.Engine(w, T, I, ar_len=ar).forward(idsd, posd, vin, 0.3)
     assert parity.metrics(plain, out)[0] > 1e-2           # the visual inputs were applied
+
+
+def test_sp_barrier_gives_up_when_a_peer_never_arrives(pkg, dev):
+    """The flag barrier's wait is bounded: with a peer whose flag nobody sets the kernel returns after about two
+    seconds, the device error word carries code 30, and the context stays usable (the next kernels run)."""
+    import ctypes as C
+    import time
+    from o1c_b200 import sp
+    w = pkg.Weights(n_layers=1, device=dev)
+    engines = [sp.EngineSP(w, 24, 104, 2, r, direct=True) for r in range(2)]
+    try:
+        for e in engines:
+            e.connect([x.region for x in engines])
+        e0 = engines[0]
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        e0.barrier()                                  # rank 1 never runs its barrier: its flag stays 0
+        torch.cuda.synchronize()
+        waited = time.perf_counter() - t0
+        assert 0.5 < waited < 10.0, waited
+        assert pkg.lib.o1_device_error() == 30        # reads and clears the word
+        assert pkg.lib.o1_device_error() == 0
+        # rank 1 arrives late with the same epoch: rank 0's flag is already there, so this one passes
+        engines[1].barrier()
+        torch.cuda.synchronize()
+        assert pkg.lib.o1_device_error() == 0
+        a = torch.ones(1024, device=dev)
+        assert float((a + a).sum()) == 2048.0
+    finally:
+        for e in engines:
+            e.close()
