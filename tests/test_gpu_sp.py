@@ -174,3 +174,44 @@ def test_sp_barrier_gives_up_when_a_peer_never_arrives(pkg, dev):
     finally:
         for e in engines:
             e.close()
+
+
+def test_sp_direct_form_with_key_split_attention(pkg, dev):
+    """Two ranks at S = 2560: each rank's 160 attention items leave a tail of 12 behind the first wave, which is cut
+    along the keys (two ranges each; the partial results fit the rank's idle SwiGLU buffer) and merged; in the
+    direct form the merge kernel writes through the peer table.  Direct == staged bit for bit (same split), and
+    both agree with the unsharded forward, whose attention runs unsplit."""
+    from o1c_b200 import sp
+    P = 2
+    T, gh, gw, L = 256, 48, 48, 1
+    I = gh * gw
+    w = pkg.Weights(n_layers=L, seed=1234, weight_set="B", device=dev)
+    pos, _ = pkg.seq_t2i(T, gh, gw)
+    rng = np.random.default_rng(2)
+    ids = rng.integers(0, 151000, size=T).astype(np.int64)
+    ids[-1] = pkg.TMS_ID
+    idsd, posd = torch.from_numpy(ids).to(dev), pos.to(dev)
+    vin = u16_to_torch(seeded_bf16((I, 3072), 44), dev)
+    pkg.lib.o1_attention_tail_ways(2)                 # two key ranges per tail item wherever scratch and keys allow
+    try:
+        staged = sp.run_emulated([sp.EngineSP(w, T, I, P, r, None) for r in range(P)], idsd, posd, vin, 0.5)
+        engines = [sp.EngineSP(w, T, I, P, r, direct=True) for r in range(P)]
+        try:
+            for e in engines:
+                e.connect([x.region for x in engines])
+            direct = sp.run_emulated(engines, idsd, posd, vin, 0.5)
+            torch.cuda.synchronize()
+        finally:
+            for e in engines:
+                e.close()
+        pkg.lib.o1_attention_tail_ways(1)             # and the same sharded forward without any split
+        unsplit = sp.run_emulated([sp.EngineSP(w, T, I, P, r, None) for r in range(P)], idsd, posd, vin, 0.5)
+        torch.cuda.synchronize()
+    finally:
+        pkg.lib.o1_attention_tail_ways(0)
+    ref = pkg.Engine(w, T, I).forward(idsd, posd, vin, 0.5)
+    torch.cuda.synchronize()
+    assert torch.equal(direct.view(torch.int16), staged.view(torch.int16))
+    assert not torch.equal(staged.view(torch.int16), unsplit.view(torch.int16)), "the split path did not run"
+    assert_close(staged, unsplit, "C", "split vs unsplit sharded forward")
+    assert_close(direct, ref, "C", "sharded forward with key-split attention vs unsharded")
