@@ -197,11 +197,17 @@ def run_ours(args):
     if sp_size > 1:
         del eng
         torch.cuda.empty_cache()
+        eng = None
         if args.exchange == "direct":
             # exchanges done by the producing kernels' epilogues (peer stores) + flag barriers
             eng = spmod.EngineSP(w, T, I, sp_size, sp_rank, ar_len=ar, direct=True)
-            spmod.connect_direct(eng, sp_group)
-        else:
+            if not spmod.connect_direct(eng, sp_group):
+                # peer memory cannot be mapped here (no CUDA IPC between these processes): same kernels, NCCL
+                # all-to-all between the stages instead of peer stores
+                eng.close()
+                eng = None
+                args.exchange = "nccl (peer mapping unavailable)"
+        if eng is None:
             eng = spmod.EngineSP(w, T, I, sp_size, sp_rank, spmod.nccl_exchange(sp_group), ar_len=ar)
         i0, i1, n_text_local = eng.i0, eng.i1, eng.t1 - eng.t0
         z, z_next = z[i0:i1].contiguous(), z_next[i0:i1].contiguous()
@@ -336,7 +342,8 @@ def run_ours(args):
                                        + (f" x dp{images}" if images > 1 else "")),
                        "sp_exchange": (None if sp_size == 1 else
                                        ("peer stores from the GEMM / attention epilogues + flag barriers"
-                                        if args.exchange == "direct" else "NCCL all-to-all")),
+                                        if args.exchange == "direct" else "NCCL all-to-all"
+                                        + (" (peer mapping unavailable)" if "unavailable" in args.exchange else ""))),
                        "weights": "random-init N(0,0.02) bf16, seed 1234",
                        "l2": "no flush needed: every step streams 2 x %.1f GB of weights (L2 is 126 MB)"
                              % (w.nbytes() / 1e9)},

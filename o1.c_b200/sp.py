@@ -249,26 +249,35 @@ def nccl_exchange(group):
 
 def connect_direct(engine, group):
     """Exchange CUDA IPC handles of the peer regions inside the SP process group (ranks in sp_rank order)
-    and map them; every rank of the group must call this."""
+    and map them; every rank of the group must call this.  Returns True when every rank mapped every peer;
+    otherwise every rank gets False with nothing left mapped (the caller then uses the staged exchange)."""
     import torch.distributed as dist
     h = (C.c_ubyte * 64)()
-    if lib.o1_peer_export(engine.region, h) != 0:
-        raise RuntimeError("peer export failed")
+    ok = lib.o1_peer_export(engine.region, h) == 0
     handles = [None] * engine.P
-    dist.all_gather_object(handles, bytes(h), group=group)
+    dist.all_gather_object(handles, bytes(h) if ok else None, group=group)
     bases, opened = [], []
     for p in range(engine.P):
         if p == engine.r:
             bases.append(engine.region)
             continue
         q = c_void_p()
-        if lib.o1_peer_open((C.c_ubyte * 64).from_buffer_copy(handles[p]), C.byref(q)) != 0:
-            raise RuntimeError(f"cannot map the region of SP rank {p}")
+        if not ok or handles[p] is None or \
+                lib.o1_peer_open((C.c_ubyte * 64).from_buffer_copy(handles[p]), C.byref(q)) != 0:
+            ok = False
+            break
         bases.append(q.value)
         opened.append(q.value)
+    flag = torch.tensor([1 if ok else 0], device=engine.w.device, dtype=torch.int32)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)       # all ranks take the same branch
+    if int(flag.item()) == 0:
+        for q in opened:
+            lib.o1_peer_close(q)
+        return False
     engine.connect(bases, opened)
     torch.cuda.synchronize()
     dist.barrier(group=group)      # every region is zeroed and mapped before the first store into it
+    return True
 
 
 def run_emulated(engines, ids, pos, vin, t):

@@ -72,7 +72,7 @@ def main():
     ms_staged = timed(staged_eng) if args.time else None
     del staged_eng
     direct_eng = sp.EngineSP(w, T, I, world, rank, direct=True)
-    sp.connect_direct(direct_eng, dist.group.WORLD)
+    assert sp.connect_direct(direct_eng, dist.group.WORLD), "CUDA IPC mapping of the peer regions failed"
     direct = run(direct_eng)
     direct2 = run(direct_eng)
     ms_direct = timed(direct_eng) if args.time else None
