@@ -335,6 +335,104 @@ typedef struct {
 hd_status hd_lora_merge_gpu(hd_lora_entry *entries, size_t count, void *stream /* cudaStream_t */);
 const char *hd_lora_last_error(void);
 
+/* ------------------------------------------------ vision tower (edit / reference-image modes)
+ * src/model/vision.h:39-230 and src/cuda/vision_kernels.h:17-51: the Qwen3-VL ViT that turns the patchified
+ * conditioning image into `image_embeds` and the three DeepStack tensors consumed by hd_forward
+ * (hd_visual_cond).  Frozen configuration: 27 blocks, hidden 1152, 16 heads x 72, MLP 4304, LayerNorm eps
+ * 1e-6, GELU tanh in the blocks / erf in the mergers, 2x2 spatial merge into 4096-wide rows. */
+#define HD_VISION_DEPTH 27
+#define HD_VISION_HIDDEN 1152
+#define HD_VISION_HEADS 16
+#define HD_VISION_HEAD_DIM 72
+#define HD_VISION_INTERMEDIATE 4304
+#define HD_VISION_OUT_HIDDEN 4096
+#define HD_VISION_MERGE_SIZE 2
+#define HD_VISION_PATCH_DIM 1536
+#define HD_VISION_NUM_POS 2304
+#define HD_VISION_NUM_DS 3
+enum {
+    HD_B0_INPUT = 0, HD_B0_NORM1, HD_B0_QKV, HD_B0_Q, HD_B0_K, HD_B0_V, HD_B0_Q_ROT, HD_B0_K_ROT,
+    HD_B0_ATTN_HEADS, HD_B0_ATTN_MERGED, HD_B0_PROJ, HD_B0_ATTN_RESID, HD_B0_NORM2, HD_B0_FC1, HD_B0_FC2,
+    HD_B0_OUTPUT, HD_B0_SNAP_COUNT
+};
+/* src/model/vision.h:76-109: borrowed bf16 tensors [out, in] of the weight store */
+typedef struct {
+    const void *norm1_w, *norm1_b, *norm2_w, *norm2_b;   /* [1152] */
+    const void *qkv_w, *qkv_b;                           /* [3456,1152], [3456] */
+    const void *proj_w, *proj_b;                         /* [1152,1152], [1152] */
+    const void *fc1_w, *fc1_b;                           /* [4304,1152], [4304] */
+    const void *fc2_w, *fc2_b;                           /* [1152,4304], [1152] */
+} hd_vision_block_binding;
+typedef struct {
+    const void *norm_w, *norm_b;                         /* [1152] (final) or [4608] (DeepStack) */
+    const void *fc1_w, *fc1_b;                           /* [4608,4608], [4608] */
+    const void *fc2_w, *fc2_b;                           /* [4096,4608], [4096] */
+} hd_vision_merger_binding;
+typedef struct {
+    const void *patch_proj_w, *patch_proj_b;             /* [1152,1536], [1152] */
+    const void *pos_embed;                               /* [2304,1152] */
+    hd_vision_block_binding blocks[HD_VISION_DEPTH];
+    hd_vision_merger_binding merger;
+    hd_vision_merger_binding deepstack[HD_VISION_NUM_DS];
+} hd_vision_binding;
+/* src/model/vision.h:116-180, same fields in the same order.  On input only `patch_out` (= base of a
+ * region of hd_vision_workspace_bytes(n) bytes), the table fields filled by hd_vision_prepare_tables and the
+ * snapshot pointers are read; `sdpa` is accepted and ignored (attention is this library's flash kernel for
+ * every n).  Snapshots that exist on this path: block0_snap, block_out_snaps[], block0_snaps[INPUT, NORM1,
+ * QKV, ATTN_MERGED, PROJ, ATTN_RESID, NORM2, FC2, OUTPUT]; the others name tensors that are never
+ * materialised here (head-major q/k/v, pre-GELU fc1, merger stages) and are left untouched. */
+typedef struct {
+    void *patch_out, *pos_emb, *rot, *cosf, *sinf, *h_a, *h_b, *ln1, *qkv, *q, *k, *v, *qr, *kr, *scores, *probs,
+        *attn_out, *attn_resid, *ln2, *fc1, *fc2, *mlp_resid, *merged, *merge_norm, *merge_fc1, *merge_fc2,
+        *ds_merged, *ds_fc1, *ds_fc2;
+    void *pos_idx, *pos_wgt, *rot_coords, *rot_inv;      /* device tables inside `tables` */
+    void *tables;                                        /* hd_vision_tables_bytes(n) bytes, caller-owned */
+    int tables_n, tables_gh, tables_gw;                  /* what the tables were built for (-1 = nothing) */
+    int64_t bytes;
+    hd_sdpa_plan *sdpa;
+    void *block0_snap;
+    void *block0_snaps[HD_B0_SNAP_COUNT];
+    void *block_out_snaps[HD_VISION_DEPTH];
+    void *merger_snaps[5];
+    void *ds_merger_snaps[HD_VISION_NUM_DS][4];
+} hd_vision_workspace;
+/* src/model/vision.h:184-191: byte offsets from the workspace base.  The workspace here is O(n): -1 marks a
+ * tensor of the reference layout that this path never materialises (pos_emb, rot, probs, mask, merged,
+ * merge_fc2, ds_fc2).  q, k, v are the three 2048-column slices of one [n, 6144] buffer: head h occupies
+ * columns 128h .. 128h+71 of its slice, the remaining 56 are zero, q and k are already rotated (qr = q,
+ * kr = k).  `scores` is the attention output in the same padded form [n, 2048]; cosf / sinf are [n, 72] fp32;
+ * mlp_resid = h_b (where the 27th block leaves its output). */
+typedef struct {
+    int64_t patch_out, pos_emb, rot, h_a, h_b, ln1, attn_resid, ln2, fc2, mlp_resid, q, k, v, qr, kr, qkv,
+        scores, probs, mask, attn_out, fc1, cosf, sinf, merged, merge_norm, merge_fc1, merge_fc2, ds_merged,
+        ds_fc1, ds_fc2, total_bytes;
+} hd_vision_offsets;
+void hd_vision_layout(int64_t n, int64_t m, hd_vision_offsets *o);
+/* src/model/vision.h:197-209 */
+hd_status hd_vision_resolve(const hd_weight_store *wstore, hd_vision_binding *out);
+int64_t hd_vision_workspace_bytes(int64_t n);
+int64_t hd_vision_tables_bytes(int64_t n);
+/* src/model/vision.c:288-339: interpolation corners / weights, rotary coordinates and inverse frequencies for
+ * an (n = grid_h * grid_w) image, computed on the host and copied into ws->tables (blocking copies: set-up,
+ * not forward).  A repeated shape returns at once. */
+hd_status hd_vision_prepare_tables(hd_vision_workspace *ws, int n, int grid_h, int grid_w);
+/* src/model/vision.h:225-230.  pixel_values [n,1536] bf16 in processor (2x2 block-major) order;
+ * image_embeds_out [n/4,4096]; deepstack_out NULL or three [n/4,4096] buffers.  Enqueued on the library's
+ * current stream. */
+hd_status hd_vision_forward(const hd_vision_binding *bw, hd_vision_workspace *ws, const void *pixel_values, int n,
+                            int grid_h, int grid_w, void *image_embeds_out, void *deepstack_out[HD_VISION_NUM_DS]);
+/* src/cuda/vision_kernels.h:17-45: the tower's stand-alone kernels (void, errors via hd_cuda_last_error) */
+void hd_vision_patch(const void *x, const void *w, const void *bias, void *y, int n, int in_dim, int out_dim);
+void hd_vision_layernorm(const void *x, const void *w, const void *b, void *y, int rows, int cols, float eps);
+void hd_vision_gelu(const void *x, void *y, size_t n);
+void hd_vision_gelu_exact(const void *x, void *y, size_t n);
+void hd_vision_pos_interp(const void *pos_embed, const int *idx, const float *wgt, void *y, int n, int hidden);
+void hd_vision_rot(const float *inv_freq, const int *coords, void *y, int n, int half);
+void hd_vision_rot_cos_sin(const void *rot, float *cosd, float *sind, int n, int half);
+void hd_vision_spatial_merge(const void *in, void *out, int gh, int gw, int hidden);
+void hd_vision_qkv_split(const void *qkv, void *q, void *k, void *v, int n, int heads, int d);
+void hd_vision_attn_merge(const void *hm, void *sm, int heads, int n, int d);
+
 /* ------------------------------------------------ 3. added entry points */
 /* Stream every later call enqueues on (a cudaStream_t; NULL = legacy default). */
 void o1_set_stream(void *stream);
@@ -352,7 +450,10 @@ int64_t o1_launch_count(int reset);
 
 /* Tensor-core GEMM with a choice of fused epilogue and explicit row pitches.
  * epi: 0 store, 1 +bias, 2 +residual, 3 SwiGLU (w = gate, w2 = up, N = ff),
- * 4 LoRA read-modify-write.  force_bn: 0 auto, 128 or 256.  Returns 0 on success. */
+ * 4 LoRA read-modify-write, 7 +bias then GELU (tanh form when scale == 0, erf form otherwise).
+ * force_bn: 0 auto, 128 or 256.  Shapes: M >= 8 and K % 8 == 0 run on the tensor cores (a ragged last K block
+ * is zero-filled); epilogues 0, 1, 7 accept any N % 8 == 0 (ragged right tile edge), the others N % 128 == 0;
+ * anything else runs a SIMT kernel (epilogues 0 and 1 only).  Returns 0 on success. */
 int o1_gemm(const void *x, int ldx, const void *w, const void *w2, void *y, int ldy, int M, int N,
             int K, int epi, const void *bias, const void *resid, int ldr, float scale, int force_bn);
 /* Prefix-causal flash attention on seq-major operands: q [S, ldq], k [S, ldk],

@@ -95,6 +95,33 @@ class WeightStore(C.Structure):
                 ("gemm", c_void_p), ("arena_ptr", c_void_p), ("arena_bytes", c_int64), ("upload_stream", c_void_p)]
 
 
+VISION_DEPTH, VISION_HIDDEN, VISION_HEADS, VISION_HEAD_DIM, VISION_FF = 27, 1152, 16, 72, 4304
+VISION_OUT, VISION_PATCH_DIM, VISION_NUM_POS = 4096, 1536, 2304
+# hd_vision_binding (src/model/vision.h:76-109) is 351 consecutive tensor pointers: patch_proj w, b, pos_embed,
+# 27 x {norm1 w b, norm2 w b, qkv w b, proj w b, fc1 w b, fc2 w b}, merger {norm w b, fc1 w b, fc2 w b}, 3 x DeepStack
+VisionBinding = c_void_p * (3 + 12 * VISION_DEPTH + 6 + 3 * 6)
+
+
+class VisionWorkspace(C.Structure):
+    """hd_vision_workspace (src/model/vision.h:116-180)."""
+    _fields_ = [(n, c_void_p) for n in (
+        "patch_out", "pos_emb", "rot", "cosf", "sinf", "h_a", "h_b", "ln1", "qkv", "q", "k", "v", "qr", "kr",
+        "scores", "probs", "attn_out", "attn_resid", "ln2", "fc1", "fc2", "mlp_resid", "merged", "merge_norm",
+        "merge_fc1", "merge_fc2", "ds_merged", "ds_fc1", "ds_fc2", "pos_idx", "pos_wgt", "rot_coords", "rot_inv",
+        "tables")] + [("tables_n", c_int), ("tables_gh", c_int), ("tables_gw", c_int), ("bytes", c_int64),
+                      ("sdpa", c_void_p), ("block0_snap", c_void_p), ("block0_snaps", c_void_p * 16),
+                      ("block_out_snaps", c_void_p * VISION_DEPTH), ("merger_snaps", c_void_p * 5),
+                      ("ds_merger_snaps", (c_void_p * 4) * 3)]
+
+
+class VisionOffsets(C.Structure):
+    """hd_vision_offsets (src/model/vision.h:184-189)."""
+    _fields_ = [(n, c_int64) for n in (
+        "patch_out", "pos_emb", "rot", "h_a", "h_b", "ln1", "attn_resid", "ln2", "fc2", "mlp_resid", "q", "k", "v",
+        "qr", "kr", "qkv", "scores", "probs", "mask", "attn_out", "fc1", "cosf", "sinf", "merged", "merge_norm",
+        "merge_fc1", "merge_fc2", "ds_merged", "ds_fc1", "ds_fc2", "total_bytes")]
+
+
 # ----------------------------------------------------------------- signatures
 def _sig(name, restype, *argtypes):
     fn = getattr(lib, name)
@@ -140,6 +167,23 @@ _sig("hd_unipc_predict", None, _P, _P, _P, c_float, c_float, c_float, c_float, c
      c_float, c_int, _P, c_int)
 _sig("hd_vision_masked_scatter", None, _P, _P, _P, _P, c_int, c_int)
 _sig("hd_vision_deepstack_inject", None, _P, _P, _P, _P, c_int, c_int)
+_sig("hd_vision_layout", None, c_int64, c_int64, C.POINTER(VisionOffsets))
+_sig("hd_vision_resolve", c_int, C.POINTER(WeightStore), C.POINTER(VisionBinding))
+_sig("hd_vision_workspace_bytes", c_int64, c_int64)
+_sig("hd_vision_tables_bytes", c_int64, c_int64)
+_sig("hd_vision_prepare_tables", c_int, C.POINTER(VisionWorkspace), c_int, c_int, c_int)
+_sig("hd_vision_forward", c_int, C.POINTER(VisionBinding), C.POINTER(VisionWorkspace), _P, c_int, c_int, c_int, _P,
+     C.POINTER(c_void_p * 3))
+_sig("hd_vision_patch", None, _P, _P, _P, _P, c_int, c_int, c_int)
+_sig("hd_vision_layernorm", None, _P, _P, _P, _P, c_int, c_int, c_float)
+_sig("hd_vision_gelu", None, _P, _P, c_size_t)
+_sig("hd_vision_gelu_exact", None, _P, _P, c_size_t)
+_sig("hd_vision_pos_interp", None, _P, _P, _P, _P, c_int, c_int)
+_sig("hd_vision_rot", None, _P, _P, _P, c_int, c_int)
+_sig("hd_vision_rot_cos_sin", None, _P, _P, _P, c_int, c_int)
+_sig("hd_vision_spatial_merge", None, _P, _P, c_int, c_int, c_int)
+_sig("hd_vision_qkv_split", None, _P, _P, _P, _P, c_int, c_int, c_int)
+_sig("hd_vision_attn_merge", None, _P, _P, c_int, c_int, c_int)
 _sig("hd_sdpa_create", c_int, C.POINTER(_P), c_int, c_int, c_int, c_int, c_int, c_int, c_float)
 _sig("hd_sdpa_create_split", c_int, C.POINTER(_P), c_int, c_int, c_int, c_int, c_int, c_int, c_float)
 _sig("hd_sdpa_create_prod", c_int, C.POINTER(_P), c_int, c_int, c_int, c_int, c_int, c_int, c_float)
@@ -214,7 +258,7 @@ _sig("o1_denoise_step_cfg_host", c_int, C.POINTER(ForwardBinding), C.POINTER(For
      _P, c_int, _P, c_int, _P, _P, c_int, c_float, c_float, c_float, _P, _P, _P, _P, c_int, c_int,
      c_int, c_int, c_int, c_int)
 
-EPI_STORE, EPI_BIAS, EPI_RESID, EPI_SWIGLU, EPI_LORA = 0, 1, 2, 3, 4
+EPI_STORE, EPI_BIAS, EPI_RESID, EPI_SWIGLU, EPI_LORA, EPI_BIAS_GELU = 0, 1, 2, 3, 4, 7
 
 
 class O1Error(RuntimeError):

@@ -11,7 +11,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libo1b200.so")
-SOURCES = ["gemm_tc.cu", "attn_tc.cu", "elementwise.cu", "sched.cu", "lora.cu", "lora_static.cu", "sp.cu", "host.cu", "weights.cu", "engine.cu"]
+SOURCES = ["gemm_tc.cu", "attn_tc.cu", "elementwise.cu", "vision.cu", "sched.cu", "lora.cu", "lora_static.cu", "sp.cu", "host.cu", "weights.cu", "engine.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",

@@ -75,6 +75,13 @@ __device__ __forceinline__ void tile_coords(int tile, const GemmArgs& g, int& mb
     nb = r / gm;
 }
 
+// GELU of a bf16-valued activation, as o1.c's vision kernels compute it (src/cuda/vision_kernels.cu:100-133):
+// the tanh form of the ViT block MLP or the erf form of the patch mergers, fp32 throughout, rounded by the caller
+__device__ __forceinline__ float gelu_of(float v, bool exact) {
+    if (exact) return 0.5f * v * (1.0f + erff(v * 0.7071067811865476f));
+    const float u = 0.7978845608028654f * (v + 0.044715f * v * v * v);
+    return 0.5f * v * (1.0f + tanhf(u));
+}
 __device__ __forceinline__ void store32_bf16(uint16_t* dst, const float (&v)[32]) {
     uint4* d4 = reinterpret_cast<uint4*>(dst);
 #pragma unroll
@@ -145,7 +152,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const uint32_t tmem_base = *tmem_slot;
 
     const int num_tiles = g.num_m * g.num_n;
-    const int kblocks = g.K / BK;
+    const int kblocks = (g.K + BK - 1) / BK;   // a ragged last K block is zero-filled by TMA in both operands
 
     if (warp == 0) {
         // ------------------------------------------------------ TMA producer
@@ -396,18 +403,47 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     uint32_t r[32];
                     tmem_ld32(t_row + c * 32, r);
                     tmem_ld_wait();
-                    if (row_ok) {
-                        const int col = nb * BN + c * 32;
+                    const int col = nb * BN + c * 32;
+                    if (row_ok && col + 32 > g.N) {
+                        // ragged right edge (N % 32 != 0, N % 8 == 0; plain, bias and bias+GELU epilogues only):
+                        // the same arithmetic, eight columns at a time, nothing read or written beyond column N
+                        if (EPI == EPI_STORE || EPI == EPI_BIAS || EPI == EPI_BIAS_GELU) {
+                            for (int c8 = 0; c8 < 4 && col + c8 * 8 < g.N; ++c8) {
+                                float v8[8];
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) v8[j] = __uint_as_float(r[c8 * 8 + j]);
+                                if (EPI != EPI_STORE) {
+                                    const uint4 b4 = *reinterpret_cast<const uint4*>(g.bias + col + c8 * 8);
+                                    const float b8[8] = {bf16lo(b4.x), bf16hi(b4.x), bf16lo(b4.y), bf16hi(b4.y),
+                                                         bf16lo(b4.z), bf16hi(b4.z), bf16lo(b4.w), bf16hi(b4.w)};
+#pragma unroll
+                                    for (int j = 0; j < 8; ++j) v8[j] = bf16_round(v8[j]) + b8[j];
+                                    if (EPI == EPI_BIAS_GELU) {
+#pragma unroll
+                                        for (int j = 0; j < 8; ++j) v8[j] = gelu_of(bf16_round(v8[j]), g.scale != 0.f);
+                                    }
+                                }
+                                uint4 o;
+                                o.x = pack_bf16x2(v8[0], v8[1]); o.y = pack_bf16x2(v8[2], v8[3]);
+                                o.z = pack_bf16x2(v8[4], v8[5]); o.w = pack_bf16x2(v8[6], v8[7]);
+                                *reinterpret_cast<uint4*>(g.out + (size_t)row * g.ldo + col + c8 * 8) = o;
+                            }
+                        }
+                    } else if (row_ok) {
                         const size_t ocol = g.o_cb ? (size_t)(col / g.o_cb) * g.o_cb_stride + (col % g.o_cb)
                                                    : (size_t)col;
                         float v[32];
 #pragma unroll
                         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-                        if (EPI == EPI_BIAS) {
+                        if (EPI == EPI_BIAS || EPI == EPI_BIAS_GELU) {
                             float b[32];
                             load32_bf16(g.bias + col, b);
 #pragma unroll
                             for (int j = 0; j < 32; ++j) v[j] = bf16_round(v[j]) + b[j];
+                            if (EPI == EPI_BIAS_GELU) {
+#pragma unroll
+                                for (int j = 0; j < 32; ++j) v[j] = gelu_of(bf16_round(v[j]), g.scale != 0.f);
+                            }
                         } else if (EPI == EPI_RESID) {
                             float b[32];
                             load32_bf16(g.resid + (size_t)row * g.ldr + col, b);
@@ -547,7 +583,7 @@ static bool launch_tc(const CUtensorMap* tA, const CUtensorMap* tB, const CUtens
     const int tiles = g.num_m * g.num_n;
     int grid = sm_count();
     if (grid > tiles) grid = tiles;
-    prof_before(EPI == EPI_QKNORM ? (int)EPI_STORE : EPI, 2.0 * g.M * (double)g.N * g.K * (EPI == EPI_SWIGLU ? 2.0 : 1.0), st);
+    prof_before(EPI == EPI_QKNORM ? (int)EPI_STORE : (EPI == EPI_BIAS_GELU ? (int)EPI_BIAS : EPI), 2.0 * g.M * (double)g.N * g.K * (EPI == EPI_SWIGLU ? 2.0 : 1.0), st);
     kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, st>>>(*tA, *tB, *tB2, g);
     prof_after(st);
     cudaError_t e = cudaGetLastError();
@@ -556,9 +592,13 @@ static bool launch_tc(const CUtensorMap* tA, const CUtensorMap* tB, const CUtens
 }
 
 bool gemm_tc_supported(int M, int N, int K, int epi) {
-    if (M < 8 || (K % BK) != 0) return false;   // tiny M (timestep MLP, M = 1) is a GEMV: SIMT path
-    if (epi == EPI_SWIGLU) return (N % 128) == 0;  // N = ff columns of each of gate/up
-    return (N % 128) == 0;
+    // tiny M (timestep MLP, M = 1) is a GEMV: SIMT path.  K only has to keep the rows 16-byte aligned for TMA
+    // (the last K block may be ragged: both operands are zero-filled beyond K).
+    if (M < 8 || (K % 8) != 0) return false;
+    // a ragged right edge (N % 128 != 0, e.g. the 4304-wide MLP of the vision tower) is covered by the plain,
+    // bias and bias+GELU epilogues, in steps of eight columns
+    if (epi == EPI_STORE || epi == EPI_BIAS || epi == EPI_BIAS_GELU) return (N % 8) == 0;
+    return (N % 128) == 0;   // EPI_SWIGLU: N = ff columns of each of gate / up
 }
 
 // epi: see Epi.  For EPI_SWIGLU, w = gate weight, w2 = up weight, N = ff.
@@ -603,6 +643,10 @@ bool gemm_bf16_ex(const void* x, int ldx, const void* w, const void* w2, void* y
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) { set_error("gemm(simt): launch: %s", cudaGetErrorString(e)); return false; }
         return true;
+    }
+    if ((N % 128) != 0 && ((ldy % 8) != 0 || (((uintptr_t)y) & 15) || (bias && (((uintptr_t)bias) & 15)))) {
+        set_error("gemm: a ragged N needs 16-byte aligned output rows and bias");
+        return false;
     }
     GemmArgs g;
     g.M = M; g.N = N; g.K = K;
@@ -665,7 +709,7 @@ bool gemm_bf16_ex(const void* x, int ldx, const void* w, const void* w2, void* y
         }
         bn = force_bn;
     }
-    g.num_n = N / bn;
+    g.num_n = (N + bn - 1) / bn;
     if (bn == 256) {
         switch (epi) {
             case EPI_STORE: return launch_tc<EPI_STORE, 256>(tA, tB, tB2, g, st);
@@ -673,6 +717,7 @@ bool gemm_bf16_ex(const void* x, int ldx, const void* w, const void* w2, void* y
             case EPI_RESID: return launch_tc<EPI_RESID, 256>(tA, tB, tB2, g, st);
             case EPI_LORA:  return launch_tc<EPI_LORA, 256>(tA, tB, tB2, g, st);
             case EPI_QKNORM: return launch_tc<EPI_QKNORM, 256>(tA, tB, tB2, g, st);
+            case EPI_BIAS_GELU: return launch_tc<EPI_BIAS_GELU, 256>(tA, tB, tB2, g, st);
         }
     } else {
         switch (epi) {
@@ -681,6 +726,7 @@ bool gemm_bf16_ex(const void* x, int ldx, const void* w, const void* w2, void* y
             case EPI_RESID: return launch_tc<EPI_RESID, 128>(tA, tB, tB2, g, st);
             case EPI_LORA:  return launch_tc<EPI_LORA, 128>(tA, tB, tB2, g, st);
             case EPI_QKNORM: return launch_tc<EPI_QKNORM, 128>(tA, tB, tB2, g, st);
+            case EPI_BIAS_GELU: return launch_tc<EPI_BIAS_GELU, 128>(tA, tB, tB2, g, st);
         }
     }
     set_error("gemm: unknown epilogue %d", epi);

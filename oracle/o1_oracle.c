@@ -846,3 +846,193 @@ ORC_API void orc_prefix_causal_mask(int S, int ar_len, uint16_t *mask /* [S,S] *
     for (int r = 0; r < S; ++r)
         for (int c = 0; c < S; ++c) mask[(size_t)r * S + c] = (r < ar_len && c > r) ? 0xFF7Fu : 0u;
 }
+
+/* ====================================================================== vision tower
+ * Qwen3-VL ViT of the edit modes, src/model/vision.c:345-650 with the kernels of
+ * src/cuda/vision_kernels.cu.  Tokens are in the processor's 2x2 block-major order. */
+
+/* vision_kernels.cu:50-87: fp32 sum and sum of squares, var = E[x^2] - mean^2,
+ * y = bf16((x - mean) * rsqrt(var + eps) * w + b) */
+ORC_API void orc_layernorm(const uint16_t *x, const uint16_t *w, const uint16_t *b, uint16_t *y, int rows,
+                           int cols, float eps) {
+#pragma omp parallel for schedule(static)
+    for (int r = 0; r < rows; ++r) {
+        const uint16_t *xr = x + (size_t)r * cols;
+        uint16_t *yr = y + (size_t)r * cols;
+        float s = 0.f, ss = 0.f;
+        for (int i = 0; i < cols; ++i) {
+            const float v = bf2f(xr[i]);
+            s += v;
+            ss += v * v;
+        }
+        const float inv = 1.0f / (float)cols;
+        const float mean = s * inv;
+        const float var = ss * inv - mean * mean;
+        const float inv_std = 1.0f / sqrtf(var + eps);
+        for (int i = 0; i < cols; ++i) {
+            const float v = (bf2f(xr[i]) - mean) * inv_std;
+            yr[i] = f2bf(v * bf2f(w[i]) + (b ? bf2f(b[i]) : 0.0f));
+        }
+    }
+}
+
+/* vision_kernels.cu:100-133: exact = 0 tanh form (block MLP), 1 erf form (mergers) */
+ORC_API void orc_gelu(const uint16_t *x, uint16_t *y, size_t n, int exact) {
+#pragma omp parallel for schedule(static)
+    for (size_t i = 0; i < n; ++i) {
+        const float v = bf2f(x[i]);
+        float r;
+        if (exact) {
+            r = 0.5f * v * (1.0f + erff(v * 0.7071067811865476f));
+        } else {
+            const float g = 0.7978845608028654f * (v + 0.044715f * v * v * v);
+            r = 0.5f * v * (1.0f + tanhf(g));
+        }
+        y[i] = f2bf(r);
+    }
+}
+
+/* src/cuda/rope.cu:155-178 (hd_apply_rotary_f32): fp32 rotation, one bf16 rounding.
+ * x, y [heads, seq, dim]; cos / sin [seq, dim]. */
+ORC_API void orc_apply_rotary_f32(const uint16_t *x, const float *cosd, const float *sind, uint16_t *y, int heads,
+                                  int seq, int dim) {
+    const int half = dim / 2;
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int h = 0; h < heads; ++h)
+        for (int s = 0; s < seq; ++s) {
+            const uint16_t *xr = x + ((size_t)h * seq + s) * dim;
+            uint16_t *yr = y + ((size_t)h * seq + s) * dim;
+            for (int d = 0; d < dim; ++d) {
+                const float x0 = bf2f(xr[d]);
+                const float xh = bf2f(xr[d < half ? d + half : d - half]);
+                const float c = cosd[(size_t)s * dim + d], sn = sind[(size_t)s * dim + d];
+                yr[d] = f2bf(d < half ? x0 * c - xh * sn : x0 * c + xh * sn);
+            }
+        }
+}
+
+/* Host tables of vision.c:215-280 and :324-328 for an image of grid_h x grid_w patches:
+ * idx / wgt [4, n] (bilinear corners in the 48 x 48 learned grid), coords [2, n] (row, col), inv_freq [18]. */
+ORC_API void orc_vision_tables(int grid_h, int grid_w, int *idx, float *wgt, int *coords, float *inv_freq) {
+    const int side = 48, mw = grid_w / 2, n = grid_h * grid_w;
+    for (int r = 0; r < n; ++r) {
+        const int blk = r / 4, in = r % 4;
+        const int h = (blk / mw) * 2 + in / 2, w = (blk % mw) * 2 + in % 2;
+        const float hf = (float)h * (float)(side - 1) / (float)(grid_h - 1);
+        const float wf = (float)w * (float)(side - 1) / (float)(grid_w - 1);
+        const int h0 = (int)hf, w0 = (int)wf;
+        const int h1 = h0 + 1 < side ? h0 + 1 : side - 1, w1 = w0 + 1 < side ? w0 + 1 : side - 1;
+        const float dh = hf - (float)h0, dw = wf - (float)w0;
+        idx[r] = h0 * side + w0;
+        idx[n + r] = h0 * side + w1;
+        idx[2 * n + r] = h1 * side + w0;
+        idx[3 * n + r] = h1 * side + w1;
+        wgt[r] = (1.0f - dh) * (1.0f - dw);
+        wgt[n + r] = (1.0f - dh) * dw;
+        wgt[2 * n + r] = dh * (1.0f - dw);
+        wgt[3 * n + r] = dh * dw;
+        coords[r] = h;
+        coords[n + r] = w;
+    }
+    for (int k = 0; k < 18; ++k) inv_freq[k] = 1.0f / powf(10000.0f, (float)(2 * k) / 36.0f);
+}
+
+/* Whole tower.  w: the 351 tensors in the order of hd_vision_binding (vision.h:102-109): patch_proj w, b,
+ * pos_embed, 27 x {norm1 w b, norm2 w b, qkv w b, proj w b, fc1 w b, fc2 w b}, merger {norm w b, fc1 w b,
+ * fc2 w b}, 3 x DeepStack merger.  pixels [n,1536]; image_embeds [n/4,4096]; deepstack NULL or [3][n/4,4096];
+ * block_out NULL or [27][n,1152] (every block's output).  Returns 0, or -1 on bad arguments / allocation. */
+ORC_API int orc_vision_forward(const uint16_t *const *w, const uint16_t *pixels, int grid_h, int grid_w,
+                               uint16_t *image_embeds, uint16_t *deepstack, uint16_t *block_out) {
+    enum { H = 1152, HD = 16, D = 72, I = 4304, O = 4096, PD = 1536, MG = 4608, DEPTH = 27 };
+    if (!w || !pixels || !image_embeds || grid_h <= 0 || grid_w <= 0 || grid_h % 2 || grid_w % 2) return -1;
+    const int n = grid_h * grid_w, m = n / 4;
+    const float eps = 1e-6f, scaling = (float)(1.0 / sqrt((double)D));
+    const size_t nH = (size_t)n * H;
+    int *idx = (int *)malloc((size_t)n * 4 * sizeof(int)), *coords = (int *)malloc((size_t)n * 2 * sizeof(int));
+    float *wgt = (float *)malloc((size_t)n * 4 * sizeof(float)), inv_freq[18];
+    float *cs = (float *)malloc((size_t)n * D * sizeof(float)), *sn = (float *)malloc((size_t)n * D * sizeof(float));
+    uint16_t *buf = (uint16_t *)malloc((nH * 8 + (size_t)n * 3 * H + nH * 5 + (size_t)n * I + (size_t)m * MG * 2) * 2);
+    if (!idx || !coords || !wgt || !cs || !sn || !buf) { free(idx); free(coords); free(wgt); free(cs); free(sn); free(buf); return -1; }
+    uint16_t *p = buf;
+    uint16_t *cur = p; p += nH;
+    uint16_t *pos = p; p += nH;
+    uint16_t *ln = p; p += nH;
+    uint16_t *att = p; p += nH;
+    uint16_t *ares = p; p += nH;
+    uint16_t *ln2 = p; p += nH;
+    uint16_t *f2 = p; p += nH;
+    uint16_t *tmp = p; p += nH;
+    uint16_t *qkv = p; p += (size_t)n * 3 * H;
+    uint16_t *q = p; p += nH;
+    uint16_t *k = p; p += nH;
+    uint16_t *v = p; p += nH;
+    uint16_t *qr = p; p += nH;
+    uint16_t *kr = p; p += nH;
+    uint16_t *f1 = p; p += (size_t)n * I;
+    uint16_t *mn = p; p += (size_t)m * MG;
+    uint16_t *mf = p; p += (size_t)m * MG;
+    orc_vision_tables(grid_h, grid_w, idx, wgt, coords, inv_freq);
+
+    /* patch embedding, vision_kernels.cu:16-31 (default path): bf16(acc + bias), one rounding */
+#pragma omp parallel for schedule(static)
+    for (int r = 0; r < n; ++r)
+        for (int c = 0; c < H; ++c) {
+            float acc = 0.f;
+            for (int kk = 0; kk < PD; ++kk) acc += bf2f(pixels[(size_t)r * PD + kk]) * bf2f(w[0][(size_t)c * PD + kk]);
+            tmp[(size_t)r * H + c] = f2bf(acc + bf2f(w[1][c]));
+        }
+    /* interpolated position embedding :148-168, then hidden = bf16(patch + pos) (vision.c:439) */
+    for (int r = 0; r < n; ++r)
+        for (int c = 0; c < H; ++c) {
+            float acc = 0.f;
+            for (int kk = 0; kk < 4; ++kk) acc += wgt[(size_t)kk * n + r] * bf2f(w[2][(size_t)idx[(size_t)kk * n + r] * H + c]);
+            pos[(size_t)r * H + c] = f2bf(acc);
+        }
+    orc_residual_add(tmp, pos, cur, nH);
+    /* rotary tables :183-231: angle = bf16(inv_freq * coord), emb = [rowf | colf | rowf | colf] */
+    for (int r = 0; r < n; ++r)
+        for (int kk = 0; kk < 36; ++kk) {
+            const float a = bfr(inv_freq[kk % 18] * (float)(kk < 18 ? coords[r] : coords[n + r]));
+            cs[(size_t)r * D + kk] = cs[(size_t)r * D + 36 + kk] = cosf(a);
+            sn[(size_t)r * D + kk] = sn[(size_t)r * D + 36 + kk] = sinf(a);
+        }
+
+    const uint16_t *const *bw = w + 3;
+    for (int i = 0; i < DEPTH; ++i, bw += 12) {
+        orc_layernorm(cur, bw[0], bw[1], ln, n, H, eps);                       /* vision.c:465 */
+        orc_linear(ln, bw[4], bw[5], qkv, n, 3 * H, H);                        /* :469 */
+        for (int h = 0; h < HD; ++h)                                           /* :473, vision_kernels.cu:283-302 */
+            for (int s = 0; s < n; ++s)
+                for (int d = 0; d < D; ++d) {
+                    const size_t dst = ((size_t)h * n + s) * D + d, src = (size_t)s * 3 * H + (size_t)h * D + d;
+                    q[dst] = qkv[src];
+                    k[dst] = qkv[src + H];
+                    v[dst] = qkv[src + 2 * H];
+                }
+        orc_apply_rotary_f32(q, cs, sn, qr, HD, n, D);                         /* :475-476 */
+        orc_apply_rotary_f32(k, cs, sn, kr, HD, n, D);
+        orc_attention(qr, kr, v, att, HD, HD, n, D, scaling, 0);               /* :500 (zero mask: full attention) */
+        orc_linear(att, bw[6], bw[7], tmp, n, H, H);                           /* :506 */
+        orc_residual_add(cur, tmp, ares, nH);                                  /* :508 */
+        orc_layernorm(ares, bw[2], bw[3], ln2, n, H, eps);                     /* :512 */
+        orc_linear(ln2, bw[8], bw[9], f1, n, I, H);                            /* :516 */
+        orc_gelu(f1, f1, (size_t)n * I, 0);                                    /* :522 */
+        orc_linear(f1, bw[10], bw[11], f2, n, H, I);                           /* :525 */
+        orc_residual_add(ares, f2, cur, nH);                                   /* :527 */
+        if (block_out) memcpy(block_out + (size_t)i * nH, cur, nH * 2);
+        if (deepstack && (i == 8 || i == 16 || i == 24)) {                     /* :562-596 */
+            const uint16_t *const *ds = w + 3 + 12 * DEPTH + 6 + 6 * (i / 8 - 1);
+            orc_layernorm(cur, ds[0], ds[1], mn, m, MG, eps);
+            orc_linear(mn, ds[2], ds[3], mf, m, MG, MG);
+            orc_gelu(mf, mf, (size_t)m * MG, 1);
+            orc_linear(mf, ds[4], ds[5], deepstack + (size_t)(i / 8 - 1) * m * O, m, O, MG);
+        }
+    }
+    const uint16_t *const *mg = w + 3 + 12 * DEPTH;                            /* :617-645 */
+    orc_layernorm(cur, mg[0], mg[1], mn, n, H, eps);
+    orc_linear(mn, mg[2], mg[3], mf, m, MG, MG);
+    orc_gelu(mf, mf, (size_t)m * MG, 1);
+    orc_linear(mf, mg[4], mg[5], image_embeds, m, O, MG);
+    free(idx); free(coords); free(wgt); free(cs); free(sn); free(buf);
+    return 0;
+}
