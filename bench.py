@@ -5,7 +5,7 @@ Metric: seconds per image for 28-step CFG text-to-image at 16384 image tokens
 (+256 text tokens, 36 decoder blocks).  A "step" here is one denoise step: cond forward, uncond
 forward, fused CFG + flow-match scheduler update.  sec/image = 28 x mean step time.
 
-  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c0|c1|c2|c3|c4]
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c0|c1|c2|c3|c4|vision|vision64]
                   [--exchange direct|nccl]
 
 Prints ONE JSON line (rank 0): value = s/image from CUDA-event step times with the latent resident on the
@@ -544,13 +544,116 @@ def run_reference(args):
     return base
 
 
+# --------------------------------------------------------------------------------------- vision tower
+VISION_GRIDS = {"vision": (26, 20), "vision64": (64, 64)}   # patches: the documented 416 x 320 image; 1024 x 1024
+
+
+def run_vision(args):
+    """Times hd_vision_forward (27-block ViT of the edit modes) on one GPU: plain launches and CUDA-graph replay,
+    next to the reference's CUDA build (cuBLASLt hd_linear + its eager attention) when oracle/_ref holds it."""
+    import torch
+    from __graft_entry__ import load_package
+    import parity
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    pkg = load_package()
+    pkg.use_torch_stream()
+    lib = pkg.lib
+    gh, gw = VISION_GRIDS[args.workload]
+    n, m = gh * gw, gh * gw // 4
+    tensors = []
+    for i, (name, shape) in enumerate(parity.vision_tensor_list()):
+        t = torch.empty(shape, dtype=torch.bfloat16, device=dev)
+        mean = 1.0 if name.endswith(("norm1.weight", "norm2.weight", "norm.weight")) else 0.0
+        assert lib.o1_fill_normal_bf16(pkg.ptr(t), t.numel(), 4321 + i, mean, 0.02) == 0
+        tensors.append(t)
+    binding = pkg.VisionBinding(*[t.data_ptr() for t in tensors])
+    px = torch.empty((n, 1536), dtype=torch.bfloat16, device=dev)
+    lib.o1_fill_normal_bf16(pkg.ptr(px), px.numel(), 7, 0.0, 1.0)
+    emb = torch.empty((m, 4096), dtype=torch.bfloat16, device=dev)
+    ds = torch.empty((3, m, 4096), dtype=torch.bfloat16, device=dev)
+    dsp = (C.c_void_p * 3)(*[ds[j].data_ptr() for j in range(3)])
+
+    def make_ws(l):
+        ws = pkg.VisionWorkspace()
+        space = torch.zeros(l.hd_vision_workspace_bytes(n), dtype=torch.uint8, device=dev)
+        tables = torch.zeros(l.hd_vision_tables_bytes(n), dtype=torch.uint8, device=dev)
+        ws.patch_out, ws.tables, ws.tables_n = space.data_ptr(), tables.data_ptr(), -1
+        assert l.hd_vision_prepare_tables(C.byref(ws), n, gh, gw) == 0
+        return ws, (space, tables)
+
+    def forward(l, ws):
+        rc = l.hd_vision_forward(C.byref(binding), C.byref(ws), C.c_void_p(px.data_ptr()), n, gh, gw,
+                                 C.c_void_p(emb.data_ptr()), C.byref(dsp))
+        assert rc == 0, l.hd_last_error()
+
+    def timed(fn, reps):
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(reps + 1)]
+        torch.cuda.synchronize()
+        ev[0].record()
+        for i in range(reps):
+            fn()
+            ev[i + 1].record()
+        torch.cuda.synchronize()
+        return statistics.median(ev[i].elapsed_time(ev[i + 1]) for i in range(reps))
+
+    ws, keep = make_ws(lib)
+    reps = args.steps if args.short else max(args.steps, 10)
+    for _ in range(args.warmup if args.short else max(args.warmup, 3)):
+        forward(lib, ws)
+    lib.o1_launch_count(1)
+    forward(lib, ws)
+    launches = int(lib.o1_launch_count(1))
+    ms_plain = timed(lambda: forward(lib, ws), reps)
+    if args.short:      # profiler runs: plain launches only, no graph, no reference arm; not a benchmark value
+        return {"metric": "vision tower ms/forward", "value": round(ms_plain, 4), "unit": "ms", "short": True,
+                "gpu_launches": launches}
+    # the forward neither allocates nor synchronises, so it can be captured once and replayed
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        pkg.use_torch_stream()
+        forward(lib, ws)
+        side.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            pkg.use_torch_stream()
+            forward(lib, ws)
+    pkg.use_torch_stream()
+    ms_graph = timed(graph.replay, reps)
+    assert lib.o1_device_error() == 0
+    # algorithmic FLOPs: block GEMMs, attention at head_dim 72, patch embedding, four mergers
+    gemm = 2.0 * n * (1152 * 3456 + 1152 * 1152 + 2 * 1152 * 4304) * 27 + 2.0 * n * 1536 * 1152
+    attn = 4.0 * 16 * 72 * n * n * 27
+    merg = 4 * 2.0 * m * (4608 * 4608 + 4096 * 4608)
+    flops = gemm + attn + merg
+    out = {"metric": "vision tower ms/forward", "value": round(ms_graph, 4), "unit": "ms", "n_gpus": 1, "steps": reps,
+           "warmup": max(args.warmup, 3), "higher_is_better": False, "dtype": "bf16", "data": "synthetic",
+           "config": {"workload": f"{args.workload}: Qwen3-VL tower, {gh}x{gw} patches ({n} tokens -> {m} merged), 27 blocks, "
+                                  "random-init weights seed 4321", "mode": "CUDA-graph replay of hd_vision_forward"},
+           "ms_plain_launches": round(ms_plain, 4), "gpu_launches": launches,
+           "model_gflops_per_forward": round(flops / 1e9, 1), "achieved_tflops": round(flops / ms_graph / 1e9, 1)}
+    r = parity.reflib()
+    if r is not None and hasattr(r, "hd_vision_forward"):
+        rt = r.hd_gemm_runtime_init(0, 64 << 20)
+        if rt:
+            r.hd_gemm_set_backend(1)
+            rws, rkeep = make_ws(r)
+            for _ in range(3):
+                forward(r, rws)
+            out["reference_cuda_build_ms"] = round(timed(lambda: forward(r, rws), reps), 4)
+            out["reference_backend"] = "cuBLASLt hd_linear + the reference's eager attention (sdpa = NULL)"
+            r.hd_gemm_runtime_destroy(rt)
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + sorted(VISION_GRIDS))
     ap.add_argument("--layers", type=int, default=36)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--exchange", choices=("direct", "nccl"), default="direct",
@@ -560,7 +663,10 @@ def main():
                     help="profiler runs only: take --warmup literally, skip the end-to-end and CPU legs "
                          "(a number from such a run is not a benchmark value)")
     args = ap.parse_args()
-    out = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if args.workload in VISION_GRIDS:
+        out = run_vision(args)     # one GPU, both arms in one line
+    else:
+        out = run_reference(args) if args.impl == "reference" else run_ours(args)
     if out is not None:
         print(json.dumps(out), flush=True)
 
