@@ -450,7 +450,8 @@ int64_t o1_launch_count(int reset);
 
 /* Tensor-core GEMM with a choice of fused epilogue and explicit row pitches.
  * epi: 0 store, 1 +bias, 2 +residual, 3 SwiGLU (w = gate, w2 = up, N = ff),
- * 4 LoRA read-modify-write, 7 +bias then GELU (tanh form when scale == 0, erf form otherwise).
+ * 4 LoRA read-modify-write, 7 +bias then GELU (tanh form when scale == 0, erf form otherwise), 8 +bias then
+ * +residual (bf16(resid + bf16(bf16(acc) + bias))).
  * force_bn: 0 auto, 128 or 256.  Shapes: M >= 8 and K % 8 == 0 run on the tensor cores (a ragged last K block
  * is zero-filled); epilogues 0, 1, 7 accept any N % 8 == 0 (ragged right tile edge), the others N % 128 == 0;
  * anything else runs a SIMT kernel (epilogues 0 and 1 only).  Returns 0 on success. */

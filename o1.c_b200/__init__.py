@@ -258,7 +258,7 @@ _sig("o1_denoise_step_cfg_host", c_int, C.POINTER(ForwardBinding), C.POINTER(For
      _P, c_int, _P, c_int, _P, _P, c_int, c_float, c_float, c_float, _P, _P, _P, _P, c_int, c_int,
      c_int, c_int, c_int, c_int)
 
-EPI_STORE, EPI_BIAS, EPI_RESID, EPI_SWIGLU, EPI_LORA, EPI_BIAS_GELU = 0, 1, 2, 3, 4, 7
+EPI_STORE, EPI_BIAS, EPI_RESID, EPI_SWIGLU, EPI_LORA, EPI_BIAS_GELU, EPI_BIAS_RESID = 0, 1, 2, 3, 4, 7, 8
 
 
 class O1Error(RuntimeError):

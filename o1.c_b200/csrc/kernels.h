@@ -11,7 +11,9 @@ namespace o1 {
 // EPI_QKNORM: per-head RMSNorm + rotary of a q / k projection inside the GEMM epilogue (every 128 output columns
 // are one head; `bias` carries the norm weight [128], `resid` the fp32 cos|sin table [M,128], `scale` the epsilon)
 // EPI_BIAS_GELU: bf16(gelu(bf16(bf16(acc) + bias))), tanh form when `scale` == 0, erf form otherwise (vision tower)
-enum Epi { EPI_STORE = 0, EPI_BIAS = 1, EPI_RESID = 2, EPI_SWIGLU = 3, EPI_LORA = 4, EPI_QKNORM = 6, EPI_BIAS_GELU = 7 };
+// EPI_BIAS_RESID: bf16(resid + bf16(bf16(acc) + bias)): a biased projection followed by the residual add
+enum Epi { EPI_STORE = 0, EPI_BIAS = 1, EPI_RESID = 2, EPI_SWIGLU = 3, EPI_LORA = 4, EPI_QKNORM = 6, EPI_BIAS_GELU = 7,
+           EPI_BIAS_RESID = 8 };
 
 // ---- engine.cu: optional per-launch event timing of the tensor-core kernels.
 // kind: 0..4 = GEMM by epilogue (Epi), 5 = flash attention.  Costs two event

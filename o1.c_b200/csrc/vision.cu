@@ -579,20 +579,31 @@ hd_status hd_vision_forward(const hd_vision_binding* bw, hd_vision_workspace* ws
             unpad_heads_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(attn_pad, attn_out, n);
         }
         VIS_TRY(cudaGetLastError() == cudaSuccess);
-        VIS_TRY(linear_act(attn_out, blk->proj_w, blk->proj_b, attn_resid, n, V_H, V_H, 0, st, &launches));
-        if (s0) VIS_TRY(snap(s0[HD_B0_PROJ], attn_resid, nH, st));
-        VIS_TRY(residual_add(cur_in, attn_resid, attn_resid, (size_t)n * V_H, st));
+        // the two residual adds ride in the projections' epilogues unless a snapshot asks for the bare projection
+        // (or the row count is below the tensor-core tile minimum)
+        const bool fuse = gemm_tc_supported(n, V_H, V_H, EPI_BIAS_RESID) && !(s0 && (s0[HD_B0_PROJ] || s0[HD_B0_FC2]));
+        if (fuse) {
+            VIS_TRY(gemm_bf16(attn_out, blk->proj_w, nullptr, attn_resid, n, V_H, V_H, EPI_BIAS_RESID, blk->proj_b, cur_in, 0.f, 0, st));
+        } else {
+            VIS_TRY(linear_act(attn_out, blk->proj_w, blk->proj_b, attn_resid, n, V_H, V_H, 0, st, &launches));
+            if (s0) VIS_TRY(snap(s0[HD_B0_PROJ], attn_resid, nH, st));
+            VIS_TRY(residual_add(cur_in, attn_resid, attn_resid, (size_t)n * V_H, st));
+        }
         VIS_TRY(vision_layernorm(attn_resid, blk->norm2_w, blk->norm2_b, ln2, n, V_H, eps, st));
         VIS_TRY(linear_act(ln2, blk->fc1_w, blk->fc1_b, fc1, n, V_I, V_H, 1, st, &launches));
-        VIS_TRY(linear_act(fc1, blk->fc2_w, blk->fc2_b, fc2, n, V_H, V_I, 0, st, &launches));
-        VIS_TRY(residual_add(attn_resid, fc2, cur_out, (size_t)n * V_H, st));
+        if (fuse) {
+            VIS_TRY(gemm_bf16(fc1, blk->fc2_w, nullptr, cur_out, n, V_H, V_I, EPI_BIAS_RESID, blk->fc2_b, attn_resid, 0.f, 0, st));
+        } else {
+            VIS_TRY(linear_act(fc1, blk->fc2_w, blk->fc2_b, fc2, n, V_H, V_I, 0, st, &launches));
+            VIS_TRY(residual_add(attn_resid, fc2, cur_out, (size_t)n * V_H, st));
+        }
         launches += 7;
 
         if (s0) {
             VIS_TRY(snap(s0[HD_B0_INPUT], cur_in, nH, st) && snap(s0[HD_B0_NORM1], ln1, nH, st) &&
                     snap(s0[HD_B0_QKV], qkv, (size_t)n * 3 * V_H * 2, st) && snap(s0[HD_B0_ATTN_MERGED], attn_out, nH, st) &&
                     snap(s0[HD_B0_ATTN_RESID], attn_resid, nH, st) && snap(s0[HD_B0_NORM2], ln2, nH, st) &&
-                    snap(s0[HD_B0_FC2], fc2, nH, st) && snap(s0[HD_B0_OUTPUT], cur_out, nH, st));
+                    (fuse || snap(s0[HD_B0_FC2], fc2, nH, st)) && snap(s0[HD_B0_OUTPUT], cur_out, nH, st));
             VIS_TRY(snap(ws->block0_snap, cur_out, nH, st));
         }
         VIS_TRY(snap(ws->block_out_snaps[i], cur_out, nH, st));

@@ -75,6 +75,21 @@ def test_gemm_bias_gelu_epilogue(pkg, orc, dev, exact):
     assert_close(torch_to_u16(y), ref, "C", "gemm + bias + gelu")
 
 
+@pytest.mark.parametrize("M,N,K", [(520, 1152, 4304), (300, 1152, 1152)])
+def test_gemm_bias_residual_epilogue(pkg, orc, dev, M, N, K):
+    x, w, b = seeded_bf16((M, K), 24), seeded_bf16((N, K), 25, 0.0, 0.05), seeded_bf16(N, 26, 0.0, 0.5)
+    res = seeded_bf16((M, N), 27)
+    y = empty_bf16((M, N), dev)
+    rc = pkg.lib.o1_gemm(pkg.ptr(dv(x, dev)), K, pkg.ptr(dv(w, dev)), None, pkg.ptr(y), N, M, N, K, pkg.EPI_BIAS_RESID,
+                         pkg.ptr(dv(b, dev)), pkg.ptr(dv(res, dev)), N, 0.0, 0)
+    assert rc == 0, pkg.last_error()
+    done(pkg, "gemm+bias+residual")
+    ref = np.empty((M, N), dtype=np.uint16)
+    orc.orc_linear(np_ptr(x), np_ptr(w), np_ptr(b), np_ptr(ref), M, N, K)
+    orc.orc_residual_add(np_ptr(res), np_ptr(ref), np_ptr(ref), ref.size)
+    assert_close(torch_to_u16(y), ref, "C", "gemm + bias + residual")
+
+
 # ------------------------------------------------------------------ stand-alone kernels
 @pytest.mark.parametrize("rows,cols", [(520, 1152), (130, 4608), (7, 96), (3, 100)])
 def test_layernorm(pkg, orc, dev, rows, cols):
@@ -256,3 +271,38 @@ def test_forward_rejects_bad_arguments(pkg, dev, tower):
     # odd grid
     assert pkg.lib.hd_vision_forward(C.byref(binding), C.byref(ws), pkg.ptr(buf), 15, 3, 5, pkg.ptr(out), None) != 0
     assert pkg.lib.hd_vision_forward(None, C.byref(ws), pkg.ptr(buf), 16, 4, 4, pkg.ptr(out), None) != 0
+
+
+def test_edit_pipeline_tower_into_forward(pkg, orc, dev, tower):
+    """The edit path end to end (o1.c src/runtime/generate.c:435-640 then hd_forward): one conditioning image goes
+    through the vision tower, its image_embeds replace the <image_pad> rows of the text and the DeepStack tensors are
+    added after decoder blocks 0..2; the target grid and one reference grid follow.  GPU pipeline against the oracle
+    pipeline (orc_vision_forward -> orc_forward_visual)."""
+    vw, _, binding = tower
+    ch, cw = 4, 6                                           # merged vision tokens: 24 <image_pad> rows
+    px = seeded_bf16((4 * ch * cw, 1536), 17)
+    emb, ds, _ = run_tower(pkg, dev, binding, px, 2 * ch, 2 * cw, snaps=False)
+    text = np.array([9906, 1917, 11, 151652] + [151655] * (ch * cw) + [151653, 151673], dtype=np.int64)
+    refs = [(16, 4, 4, ch, cw)]
+    gh = gw = 8
+    _, pos, ar = pkg.seq_ref(text, refs, gh, gw)
+    T, I = len(text), gh * gw + 16
+    S = T + I
+    L = 4
+    w = pkg.Weights(n_layers=L, seed=1234, weight_set="B", device=dev)
+    eng = pkg.Engine(w, T, I, ar_len=ar)
+    vmask = np.zeros(S, dtype=np.uint8)
+    vmask[:T] = (text == 151655)
+    vin = seeded_bf16((I, 3072), 90)
+    vis = (torch.from_numpy(vmask).to(dev), emb, [ds[k] for k in range(3)])
+    out = eng.forward(torch.from_numpy(text).to(dev), pos.to(dev), u16_to_torch(vin, dev), 0.3, visual=vis)
+    torch.cuda.synchronize()
+    emb_o, ds_o = parity.oracle_vision(vw, px, 2 * ch, 2 * cw)
+    hw = parity.HostWeights(pkg, L, 1234, "B")
+    ref = parity.oracle_forward(hw, text, pos.numpy(), ar, vin, 0.3, visual=(vmask, emb_o, [ds_o[k] for k in range(3)]))
+    print("edit pipeline vs oracle pipeline:", metrics(out, ref)[:2])
+    assert_close(torch_to_u16(out), ref, "V", "tower -> forward")
+    # the tower's outputs reach the prediction
+    out_plain = eng.forward(torch.from_numpy(text).to(dev), pos.to(dev), u16_to_torch(vin, dev), 0.3)
+    torch.cuda.synchronize()
+    assert metrics(out_plain, out)[0] > 1e-2
