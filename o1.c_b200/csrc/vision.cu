@@ -8,9 +8,9 @@
 //   rotary table           one kernel: bf16(inv_freq * coord) -> cos|sin [n,72]     (vision.c:444-446)
 //   27 x block             LayerNorm -> qkv GEMM+bias -> split + fp32 rotary into 128-wide zero-padded heads
 //                          -> flash attention (head_dim 72 runs as 128: the pad columns add 0 to every
-//                          score and produce 0 output columns) -> compact -> proj GEMM+bias -> +residual
+//                          score and produce 0 output columns) -> compact -> proj GEMM+bias+residual
 //                          -> LayerNorm -> fc1 GEMM+bias+GELU(tanh) (N = 4304, ragged tile edge)
-//                          -> fc2 GEMM+bias (K = 4304, ragged last K block) -> +residual
+//                          -> fc2 GEMM+bias+residual (K = 4304, ragged last K block)
 //   DeepStack mergers      after blocks 8 / 16 / 24: LayerNorm over 4608 -> GEMM+bias+GELU(erf) -> GEMM+bias
 //   final merger           LayerNorm over 1152 -> view [n/4, 4608] -> GEMM+bias+GELU(erf) -> GEMM+bias
 //
