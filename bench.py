@@ -5,7 +5,7 @@ Metric: seconds per image for 28-step CFG text-to-image at 16384 image tokens
 (+256 text tokens, 36 decoder blocks).  A "step" here is one denoise step: cond forward, uncond
 forward, fused CFG + flow-match scheduler update.  sec/image = 28 x mean step time.
 
-  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c0|c1|c2|c3|c4|vision|vision64]
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c0|c1|c2|c3|c4|vision|vision64|elementwise]
                   [--exchange direct|nccl]
 
 Prints ONE JSON line (rank 0): value = s/image from CUDA-event step times with the latent resident on the
@@ -647,13 +647,80 @@ def run_vision(args):
     return out
 
 
+# --------------------------------------------------------------------------------------- elementwise kernels
+def run_elementwise(args):
+    """HBM-bound kernels of the path at the c2 shapes (S = 16640), each timed alone with CUDA events against the
+    measured copy bandwidth.  Every kernel cycles through four sets of buffers (> 1 GB in total) so that no launch
+    finds its operands in the 126 MB L2."""
+    import torch
+    from __graft_entry__ import load_package
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    pkg = load_package()
+    pkg.use_torch_stream()
+    lib = pkg.lib
+    S, H, NB = 16640, 4096, (1 if args.short else 4)     # profiler runs hold one buffer set (1.3 GB)
+    _, _, hbm, src = measured_peaks()
+    bf = lambda *shape: [torch.randn(*shape, device=dev, dtype=torch.float32).to(torch.bfloat16) for _ in range(NB)]
+    x, y, x2 = bf(S, H), bf(S, H), bf(S, H)
+    w = torch.ones(H, dtype=torch.bfloat16, device=dev)
+    lb = torch.zeros(H, dtype=torch.bfloat16, device=dev)
+    qk = bf(S, 40 * 128)                                       # 32 q heads + 8 k heads of one token row
+    w128 = torch.ones(128, dtype=torch.bfloat16, device=dev)
+    pos, _ = pkg.seq_t2i(256, 128, 128)
+    cs = torch.empty(S, 128, dtype=torch.float32, device=dev)
+    assert lib.o1_mrope_table(pkg.ptr(pos.to(dev)), S, 5000000.0, pkg.ptr(cs)) == 0
+    n_lat = 16384 * 3072
+    z, xc, xu, zn = bf(n_lat), bf(n_lat), bf(n_lat), bf(n_lat)
+    g, u, sw = bf(S, 12288 // 4), bf(S, 12288 // 4), bf(S, 12288 // 4)   # a quarter of the SwiGLU width keeps the set at 1.2 GB
+    P = pkg.ptr
+    cases = [
+        ("rmsnorm_vec_kernel [16640,4096]", 2 * S * H * 2 + H * 2,
+         lambda i: lib.hd_rmsnorm(P(x[i]), P(w), P(y[i]), S, H, 1e-6)),
+        ("qk_norm_rope_kernel 40 heads x 128", 2 * S * 40 * 128 * 2 + S * 512,
+         lambda i: lib.o1_qk_norm_rope(P(qk[i]), 40 * 128, S, 40, P(w128), P(cs), 1e-6)),
+        ("pointwise residual add [16640,4096]", 3 * S * H * 2,
+         lambda i: lib.hd_residual_add(P(x[i]), P(x2[i]), P(y[i]), S * H)),
+        ("pointwise SwiGLU [16640,3072]", 3 * S * 3072 * 2,
+         lambda i: lib.hd_swiglu(P(g[i]), P(u[i]), P(sw[i]), S * 3072)),
+        ("cfg_flow_step_kernel 50.3 M elements", 4 * n_lat * 2,
+         lambda i: lib.o1_sched_cfg_flow_step(P(z[i]), P(xc[i]), P(xu[i]), 0.7, 0.65, 5.0, P(zn[i]), n_lat)),
+        ("layernorm_kernel [16640,1152] (vision)", 2 * S * 1152 * 2,
+         lambda i: lib.hd_vision_layernorm(P(x[i]), P(w), P(lb), P(y[i]), S, 1152, 1e-6)),
+    ]
+    reps = args.steps if args.short else max(args.steps, 12)
+    rows = {}
+    for name, nbytes, fn in cases:
+        for i in range(args.warmup if args.short else max(args.warmup, 3)):
+            fn(i % NB)
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(reps + 1)]
+        torch.cuda.synchronize()
+        ev[0].record()
+        for i in range(reps):
+            fn(i % NB)
+            ev[i + 1].record()
+        torch.cuda.synchronize()
+        pkg.check_cuda_errbuf(name)
+        us = statistics.median(ev[i].elapsed_time(ev[i + 1]) for i in range(reps)) * 1e3
+        rows[name] = {"us": round(us, 2), "algorithmic_MB": round(nbytes / 1e6, 1), "GBps": round(nbytes / us / 1e3, 1),
+                      "frac_of_hbm_peak": round(nbytes / us / 1e3 / hbm, 3)}
+    top = rows["rmsnorm_vec_kernel [16640,4096]"]
+    return {"metric": "elementwise kernels, achieved HBM GB/s", "value": top["GBps"], "unit": "GB/s", "n_gpus": 1,
+            "steps": reps, "warmup": max(args.warmup, 3), "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "elementwise: c2 shapes (S = 16640), four rotating buffer sets per kernel (no L2 reuse)"},
+            "roofline": {"bound": "hbm", "kernel": "rmsnorm_vec_kernel", "achieved": top["GBps"], "peak": hbm, "unit": "GB/s",
+                         "frac": top["frac_of_hbm_peak"], "traffic": None, "peak_source": src + " (STREAM-style copy)"},
+            "kernels": rows, "gpu_launches": len(cases) * (reps + max(args.warmup, 3))}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + sorted(VISION_GRIDS))
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + sorted(VISION_GRIDS) + ["elementwise"])
     ap.add_argument("--layers", type=int, default=36)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--exchange", choices=("direct", "nccl"), default="direct",
@@ -663,7 +730,9 @@ def main():
                     help="profiler runs only: take --warmup literally, skip the end-to-end and CPU legs "
                          "(a number from such a run is not a benchmark value)")
     args = ap.parse_args()
-    if args.workload in VISION_GRIDS:
+    if args.workload == "elementwise":
+        out = run_elementwise(args)
+    elif args.workload in VISION_GRIDS:
         out = run_vision(args)     # one GPU, both arms in one line
     else:
         out = run_reference(args) if args.impl == "reference" else run_ours(args)

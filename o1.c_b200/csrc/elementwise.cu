@@ -334,14 +334,16 @@ bool apply_rotary(const void* x, const float* cosd, const float* sind, void* y, 
 __global__ void __launch_bounds__(256)
 qk_norm_rope_kernel(uint16_t* __restrict__ x, int ld, int S, int heads, int hpb, long blk_stride,
                     const uint16_t* __restrict__ w, const float* __restrict__ cs, float eps) {
-    // 8 threads per token walk over its heads: the token's cos|sin values and the norm weights are loaded once
-    // and reused for every head (the table row is twice the size of a head, so loading it per head doubled the
-    // traffic of this kernel)
-    const int s = blockIdx.x * 32 + (threadIdx.x >> 3);
-    const int t = threadIdx.x & 7;
-    const bool active = s < S;
+    // One warp per token: lanes = (head within a quad) x 8, so one load instruction of the warp covers the low
+    // halves of four adjacent heads and the next one their high halves -- 1 KB of contiguous memory per quad, and
+    // the warp streams through its token's row.  The token's cos|sin values and the norm weights are loaded once
+    // and reused for every head (the table row is twice the size of a head).
+    const int s = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (s >= S) return;                          // whole warp
+    const int lane = threadIdx.x & 31;
+    const int hq = lane >> 3, t = lane & 7;
     float wl[8], wh[8], cc[8], ss[8];
-    if (active) {
+    {
         unpack8(*reinterpret_cast<const uint4*>(w + 8 * t), wl);
         unpack8(*reinterpret_cast<const uint4*>(w + 64 + 8 * t), wh);
         const float4* c4 = reinterpret_cast<const float4*>(cs + (size_t)s * 128 + 8 * t);
@@ -350,32 +352,46 @@ qk_norm_rope_kernel(uint16_t* __restrict__ x, int ld, int S, int heads, int hpb,
         cc[0] = ca.x; cc[1] = ca.y; cc[2] = ca.z; cc[3] = ca.w; cc[4] = cb.x; cc[5] = cb.y; cc[6] = cb.z; cc[7] = cb.w;
         ss[0] = sa.x; ss[1] = sa.y; ss[2] = sa.z; ss[3] = sa.w; ss[4] = sb.x; ss[5] = sb.y; ss[6] = sb.z; ss[7] = sb.w;
     }
-    for (int h = 0; h < heads; ++h) {
-        uint16_t* base = x + (size_t)(h / hpb) * blk_stride + (size_t)(active ? s : 0) * ld + (h % hpb) * 128;
-        float lo[8], hi[8];
-        float sq = 0.f;
-        if (active) {
-            unpack8(*reinterpret_cast<const uint4*>(base + 8 * t), lo);
-            unpack8(*reinterpret_cast<const uint4*>(base + 64 + 8 * t), hi);
+    // G quads (16 heads) per trip: all 2*G 16-byte loads of a thread are issued before the first value is used
+    constexpr int G = 4;
+    for (int h0 = 0; h0 < heads; h0 += 4 * G) {
+        uint16_t* base[G];
+        uint4 vlo[G], vhi[G];
+        bool on[G];
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            const int h = h0 + 4 * g + hq;
+            on[g] = h < heads;
+            const int hc = on[g] ? h : 0;
+            base[g] = x + (size_t)(hc / hpb) * blk_stride + (size_t)s * ld + (hc % hpb) * 128;
+            vlo[g] = on[g] ? *reinterpret_cast<const uint4*>(base[g] + 8 * t) : make_uint4(0, 0, 0, 0);
+            vhi[g] = on[g] ? *reinterpret_cast<const uint4*>(base[g] + 64 + 8 * t) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            float lo[8], hi[8];
+            float sq = 0.f;
+            unpack8(vlo[g], lo);
+            unpack8(vhi[g], hi);
             // explicit roundings: the fused GEMM epilogue (EPI_QKNORM) sums in exactly this order
 #pragma unroll
             for (int j = 0; j < 8; ++j) sq = __fadd_rn(sq, __fmaf_rn(hi[j], hi[j], __fmul_rn(lo[j], lo[j])));
-        }
-        sq += __shfl_xor_sync(0xffffffffu, sq, 1);
-        sq += __shfl_xor_sync(0xffffffffu, sq, 2);
-        sq += __shfl_xor_sync(0xffffffffu, sq, 4);
-        if (!active) continue;
-        const float inv = rsqrtf(sq / 128.0f + eps);
-        float ol[8], oh[8];
+            sq += __shfl_xor_sync(0xffffffffu, sq, 1);
+            sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+            sq += __shfl_xor_sync(0xffffffffu, sq, 4);
+            if (!on[g]) continue;
+            const float inv = rsqrtf(sq / 128.0f + eps);
+            float ol[8], oh[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const float a = bf16_round(wl[j] * lo[j] * inv);
-            const float b = bf16_round(wh[j] * hi[j] * inv);
-            ol[j] = bf16_round(a * cc[j]) - bf16_round(b * ss[j]);
-            oh[j] = bf16_round(b * cc[j]) + bf16_round(a * ss[j]);
+            for (int j = 0; j < 8; ++j) {
+                const float a = bf16_round(wl[j] * lo[j] * inv);
+                const float b = bf16_round(wh[j] * hi[j] * inv);
+                ol[j] = bf16_round(a * cc[j]) - bf16_round(b * ss[j]);
+                oh[j] = bf16_round(b * cc[j]) + bf16_round(a * ss[j]);
+            }
+            *reinterpret_cast<uint4*>(base[g] + 8 * t) = pack8(ol);
+            *reinterpret_cast<uint4*>(base[g] + 64 + 8 * t) = pack8(oh);
         }
-        *reinterpret_cast<uint4*>(base + 8 * t) = pack8(ol);
-        *reinterpret_cast<uint4*>(base + 64 + 8 * t) = pack8(oh);
     }
 }
 bool qk_norm_rope(void* x, int ld, int S, int heads, const void* w, const float* cs_table, float eps,
@@ -393,7 +409,7 @@ bool qk_norm_rope_blocked(void* x, int ld, int S, int heads, int hpb, long blk_s
         set_error("qk_norm_rope: bad args");
         return false;
     }
-    qk_norm_rope_kernel<<<(unsigned)((S + 31) / 32), 256, 0, st>>>(
+    qk_norm_rope_kernel<<<(unsigned)((S + 7) / 8), 256, 0, st>>>(
         (uint16_t*)x, ld, S, heads, hpb, blk_stride, (const uint16_t*)w, cs_table, eps);
     O1_LAUNCH_CHECK("qk_norm_rope");
     return true;

@@ -35,30 +35,28 @@ namespace o1 {
 static constexpr int V_DEPTH = 27, V_H = 1152, V_HEADS = 16, V_D = 72, V_I = 4304, V_OUT = 4096;
 static constexpr int V_PATCH = 1536, V_NPOS_SIDE = 48, V_MERGED = 4608, V_DP = 128 /* padded head */;
 
-__device__ __forceinline__ float block_sum(float v, float* sh) {
+__device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    const int w = threadIdx.x >> 5, nw = blockDim.x >> 5;
-    __syncthreads();
-    if ((threadIdx.x & 31) == 0) sh[w] = v;
-    __syncthreads();
-    float t = 0.f;
-    for (int i = 0; i < nw; ++i) t += sh[i];
-    return t;
+    return v;
 }
 
 // LayerNorm over the last dimension, bf16 in / out, fp32 statistics as vision_kernels.cu:50-87:
 // mean = sum/cols, var = sum(x^2)/cols - mean^2, y = bf16((x - mean) * rsqrt(var + eps) * w + b).
-// One CTA per row; the second pass re-reads the row from L1/L2.  cols % 8 == 0 takes 128-bit accesses.
-__global__ void __launch_bounds__(128)
+// One warp per row (rows are 2.3 - 9 KB: shuffles only, no block barrier); the second pass re-reads the row
+// from L1.  cols % 8 == 0 takes 128-bit accesses.
+static constexpr int LN_WARPS = 4;
+__global__ void __launch_bounds__(LN_WARPS * 32)
 layernorm_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ w, const uint16_t* __restrict__ b,
-                 uint16_t* __restrict__ y, int cols, float eps, int vec) {
-    __shared__ float sh[4];
-    const uint16_t* xr = x + (size_t)blockIdx.x * cols;
-    uint16_t* yr = y + (size_t)blockIdx.x * cols;
+                 uint16_t* __restrict__ y, int rows, int cols, float eps, int vec) {
+    const int row = blockIdx.x * LN_WARPS + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const uint16_t* xr = x + (size_t)row * cols;
+    uint16_t* yr = y + (size_t)row * cols;
     float s = 0.f, ss = 0.f;
     if (vec) {
-        for (int i = threadIdx.x * 8; i < cols; i += blockDim.x * 8) {
+        for (int i = lane * 8; i < cols; i += 256) {
             const uint4 v = *reinterpret_cast<const uint4*>(xr + i);
             const float f[8] = {bf16lo(v.x), bf16hi(v.x), bf16lo(v.y), bf16hi(v.y),
                                 bf16lo(v.z), bf16hi(v.z), bf16lo(v.w), bf16hi(v.w)};
@@ -66,16 +64,16 @@ layernorm_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ w,
             for (int j = 0; j < 8; ++j) { s += f[j]; ss += f[j] * f[j]; }
         }
     } else {
-        for (int i = threadIdx.x; i < cols; i += blockDim.x) { const float f = bf16_to_f32(xr[i]); s += f; ss += f * f; }
+        for (int i = lane; i < cols; i += 32) { const float f = bf16_to_f32(xr[i]); s += f; ss += f * f; }
     }
-    s = block_sum(s, sh);
-    ss = block_sum(ss, sh);
+    s = warp_sum(s);
+    ss = warp_sum(ss);
     const float inv = 1.0f / (float)cols;
     const float mean = s * inv;
     const float var = ss * inv - mean * mean;
     const float inv_std = rsqrtf(var + eps);
     if (vec) {
-        for (int i = threadIdx.x * 8; i < cols; i += blockDim.x * 8) {
+        for (int i = lane * 8; i < cols; i += 256) {
             const uint4 v = *reinterpret_cast<const uint4*>(xr + i);
             const uint4 wv = *reinterpret_cast<const uint4*>(w + i);
             uint4 bv = make_uint4(0, 0, 0, 0);
@@ -95,7 +93,7 @@ layernorm_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ w,
             *reinterpret_cast<uint4*>(yr + i) = ov;
         }
     } else {
-        for (int i = threadIdx.x; i < cols; i += blockDim.x) {
+        for (int i = lane; i < cols; i += 32) {
             const float f = (bf16_to_f32(xr[i]) - mean) * inv_std;
             yr[i] = f32_to_bf16(f * bf16_to_f32(w[i]) + (b ? bf16_to_f32(b[i]) : 0.0f));
         }
@@ -106,8 +104,8 @@ bool vision_layernorm(const void* x, const void* w, const void* b, void* y, int 
                       cudaStream_t st) {
     if (!x || !w || !y || rows <= 0 || cols <= 0) { set_error("vision_layernorm: bad args"); return false; }
     const int vec = (cols % 8) == 0 && ((((uintptr_t)x) | ((uintptr_t)w) | ((uintptr_t)b) | ((uintptr_t)y)) & 15) == 0;
-    layernorm_kernel<<<rows, 128, 0, st>>>((const uint16_t*)x, (const uint16_t*)w, (const uint16_t*)b,
-                                           (uint16_t*)y, cols, eps, vec);
+    layernorm_kernel<<<(rows + LN_WARPS - 1) / LN_WARPS, LN_WARPS * 32, 0, st>>>(
+        (const uint16_t*)x, (const uint16_t*)w, (const uint16_t*)b, (uint16_t*)y, rows, cols, eps, vec);
     O1_VLAUNCH_CHECK("vision_layernorm");
     return true;
 }
