@@ -434,6 +434,20 @@ void hd_vision_qkv_split(const void *qkv, void *q, void *k, void *v, int n, int 
 void hd_vision_attn_merge(const void *hm, void *sm, int heads, int n, int d);
 
 /* ------------------------------------------------ 3. added entry points */
+/* adaLN-modulated decoder block (the "6-way modulation from a timestep embedding" block shape).  No counterpart
+ * in o1.c, whose blocks are unmodulated (src/model/block.c:247-356) and whose timestep enters as a token
+ * (src/cuda/embed.cu:44-58): results are defined by the CPU oracle's orc_decoder_block_adaln only.
+ * mod6 = [shift_msa | scale_msa | gate_msa | shift_mlp | scale_mlp | gate_mlp], each [hidden] bf16:
+ *   h = bf16(bf16(rmsnorm(x)) * (1 + scale) + shift) before a branch, x = bf16(x + bf16(gate * branch)) after it
+ * (the norm kernel and the o_proj / down_proj epilogues take the vectors; no extra pass over the activations).
+ * Other arguments as hd_decoder_block.  o1_adaln_modulation: mod6 = Linear(SiLU(t_emb)), w [6*hidden, hidden]. */
+hd_status o1_adaln_modulation(const void *t_emb_dev, const void *w_dev, const void *b_dev, void *tmp_dev,
+                              void *mod6_dev, int hidden);
+hd_status o1_decoder_block_adaln(const void *in_dev, const float *pos_dev, const void *mask_dev,
+                                 const hd_block_binding *bw, const void *mod6_dev, void *scratch,
+                                 int64_t scratch_bytes, hd_block_internals *ints, void *out_dev, int64_t seq,
+                                 int heads, int kv_heads, int hidden, int ff_hidden, int head_dim,
+                                 hd_sdpa_plan *sdpa);
 /* Stream every later call enqueues on (a cudaStream_t; NULL = legacy default). */
 void o1_set_stream(void *stream);
 void *o1_get_stream(void);

@@ -193,6 +193,9 @@ _sig("hd_sdpa_destroy", None, _P)
 _sig("hd_decoder_block_scratch_bytes", c_int64, c_int64, c_int, c_int, c_int, c_int, c_int)
 _sig("hd_decoder_block", c_int, _P, _P, _P, C.POINTER(BlockBinding), _P, _P, c_int64,
      C.POINTER(BlockInternals), _P, c_int64, c_int, c_int, c_int, c_int, c_int, _P)
+_sig("o1_decoder_block_adaln", c_int, _P, _P, _P, C.POINTER(BlockBinding), _P, _P, c_int64,
+     C.POINTER(BlockInternals), _P, c_int64, c_int, c_int, c_int, c_int, c_int, _P)
+_sig("o1_adaln_modulation", c_int, _P, _P, _P, _P, _P, c_int)
 _sig("hd_forward_workspace_bytes", c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, c_int,
      C.POINTER(c_int64))
 _sig("hd_forward_ws_offset", c_int64, C.c_char_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -258,7 +261,7 @@ _sig("o1_denoise_step_cfg_host", c_int, C.POINTER(ForwardBinding), C.POINTER(For
      _P, c_int, _P, c_int, _P, _P, c_int, c_float, c_float, c_float, _P, _P, _P, _P, c_int, c_int,
      c_int, c_int, c_int, c_int)
 
-EPI_STORE, EPI_BIAS, EPI_RESID, EPI_SWIGLU, EPI_LORA, EPI_BIAS_GELU, EPI_BIAS_RESID = 0, 1, 2, 3, 4, 7, 8
+EPI_STORE, EPI_BIAS, EPI_RESID, EPI_SWIGLU, EPI_LORA, EPI_BIAS_GELU, EPI_BIAS_RESID, EPI_GATE_RESID = 0, 1, 2, 3, 4, 7, 8, 9
 
 
 class O1Error(RuntimeError):

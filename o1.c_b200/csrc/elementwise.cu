@@ -42,7 +42,8 @@ __device__ __forceinline__ float warp_sum(float v) {
 template <int THREADS, int VEC_PER_THREAD>
 __global__ void __launch_bounds__(THREADS)
 rmsnorm_vec_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ w,
-                   uint16_t* __restrict__ y, int rows, int cols, float eps) {
+                   uint16_t* __restrict__ y, int rows, int cols, float eps,
+                   const uint16_t* __restrict__ scale, const uint16_t* __restrict__ shift) {
     const int row = blockIdx.x;
     const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * cols);
     uint4* yr = reinterpret_cast<uint4*>(y + (size_t)row * cols);
@@ -82,6 +83,13 @@ rmsnorm_vec_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ 
             unpack8(wr[idx], g);
 #pragma unroll
             for (int j = 0; j < 8; ++j) f[j] = g[j] * f[j] * inv;
+            if (scale) {   // adaLN variant: the stored norm output, then * (1 + scale) + shift (NULL = o1.c's block)
+                float sc[8], sh[8];
+                unpack8(reinterpret_cast<const uint4*>(scale)[idx], sc);
+                unpack8(reinterpret_cast<const uint4*>(shift)[idx], sh);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f[j] = bf16_round(f[j]) * (1.0f + sc[j]) + sh[j];
+            }
             yr[idx] = pack8(f);
         }
     }
@@ -89,7 +97,8 @@ rmsnorm_vec_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ 
 
 // Any shape (scalar), one warp per row. Used for odd sizes only.
 __global__ void rmsnorm_generic_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ w,
-                                       uint16_t* __restrict__ y, int rows, int cols, float eps) {
+                                       uint16_t* __restrict__ y, int rows, int cols, float eps,
+                                       const uint16_t* __restrict__ scale, const uint16_t* __restrict__ shift) {
     const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= rows) return;
     const int lane = threadIdx.x & 31;
@@ -99,23 +108,32 @@ __global__ void rmsnorm_generic_kernel(const uint16_t* __restrict__ x, const uin
     for (int i = lane; i < cols; i += 32) { float v = bf16_to_f32(xr[i]); sq += v * v; }
     sq = warp_sum(sq);
     const float inv = rsqrtf(sq / (float)cols + eps);
-    for (int i = lane; i < cols; i += 32)
-        yr[i] = f32_to_bf16(bf16_to_f32(w[i]) * bf16_to_f32(xr[i]) * inv);
+    for (int i = lane; i < cols; i += 32) {
+        float v = bf16_to_f32(w[i]) * bf16_to_f32(xr[i]) * inv;
+        if (scale) v = bf16_round(v) * (1.0f + bf16_to_f32(scale[i])) + bf16_to_f32(shift[i]);
+        yr[i] = f32_to_bf16(v);
+    }
 }
 
 bool rmsnorm(const void* x, const void* w, void* y, int rows, int cols, float eps, cudaStream_t st) {
-    if (!x || !w || !y || rows <= 0 || cols <= 0) { set_error("rmsnorm: bad args"); return false; }
-    const bool aligned = ((((uintptr_t)x) | ((uintptr_t)y) | ((uintptr_t)w)) & 15) == 0;
+    return rmsnorm_mod(x, w, nullptr, nullptr, y, rows, cols, eps, st);
+}
+// scale / shift [cols] bf16 or both NULL: y = bf16(bf16(rmsnorm(x)) * (1 + scale) + shift)
+bool rmsnorm_mod(const void* x, const void* w, const void* scale, const void* shift, void* y, int rows, int cols,
+                 float eps, cudaStream_t st) {
+    if (!x || !w || !y || rows <= 0 || cols <= 0 || (!scale != !shift)) { set_error("rmsnorm: bad args"); return false; }
+    const bool aligned = ((((uintptr_t)x) | ((uintptr_t)y) | ((uintptr_t)w) | ((uintptr_t)scale) | ((uintptr_t)shift)) & 15) == 0;
+    const uint16_t *sc = (const uint16_t*)scale, *sh = (const uint16_t*)shift;
     if (aligned && (cols % 8) == 0 && cols <= 128 * 8 * 8 && cols > 1024) {
         rmsnorm_vec_kernel<128, 8><<<rows, 128, 0, st>>>((const uint16_t*)x, (const uint16_t*)w,
-                                                         (uint16_t*)y, rows, cols, eps);
+                                                         (uint16_t*)y, rows, cols, eps, sc, sh);
     } else if (aligned && (cols % 8) == 0 && cols <= 1024) {
         rmsnorm_vec_kernel<32, 4><<<rows, 32, 0, st>>>((const uint16_t*)x, (const uint16_t*)w,
-                                                       (uint16_t*)y, rows, cols, eps);
+                                                       (uint16_t*)y, rows, cols, eps, sc, sh);
     } else {
         const int wpb = 4;
         rmsnorm_generic_kernel<<<(rows + wpb - 1) / wpb, wpb * 32, 0, st>>>(
-            (const uint16_t*)x, (const uint16_t*)w, (uint16_t*)y, rows, cols, eps);
+            (const uint16_t*)x, (const uint16_t*)w, (uint16_t*)y, rows, cols, eps, sc, sh);
     }
     O1_LAUNCH_CHECK("rmsnorm");
     return true;

@@ -466,9 +466,12 @@ static hd_status copy_dd(void* dst, const void* src, size_t bytes, cudaStream_t 
 }
 
 // cs: [S,128] cos|sin table for this sequence (built once per forward).
+// mod: NULL (o1.c's block) or the six adaLN vectors [shift_msa | scale_msa | gate_msa | shift_mlp | scale_mlp |
+// gate_mlp], each [hidden] bf16: norm * (1 + scale) + shift before a branch, x + gate * branch after it.
 static hd_status block_forward(const void* in, const float* cs, int ar_len, const hd_block_binding* bw,
                                void* scratch, hd_block_internals* ints, void* out, int64_t S64,
-                               int heads, int kv_heads, int hidden, int ff, int hd, cudaStream_t st) {
+                               int heads, int kv_heads, int hidden, int ff, int hd, cudaStream_t st,
+                               const uint16_t* mod = nullptr) {
     const int S = (int)S64;
     BlockScratch b = carve_block((void*)(((uintptr_t)scratch + 255) & ~(uintptr_t)255), S, heads,
                                  kv_heads, hidden, ff, hd);
@@ -477,7 +480,7 @@ static hd_status block_forward(const void* in, const float* cs, int ar_len, cons
     const int qc = heads * hd, kc = kv_heads * hd, ld = qc + 2 * kc;
 
     // 1. input RMSNorm
-    BLK_TRY(rmsnorm(in, bw->input_ln, b.ln, S, hidden, eps, st), "input_norm");
+    BLK_TRY(rmsnorm_mod(in, bw->input_ln, mod ? mod + hidden : nullptr, mod, b.ln, S, hidden, eps, st), "input_norm");
     // 2-6. q/k/v projections into one seq-major buffer [S, qc | kc | kc]; the per-head RMSNorm + MRoPE of q and k
     // (block.c:266-289) run inside the projections' epilogues where the tensor-core tiles cover the shape,
     // otherwise as one in-place kernel per tensor (no head split either way)
@@ -503,7 +506,13 @@ static hd_status block_forward(const void* in, const float* cs, int ar_len, cons
     BLK_TRY(flash_attention(b.qkv, ld, b.qkv + qc, ld, b.qkv + qc + kc, ld, b.attn, qc, S, heads,
                             kv_heads, ar_len, scaling, st, b.swi, (size_t)S * ff * 2), "attention");
     // 8-9. o_proj (+ residual)
-    if (ints && ints->attn_hidden) {
+    if (mod) {
+        if (ints && ints->attn_hidden)
+            BLK_TRY(gemm_bf16(b.attn, bw->o_proj, nullptr, ints->attn_hidden, S, hidden, qc, EPI_STORE, nullptr,
+                              nullptr, 0.f, 0, st), "o_proj");
+        BLK_TRY(gemm_bf16_ld(b.attn, qc, bw->o_proj, nullptr, b.ar, hidden, S, hidden, qc, EPI_GATE_RESID,
+                             mod + 2 * hidden, in, hidden, 0.f, 0, st), "o_proj+gate+resid");
+    } else if (ints && ints->attn_hidden) {
         BLK_TRY(gemm_bf16(b.attn, bw->o_proj, nullptr, b.tmp, S, hidden, qc, EPI_STORE, nullptr,
                           nullptr, 0.f, 0, st), "o_proj");
         BLK_TRY(residual_add(in, b.tmp, b.ar, (size_t)S * hidden, st), "attn_resid");
@@ -513,11 +522,18 @@ static hd_status block_forward(const void* in, const float* cs, int ar_len, cons
                              nullptr, in, hidden, 0.f, 0, st), "o_proj+resid");
     }
     // 10. post-attention RMSNorm
-    BLK_TRY(rmsnorm(b.ar, bw->post_ln, b.post, S, hidden, eps, st), "post_norm");
+    BLK_TRY(rmsnorm_mod(b.ar, bw->post_ln, mod ? mod + 4 * hidden : nullptr, mod ? mod + 3 * hidden : nullptr, b.post, S,
+                        hidden, eps, st), "post_norm");
     // 11. gate|up GEMM with SwiGLU epilogue, then down (+ residual) straight into out
     BLK_TRY(gemm_bf16(b.post, bw->gate_proj, bw->up_proj, b.swi, S, ff, hidden, EPI_SWIGLU, nullptr,
                       nullptr, 0.f, 0, st), "gate_up_swiglu");
-    if (ints && ints->mlp_out) {
+    if (mod) {
+        if (ints && ints->mlp_out)
+            BLK_TRY(gemm_bf16(b.swi, bw->down_proj, nullptr, ints->mlp_out, S, hidden, ff, EPI_STORE, nullptr,
+                              nullptr, 0.f, 0, st), "down_proj");
+        BLK_TRY(gemm_bf16_ld(b.swi, ff, bw->down_proj, nullptr, out, hidden, S, hidden, ff, EPI_GATE_RESID,
+                             mod + 5 * hidden, b.ar, hidden, 0.f, 0, st), "down_proj+gate+resid");
+    } else if (ints && ints->mlp_out) {
         BLK_TRY(gemm_bf16(b.swi, bw->down_proj, nullptr, b.tmp, S, hidden, ff, EPI_STORE, nullptr,
                           nullptr, 0.f, 0, st), "down_proj");
         BLK_TRY(residual_add(b.ar, b.tmp, out, (size_t)S * hidden, st), "mlp_resid");
@@ -541,11 +557,11 @@ static bool dims_supported(int heads, int kv_heads, int hidden, int ff, int hd) 
 
 extern "C" {
 
-hd_status hd_decoder_block(const void* in_dev, const float* pos_dev, const void* mask_dev,
+static hd_status decoder_block_entry(const void* in_dev, const float* pos_dev, const void* mask_dev,
                            const hd_block_binding* bw, const int64_t* sec_dev, void* scratch,
                            int64_t scratch_bytes, hd_block_internals* ints, void* out_dev,
                            int64_t seq, int heads, int kv_heads, int hidden, int ff_hidden,
-                           int head_dim, hd_sdpa_plan* sdpa) {
+                           int head_dim, hd_sdpa_plan* sdpa, const uint16_t* mod) {
     (void)sec_dev;
     if (!in_dev || !pos_dev || !bw || !scratch || !out_dev || (!mask_dev && !sdpa)) {
         hd_set_error("block: null argument");
@@ -573,7 +589,40 @@ hd_status hd_decoder_block(const void* in_dev, const float* pos_dev, const void*
     }
     count();
     return block_forward(in_dev, b.cs, ar_len, bw, scratch, ints, out_dev, seq, heads, kv_heads, hidden,
-                         ff_hidden, head_dim, g_stream);
+                         ff_hidden, head_dim, g_stream, mod);
+}
+
+hd_status hd_decoder_block(const void* in_dev, const float* pos_dev, const void* mask_dev,
+                           const hd_block_binding* bw, const int64_t* sec_dev, void* scratch,
+                           int64_t scratch_bytes, hd_block_internals* ints, void* out_dev,
+                           int64_t seq, int heads, int kv_heads, int hidden, int ff_hidden,
+                           int head_dim, hd_sdpa_plan* sdpa) {
+    return decoder_block_entry(in_dev, pos_dev, mask_dev, bw, sec_dev, scratch, scratch_bytes, ints, out_dev, seq,
+                               heads, kv_heads, hidden, ff_hidden, head_dim, sdpa, nullptr);
+}
+
+// adaLN variant of the block (six modulation vectors from the timestep embedding); o1.c has no such block
+hd_status o1_decoder_block_adaln(const void* in_dev, const float* pos_dev, const void* mask_dev,
+                                 const hd_block_binding* bw, const void* mod6_dev, void* scratch,
+                                 int64_t scratch_bytes, hd_block_internals* ints, void* out_dev, int64_t seq,
+                                 int heads, int kv_heads, int hidden, int ff_hidden, int head_dim,
+                                 hd_sdpa_plan* sdpa) {
+    if (!mod6_dev || (((uintptr_t)mod6_dev) & 15)) { hd_set_error("block: modulation vectors missing or unaligned"); return HD_ERR_MISSING; }
+    return decoder_block_entry(in_dev, pos_dev, mask_dev, bw, nullptr, scratch, scratch_bytes, ints, out_dev, seq,
+                               heads, kv_heads, hidden, ff_hidden, head_dim, sdpa, (const uint16_t*)mod6_dev);
+}
+
+// mod6 [6*hidden] = Linear(SiLU(t_emb)): w [6*hidden, hidden], b [6*hidden], tmp [hidden] scratch
+hd_status o1_adaln_modulation(const void* t_emb_dev, const void* w_dev, const void* b_dev, void* tmp_dev,
+                              void* mod6_dev, int hidden) {
+    if (!t_emb_dev || !w_dev || !b_dev || !tmp_dev || !mod6_dev || hidden <= 0) { hd_set_error("adaln: null argument"); return HD_ERR_MISSING; }
+    if (!silu(t_emb_dev, tmp_dev, (size_t)hidden, g_stream) ||
+        !gemm_bf16(tmp_dev, w_dev, nullptr, mod6_dev, 1, 6 * hidden, hidden, EPI_BIAS, b_dev, nullptr, 0.f, 0, g_stream)) {
+        hd_set_error("adaln: %s", g_cuda_err);
+        return HD_ERR_RUNTIME;
+    }
+    count(2);
+    return HD_OK;
 }
 
 // ==================================================================== forward

@@ -451,6 +451,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                             load32_bf16(g.resid + (size_t)row * g.ldr + col, rs);
 #pragma unroll
                             for (int j = 0; j < 32; ++j) v[j] = rs[j] + bf16_round(bf16_round(v[j]) + b[j]);
+                        } else if (EPI == EPI_GATE_RESID) {
+                            float gt[32], rs[32];
+                            load32_bf16(g.bias + col, gt);
+                            load32_bf16(g.resid + (size_t)row * g.ldr + col, rs);
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) v[j] = rs[j] + bf16_round(gt[j] * bf16_round(v[j]));
                         } else if (EPI == EPI_RESID) {
                             float b[32];
                             load32_bf16(g.resid + (size_t)row * g.ldr + col, b);
@@ -590,7 +596,7 @@ static bool launch_tc(const CUtensorMap* tA, const CUtensorMap* tB, const CUtens
     const int tiles = g.num_m * g.num_n;
     int grid = sm_count();
     if (grid > tiles) grid = tiles;
-    prof_before(EPI == EPI_QKNORM ? (int)EPI_STORE : (EPI == EPI_BIAS_GELU ? (int)EPI_BIAS : (EPI == EPI_BIAS_RESID ? (int)EPI_RESID : EPI)), 2.0 * g.M * (double)g.N * g.K * (EPI == EPI_SWIGLU ? 2.0 : 1.0), st);
+    prof_before(EPI == EPI_QKNORM ? (int)EPI_STORE : (EPI == EPI_BIAS_GELU ? (int)EPI_BIAS : ((EPI == EPI_BIAS_RESID || EPI == EPI_GATE_RESID) ? (int)EPI_RESID : EPI)), 2.0 * g.M * (double)g.N * g.K * (EPI == EPI_SWIGLU ? 2.0 : 1.0), st);
     kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, st>>>(*tA, *tB, *tB2, g);
     prof_after(st);
     cudaError_t e = cudaGetLastError();
@@ -655,8 +661,8 @@ bool gemm_bf16_ex(const void* x, int ldx, const void* w, const void* w2, void* y
         set_error("gemm: a ragged N needs 16-byte aligned output rows and bias");
         return false;
     }
-    if (epi == EPI_BIAS_RESID && (!bias || !resid || (((uintptr_t)bias) & 15) || (((uintptr_t)resid) & 15) || (ldr % 8))) {
-        set_error("gemm: the bias + residual epilogue needs both operands, 16-byte aligned");
+    if ((epi == EPI_BIAS_RESID || epi == EPI_GATE_RESID) && (!bias || !resid || (((uintptr_t)bias) & 15) || (((uintptr_t)resid) & 15) || (ldr % 8))) {
+        set_error("gemm: the bias / gate + residual epilogues need both operands, 16-byte aligned");
         return false;
     }
     GemmArgs g;
@@ -730,6 +736,7 @@ bool gemm_bf16_ex(const void* x, int ldx, const void* w, const void* w2, void* y
             case EPI_QKNORM: return launch_tc<EPI_QKNORM, 256>(tA, tB, tB2, g, st);
             case EPI_BIAS_GELU: return launch_tc<EPI_BIAS_GELU, 256>(tA, tB, tB2, g, st);
             case EPI_BIAS_RESID: return launch_tc<EPI_BIAS_RESID, 256>(tA, tB, tB2, g, st);
+            case EPI_GATE_RESID: return launch_tc<EPI_GATE_RESID, 256>(tA, tB, tB2, g, st);
         }
     } else {
         switch (epi) {
@@ -740,6 +747,7 @@ bool gemm_bf16_ex(const void* x, int ldx, const void* w, const void* w2, void* y
             case EPI_QKNORM: return launch_tc<EPI_QKNORM, 128>(tA, tB, tB2, g, st);
             case EPI_BIAS_GELU: return launch_tc<EPI_BIAS_GELU, 128>(tA, tB, tB2, g, st);
             case EPI_BIAS_RESID: return launch_tc<EPI_BIAS_RESID, 128>(tA, tB, tB2, g, st);
+            case EPI_GATE_RESID: return launch_tc<EPI_GATE_RESID, 128>(tA, tB, tB2, g, st);
         }
     }
     set_error("gemm: unknown epilogue %d", epi);

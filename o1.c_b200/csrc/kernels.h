@@ -12,8 +12,9 @@ namespace o1 {
 // are one head; `bias` carries the norm weight [128], `resid` the fp32 cos|sin table [M,128], `scale` the epsilon)
 // EPI_BIAS_GELU: bf16(gelu(bf16(bf16(acc) + bias))), tanh form when `scale` == 0, erf form otherwise (vision tower)
 // EPI_BIAS_RESID: bf16(resid + bf16(bf16(acc) + bias)): a biased projection followed by the residual add
+// EPI_GATE_RESID: bf16(resid + bf16(gate[col] * bf16(acc))), the gate vector passed as `bias` (adaLN block variant)
 enum Epi { EPI_STORE = 0, EPI_BIAS = 1, EPI_RESID = 2, EPI_SWIGLU = 3, EPI_LORA = 4, EPI_QKNORM = 6, EPI_BIAS_GELU = 7,
-           EPI_BIAS_RESID = 8 };
+           EPI_BIAS_RESID = 8, EPI_GATE_RESID = 9 };
 
 // ---- engine.cu: optional per-launch event timing of the tensor-core kernels.
 // kind: 0..4 = GEMM by epilogue (Epi), 5 = flash attention.  Costs two event
@@ -61,6 +62,8 @@ bool flash_attention_tab(const void* q, int ldq, const void* k, int ldk, const v
 
 // ---- elementwise.cu
 bool rmsnorm(const void* x, const void* w, void* y, int rows, int cols, float eps, cudaStream_t st);
+bool rmsnorm_mod(const void* x, const void* w, const void* scale, const void* shift, void* y, int rows, int cols,
+                 float eps, cudaStream_t st);
 bool silu(const void* x, void* y, size_t n, cudaStream_t st);
 bool swiglu(const void* gate, const void* up, void* y, size_t n, cudaStream_t st);
 bool residual_add(const void* x, const void* a, void* y, size_t n, cudaStream_t st);

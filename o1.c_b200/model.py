@@ -212,8 +212,9 @@ class Engine:
             raise KeyError(name)
         return self.ws_buf[off:off + nbytes]
 
-    def block(self, x, pos, layer, internals=False):
-        """hd_decoder_block on x [S, hidden] bf16; returns out (and the five internals)."""
+    def block(self, x, pos, layer, internals=False, mod6=None):
+        """hd_decoder_block on x [S, hidden] bf16; returns out (and the five internals).  With mod6
+        ([6*hidden] bf16: shift/scale/gate for the attention and the MLP branch) the adaLN variant runs."""
         out = torch.empty_like(x)
         scratch = self.ws_region("block_scratch", self.block_scratch_bytes)
         ints, bufs = None, {}
@@ -223,9 +224,9 @@ class Engine:
                 bufs[n] = torch.empty_like(x)
                 setattr(ints, n, bufs[n].data_ptr())
         bb = self.w.block_binding(layer)
-        rc = lib.hd_decoder_block(ptr(x), ptr(pos), None, C.byref(bb), ptr(self.sec), ptr(scratch),
-                                  self.block_scratch_bytes, C.byref(ints) if ints else None, ptr(out),
-                                  self.S, *self.dimargs, self.plan)
+        fn = lib.hd_decoder_block if mod6 is None else lib.o1_decoder_block_adaln
+        rc = fn(ptr(x), ptr(pos), None, C.byref(bb), ptr(self.sec if mod6 is None else mod6), ptr(scratch),
+                self.block_scratch_bytes, C.byref(ints) if ints else None, ptr(out), self.S, *self.dimargs, self.plan)
         check(rc, "hd_decoder_block")
         return (out, bufs) if internals else out
 

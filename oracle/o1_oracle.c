@@ -352,9 +352,54 @@ typedef struct {
         *down_proj, *q_norm, *k_norm;
 } orc_block_weights;
 
+/* adaLN pieces of the modulated block variant (BASELINE config 0; no counterpart in o1.c, whose blocks are
+ * unmodulated -- "parity unpinned": these define the arithmetic the CUDA variant is checked against).
+ * mod = [shift_msa | scale_msa | gate_msa | shift_mlp | scale_mlp | gate_mlp], each [hidden] bf16. */
+static void orc_modulate(uint16_t *x, const uint16_t *shift, const uint16_t *scale, int rows, int cols) {
+#pragma omp parallel for schedule(static)
+    for (int r = 0; r < rows; ++r)
+        for (int c = 0; c < cols; ++c) {
+            uint16_t *p = x + (size_t)r * cols + c;
+            *p = f2bf(bf2f(*p) * (1.0f + bf2f(scale[c])) + bf2f(shift[c]));
+        }
+}
+static void orc_gated_residual(const uint16_t *x, const uint16_t *branch, const uint16_t *gate, uint16_t *y,
+                               int rows, int cols) {
+#pragma omp parallel for schedule(static)
+    for (int r = 0; r < rows; ++r)
+        for (int c = 0; c < cols; ++c) {
+            const size_t i = (size_t)r * cols + c;
+            y[i] = f2bf(bf2f(x[i]) + bfr(bf2f(gate[c]) * bf2f(branch[i])));
+        }
+}
+/* mod[6*hidden] = Linear(SiLU(t_emb)): w [6*hidden, hidden], b [6*hidden] */
+ORC_API void orc_adaln_modulation(const uint16_t *t_emb, const uint16_t *w, const uint16_t *b, uint16_t *mod,
+                                  int hidden) {
+    uint16_t *act = (uint16_t *)malloc((size_t)hidden * 2);
+    if (!act) return;
+    orc_silu(t_emb, act, (size_t)hidden);
+    orc_linear(act, w, b, mod, 1, 6 * hidden, hidden);
+    free(act);
+}
+
+static int decoder_block_impl(const uint16_t *in, const float *pos /* [3,S] */, int ar_len,
+                              const orc_block_weights *w, uint16_t *out, uint16_t **ints, int S,
+                              int heads, int kv_heads, int hidden, int ff, int hd, const uint16_t *mod);
 ORC_API int orc_decoder_block(const uint16_t *in, const float *pos /* [3,S] */, int ar_len,
                               const orc_block_weights *w, uint16_t *out, uint16_t **ints, int S,
                               int heads, int kv_heads, int hidden, int ff, int hd) {
+    return decoder_block_impl(in, pos, ar_len, w, out, ints, S, heads, kv_heads, hidden, ff, hd, NULL);
+}
+/* the same block with adaLN: norm * (1 + scale) + shift before each branch, x + gate * branch after it */
+ORC_API int orc_decoder_block_adaln(const uint16_t *in, const float *pos, int ar_len, const orc_block_weights *w,
+                                    const uint16_t *mod, uint16_t *out, uint16_t **ints, int S, int heads,
+                                    int kv_heads, int hidden, int ff, int hd) {
+    if (!mod) return 1;
+    return decoder_block_impl(in, pos, ar_len, w, out, ints, S, heads, kv_heads, hidden, ff, hd, mod);
+}
+static int decoder_block_impl(const uint16_t *in, const float *pos /* [3,S] */, int ar_len,
+                              const orc_block_weights *w, uint16_t *out, uint16_t **ints, int S,
+                              int heads, int kv_heads, int hidden, int ff, int hd, const uint16_t *mod) {
     const float eps = 1e-6f, theta = 5000000.0f;
     const float scaling = (float)(1.0 / sqrt((double)hd));
     const size_t SH = (size_t)S * heads * hd, SK = (size_t)S * kv_heads * hd, SHID = (size_t)S * hidden,
@@ -370,6 +415,7 @@ ORC_API int orc_decoder_block(const uint16_t *in, const float *pos /* [3,S] */, 
         !up || !swi || !mlp || !cs || !sn) { rc = 1; goto done; }
     const int64_t section[3] = {24, 20, 20};
     orc_rmsnorm(in, w->input_ln, ln, S, hidden, eps);                          /* :248 */
+    if (mod) orc_modulate(ln, mod, mod + hidden, S, hidden);
     orc_linear(ln, w->q_proj, NULL, qp, S, heads * hd, hidden);                /* :253 */
     orc_linear(ln, w->k_proj, NULL, kp, S, kv_heads * hd, hidden);
     orc_linear(ln, w->v_proj, NULL, vp, S, kv_heads * hd, hidden);
@@ -383,13 +429,16 @@ ORC_API int orc_decoder_block(const uint16_t *in, const float *pos /* [3,S] */, 
     orc_apply_rotary(kr, cs, sn, k, kv_heads, S, hd);
     orc_attention(q, k, v, as, heads, kv_heads, S, hd, scaling, ar_len);       /* :296-312 */
     orc_linear(as, w->o_proj, NULL, ah, S, hidden, heads * hd);                /* :321 */
-    orc_residual_add(in, ah, ar, SHID);                                        /* :326 */
+    if (mod) orc_gated_residual(in, ah, mod + 2 * hidden, ar, S, hidden);
+    else orc_residual_add(in, ah, ar, SHID);                                   /* :326 */
     orc_rmsnorm(ar, w->post_ln, post, S, hidden, eps);                         /* :331 */
+    if (mod) orc_modulate(post, mod + 3 * hidden, mod + 4 * hidden, S, hidden);
     orc_linear(post, w->gate_proj, NULL, gate, S, ff, hidden);                 /* :336 */
     orc_linear(post, w->up_proj, NULL, up, S, ff, hidden);
     orc_swiglu(gate, up, swi, SI);                                             /* :340 */
     orc_linear(swi, w->down_proj, NULL, mlp, S, hidden, ff);                   /* :343 */
-    orc_residual_add(ar, mlp, out, SHID);                                      /* :348 */
+    if (mod) orc_gated_residual(ar, mlp, mod + 5 * hidden, out, S, hidden);
+    else orc_residual_add(ar, mlp, out, SHID);                                 /* :348 */
     if (ints) {
         if (ints[0]) memcpy(ints[0], ln, SHID * 2);
         if (ints[1]) memcpy(ints[1], ah, SHID * 2);

@@ -74,6 +74,8 @@ def oracle():
     sig("orc_head_split", None, _P, _P, _i, _i, _i)
     sig("orc_head_merge", None, _P, _P, _i, _i, _i)
     sig("orc_decoder_block", _i, _P, _P, _i, C.POINTER(BlockW), _P, C.POINTER(_P), _i, _i, _i, _i, _i, _i)
+    sig("orc_decoder_block_adaln", _i, _P, _P, _i, C.POINTER(BlockW), _P, _P, C.POINTER(_P), _i, _i, _i, _i, _i, _i)
+    sig("orc_adaln_modulation", None, _P, _P, _P, _P, _i)
     sig("orc_forward", _i, C.POINTER(Globals), C.POINTER(BlockW), _i, _P, _P, _i, _P, _i, _P, _i, _f,
         _i64, _P, _P, _i, _i, _i, _i, _i)
     sig("orc_forward_visual", _i, C.POINTER(Globals), C.POINTER(BlockW), _i, _P, _P, _i, _P, _i, _P, _i, _f,
@@ -299,8 +301,9 @@ class HostWeights:
             self._cache.pop((layer, n), None)
 
 
-def oracle_block(hw, layer, x_u16, pos_np, ar_len, want_ints=True):
-    """orc_decoder_block on host arrays. Returns (out, dict of the five internals)."""
+def oracle_block(hw, layer, x_u16, pos_np, ar_len, want_ints=True, mod6=None):
+    """orc_decoder_block (orc_decoder_block_adaln with mod6 [6*hidden] u16) on host arrays.
+    Returns (out, dict of the five internals)."""
     d = hw.dims
     S = x_u16.shape[0]
     out = np.empty_like(x_u16)
@@ -309,9 +312,13 @@ def oracle_block(hw, layer, x_u16, pos_np, ar_len, want_ints=True):
     arr = (C.c_void_p * 5)(*[ints[n].ctypes.data if want_ints else None for n in names])
     bw = hw.block_struct(layer)
     pos_np = np.ascontiguousarray(pos_np, dtype=np.float32)
-    rc = oracle().orc_decoder_block(np_ptr(x_u16), np_ptr(pos_np), ar_len, C.byref(bw), np_ptr(out),
-                                    arr if want_ints else None, S, d["heads"], d["kv_heads"], d["hidden"],
-                                    d["ff"], d["head_dim"])
+    dims = (S, d["heads"], d["kv_heads"], d["hidden"], d["ff"], d["head_dim"])
+    if mod6 is None:
+        rc = oracle().orc_decoder_block(np_ptr(x_u16), np_ptr(pos_np), ar_len, C.byref(bw), np_ptr(out),
+                                        arr if want_ints else None, *dims)
+    else:
+        rc = oracle().orc_decoder_block_adaln(np_ptr(x_u16), np_ptr(pos_np), ar_len, C.byref(bw), np_ptr(mod6),
+                                              np_ptr(out), arr if want_ints else None, *dims)
     assert rc == 0
     return out, ints
 

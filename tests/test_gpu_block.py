@@ -136,3 +136,39 @@ def test_block_argument_errors(pkg, dev):
     rc = pkg.lib.hd_decoder_block(pkg.ptr(x), pkg.ptr(pos.to(dev)), None, C.byref(bb), None, pkg.ptr(small), 1 << 40,
                                   None, pkg.ptr(x), 16, 32, 8, 4096, 12288, 64, eng.plan)
     assert rc == 9                                                           # HD_ERR_UNSUPPORTED
+
+
+@pytest.mark.parametrize("T,gh,gw", [(24, 8, 12), (256, 32, 32)])
+def test_adaln_block_vs_oracle(pkg, orc, dev, T, gh, gw):
+    """The adaLN-modulated block variant (six vectors from Linear(SiLU(t_emb)); the second case is the 256 + 1024
+    token block).  o1.c has no modulated block, so the CPU oracle's orc_decoder_block_adaln is the only yardstick."""
+    H = pkg.HIDDEN
+    w = pkg.Weights(n_layers=1, seed=1234, weight_set="B", device=dev)
+    eng = pkg.Engine(w, T, gh * gw)
+    pos, ar = pkg.seq_t2i(T, gh, gw)
+    x = seeded_bf16((eng.S, H), 42)
+    # modulation from a seeded timestep embedding (standing in for the embedding of t = 500)
+    t_emb, mw, mb = seeded_bf16(H, 51), seeded_bf16((6 * H, H), 52, 0.0, 0.02), seeded_bf16(6 * H, 53, 0.0, 0.1)
+    mod_ref = np.empty(6 * H, dtype=np.uint16)
+    orc.orc_adaln_modulation(parity.np_ptr(t_emb), parity.np_ptr(mw), parity.np_ptr(mb), parity.np_ptr(mod_ref), H)
+    td, mwd, mbd = (u16_to_torch(a, dev) for a in (t_emb, mw, mb))
+    tmp = torch.empty(H, dtype=torch.bfloat16, device=dev)
+    mod = torch.empty(6 * H, dtype=torch.bfloat16, device=dev)
+    pkg.check(pkg.lib.o1_adaln_modulation(pkg.ptr(td), pkg.ptr(mwd), pkg.ptr(mbd), pkg.ptr(tmp), pkg.ptr(mod), H), "adaln")
+    torch.cuda.synchronize()
+    assert_close(torch_to_u16(mod), mod_ref, "C", "modulation vectors")
+    # the block itself on identical modulation vectors
+    modd = u16_to_torch(mod_ref, dev)
+    xd = u16_to_torch(x, dev)
+    out, ints = eng.block(xd, pos.to(dev), 0, internals=True, mod6=modd)
+    out_fused = eng.block(xd, pos.to(dev), 0, mod6=modd)
+    out_plain = eng.block(xd, pos.to(dev), 0)
+    torch.cuda.synchronize()
+    hw = parity.HostWeights(pkg, 1, 1234, "B")
+    ref_out, ref_ints = parity.oracle_block(hw, 0, x, pos.numpy(), ar, mod6=mod_ref)
+    assert_close(torch_to_u16(ints["ln0"]), ref_ints["ln0"], "B", "modulated ln0")
+    for n in ("attn_hidden", "attn_resid", "post_ln", "mlp_out"):
+        assert_close(torch_to_u16(ints[n]), ref_ints[n], "D", n)
+    assert_close(torch_to_u16(out), ref_out, "D", "adaLN block output")
+    assert torch.equal(out, out_fused)
+    assert parity.metrics(out, out_plain)[0] > 1e-2, "the modulation must change the result"

@@ -346,3 +346,33 @@ def test_seq_ref_positions(orc, golden, pkg):
     T = int(g["k1_meta"][0])
     assert list(k[:, T]) == [4096, 4096, 4096] and k[:, T:T + 1024].max() == 4127
     assert list(k[:, T + 1024]) == [4128, 4128, 4128] and list(k[:, -1]) == [4128, 4143, 4143]
+
+
+def test_adaln_block_variant_reduces_to_the_plain_block(pkg, orc):
+    """orc_decoder_block_adaln with shift = scale = 0 and gate = 1 is orc_decoder_block bit for bit; a real
+    modulation changes the result; the modulation vectors are Linear(SiLU(t_emb))."""
+    import parity
+    H = pkg.HIDDEN
+    hw = parity.HostWeights(pkg, 1, 1234, "B")
+    T, gh, gw = 8, 4, 4
+    pos, ar = pkg.seq_t2i(T, gh, gw)
+    x = parity.seeded_bf16((T + gh * gw, H), 42)
+    mod = np.zeros(6 * H, dtype=np.uint16)
+    mod[2 * H:3 * H] = mod[5 * H:] = parity.f32_to_bf16_np(np.ones(H, np.float32))
+    plain, _ = parity.oracle_block(hw, 0, x, pos.numpy(), ar, want_ints=False)
+    ident, _ = parity.oracle_block(hw, 0, x, pos.numpy(), ar, want_ints=False, mod6=mod)
+    assert (plain == ident).all()
+    t_emb, mw, mb = parity.seeded_bf16(H, 51), parity.seeded_bf16((6 * H, H), 52, 0.0, 0.02), parity.seeded_bf16(6 * H, 53, 0.0, 0.1)
+    mod6 = np.empty(6 * H, dtype=np.uint16)
+    orc.orc_adaln_modulation(parity.np_ptr(t_emb), parity.np_ptr(mw), parity.np_ptr(mb), parity.np_ptr(mod6), H)
+    te = parity.bf16_to_f32_np(t_emb).astype(np.float64)
+    act = parity.bf16_to_f32_np(parity.f32_to_bf16_np((te / (1 + np.exp(-te))).astype(np.float32))).astype(np.float64)
+    want = parity.bf16_to_f32_np(mw).astype(np.float64) @ act + parity.bf16_to_f32_np(mb)
+    parity.assert_close(mod6, want.astype(np.float32), "C", "modulation vectors")
+    moded, ints = parity.oracle_block(hw, 0, x, pos.numpy(), ar, mod6=mod6)
+    assert parity.metrics(moded, plain)[0] > 1e-2
+    # ln0 is the modulated norm: bf16(norm * (1 + scale) + shift)
+    _, pints = parity.oracle_block(hw, 0, x, pos.numpy(), ar)
+    f = parity.bf16_to_f32_np
+    want_ln = f(pints["ln0"]) * (1.0 + f(mod6[H:2 * H])) + f(mod6[:H])
+    assert (ints["ln0"] == parity.f32_to_bf16_np(want_ln.astype(np.float32))).all()
