@@ -5,7 +5,7 @@ Metric: seconds per image for 28-step CFG text-to-image at 16384 image tokens
 (+256 text tokens, 36 decoder blocks).  A "step" here is one denoise step: cond forward, uncond
 forward, fused CFG + flow-match scheduler update.  sec/image = 28 x mean step time.
 
-  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c0|c1|c2|c3|c4|vision|vision64|elementwise]
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c0|c1|c2|c3|c4|vision|vision64|elementwise|block]
                   [--exchange direct|nccl]
 
 Prints ONE JSON line (rank 0): value = s/image from CUDA-event step times with the latent resident on the
@@ -714,13 +714,108 @@ def run_elementwise(args):
             "kernels": rows, "gpu_launches": len(cases) * (reps + max(args.warmup, 3))}
 
 
+# --------------------------------------------------------------------------------------- one decoder block
+def run_block(args):
+    """One decoder block at 256 text + 1024 image tokens (hidden 4096, 32 / 8 heads of 128, SwiGLU 12288): this
+    library's block, its adaLN-modulated variant, the reference's CUDA build of hd_decoder_block (cuBLASLt + cuDNN
+    SDPA) on the same GPU and weights, and the C/OpenMP oracle of the same block on the host cores."""
+    import numpy as np
+    import torch
+    from __graft_entry__ import load_package
+    import parity
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    pkg = load_package()
+    pkg.use_torch_stream()
+    T, gh, gw = WORKLOADS["c0"]
+    w = pkg.Weights(n_layers=1, seed=1234, weight_set="A", device=dev)
+    eng = pkg.Engine(w, T, gh * gw)
+    S, H = eng.S, pkg.HIDDEN
+    pos, ar = pkg.seq_t2i(T, gh, gw)
+    posd = pos.to(dev)
+    x = parity.u16_to_torch(parity.seeded_bf16((S, H), 42), dev)
+    mod = parity.u16_to_torch(parity.seeded_bf16(6 * H, 5, 0.0, 0.3), dev)
+    fl = flops_block(S, ar)
+    reps = args.steps if args.short else max(args.steps, 20)
+    warm = args.warmup if args.short else max(args.warmup, 3)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)       # written between runs: 2 x L2
+
+    def timed(fn):
+        for _ in range(warm):
+            fn()
+        ts = []
+        for _ in range(reps):
+            flush.fill_(1)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        return statistics.median(ts)
+
+    pkg.lib.o1_launch_count(1)
+    eng.block(x, posd, 0)
+    launches = int(pkg.lib.o1_launch_count(1))
+    ms = timed(lambda: eng.block(x, posd, 0))
+    ms_adaln = timed(lambda: eng.block(x, posd, 0, mod6=mod))
+    assert pkg.lib.o1_device_error() == 0
+    _, sus, _, src = measured_peaks()
+    out = {"metric": "ms per decoder block (256 text + 1024 image tokens)", "value": round(ms, 4), "unit": "ms", "n_gpus": 1,
+           "steps": reps, "warmup": warm, "higher_is_better": False, "dtype": "bf16", "data": "synthetic",
+           "config": {"workload": "block: BASELINE config 0, one decoder block, S = 1280, weights N(0,0.02) seed 1234, "
+                                  "activations N(0,1) seed 42", "l2": "256 MB written between timed launches"},
+           "block_gflop": round(fl / 1e9, 1), "achieved_tflops": round(fl / ms / 1e9, 1),
+           "roofline": {"bound": "tensor", "kernel": "whole block (%d launches)" % launches, "achieved": round(fl / ms / 1e9, 1),
+                        "peak": sus, "unit": "TFLOP/s", "frac": round(fl / ms / 1e9 / sus, 4), "traffic": None,
+                        "peak_source": src + " (sustained bf16)"},
+           "adaln_variant_ms": round(ms_adaln, 4), "gpu_launches": launches}
+    if args.short:
+        return out
+    r = parity.reflib()
+    if r is not None:
+        sec = torch.tensor([24, 20, 20], dtype=torch.int64, device=dev)
+        mask = np.empty((S, S), dtype=np.uint16)
+        parity.oracle().orc_prefix_causal_mask(S, ar, parity.np_ptr(mask))
+        md = parity.u16_to_torch(mask, dev)
+        nbytes = r.hd_decoder_block_scratch_bytes(S, 32, 8, 4096, 12288, 128)
+        scratch = torch.empty(nbytes + 256, dtype=torch.uint8, device=dev)
+        o2 = torch.empty(S, H, dtype=torch.bfloat16, device=dev)
+        bb = w.block_binding(0)
+        plan = C.c_void_p()
+        rt = r.hd_gemm_runtime_init(0, 64 << 20)
+        if rt and r.hd_sdpa_create_prod(C.byref(plan), 1, 32, 8, S, ar, 128, 128 ** -0.5) == 0:
+            r.hd_gemm_set_backend(1)
+
+            def ref_block():
+                rc = r.hd_decoder_block(pkg.ptr(x), pkg.ptr(posd), pkg.ptr(md), C.byref(bb), pkg.ptr(sec), pkg.ptr(scratch),
+                                        nbytes, None, pkg.ptr(o2), S, 32, 8, 4096, 12288, 128, plan)
+                assert rc == 0, r.hd_last_error()
+            out["reference_cuda_build_ms"] = round(timed(ref_block), 4)
+            out["reference_backend"] = "cuBLASLt + cuDNN SDPA (two-pass), hd_decoder_block"
+            r.hd_sdpa_destroy(plan)
+        if rt:
+            r.hd_gemm_runtime_destroy(rt)
+    if not args.no_cpu_baseline:
+        hw = parity.HostWeights(pkg, 1, 1234, "A")
+        xh = parity.seeded_bf16((S, H), 42)
+        hw.block_struct(0)
+        t0 = time.perf_counter()
+        parity.oracle_block(hw, 0, xh, pos.numpy(), ar, want_ints=False)
+        dt = time.perf_counter() - t0
+        out["cpu_baseline"] = {"value": round(dt * 1e3, 1), "unit": "ms", "cores": parity.oracle().orc_num_threads(),
+                               "kind": "port", "sample": "the whole block once, C/OpenMP oracle"}
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + sorted(VISION_GRIDS) + ["elementwise"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + sorted(VISION_GRIDS) + ["elementwise", "block"])
     ap.add_argument("--layers", type=int, default=36)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--exchange", choices=("direct", "nccl"), default="direct",
@@ -732,6 +827,8 @@ def main():
     args = ap.parse_args()
     if args.workload == "elementwise":
         out = run_elementwise(args)
+    elif args.workload == "block":
+        out = run_block(args)
     elif args.workload in VISION_GRIDS:
         out = run_vision(args)     # one GPU, both arms in one line
     else:
