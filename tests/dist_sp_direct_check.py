@@ -5,7 +5,8 @@
 
 Every rank runs the same sharded forward twice, once with NCCL all-to-all exchanges and once with the
 direct form; rank 0 also runs the unsharded forward.  Prints one JSON line; exit code 0 only if the direct
-form equals the staged form bit for bit and the sharded forward matches the unsharded one."""
+form equals the staged form bit for bit and the sharded forward matches the unsharded one (bit for bit with
+attention's key split off, class D with the default policy)."""
 import argparse
 import json
 import os
@@ -82,16 +83,27 @@ def main():
                 torch.equal(direct2.view(torch.int16), staged.view(torch.int16)))
     ok = torch.tensor([int(same and err == 0)], device=dev)
     dist.all_reduce(ok, op=dist.ReduceOp.MIN)
-    rel = None
+    # Against the unsharded forward.  Attention cuts the items of a partly filled last wave along the keys
+    # (fp32 partials + merge), and whether that happens depends on heads-per-rank x query blocks, so the sharded
+    # and the unsharded forward may round differently (class C, measured 6.7e-3 at S = 1088).  With the split
+    # switched off everywhere the two are the same arithmetic and must agree bit for bit.
+    pkg.lib.o1_attention_tail_ways(1)
+    unsplit = run(direct_eng)
+    rel = rel_unsplit = None
     if rank == 0:
+        ref_unsplit = pkg.Engine(w, T, I).forward(idsd, posd, vin, 0.5).float()
+        rel_unsplit = float((unsplit.float() - ref_unsplit).norm() / ref_unsplit.norm())
+        pkg.lib.o1_attention_tail_ways(0)
         ref = pkg.Engine(w, T, I).forward(idsd, posd, vin, 0.5).float()
         rel = float((direct.float() - ref).norm() / ref.norm())
+    pkg.lib.o1_attention_tail_ways(0)
     dist.barrier()
     direct_eng.close()
     if rank == 0:
-        good = bool(ok.item()) and rel < 5e-3
+        good = bool(ok.item()) and rel_unsplit == 0.0 and rel < 1e-2
         print(json.dumps({"world": world, "S": S, "layers": args.layers, "direct_equals_staged": bool(ok.item()),
-                          "rel_l2_vs_unsharded": rel, "device_error": err, "ms_forward_staged": ms_staged,
+                          "rel_l2_vs_unsharded": rel, "rel_l2_vs_unsharded_without_key_split": rel_unsplit,
+                          "device_error": err, "ms_forward_staged": ms_staged,
                           "ms_forward_direct": ms_direct, "ok": good}))
         dist.destroy_process_group()
         sys.exit(0 if good else 1)
