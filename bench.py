@@ -764,7 +764,7 @@ def run_block(args):
     _, sus, _, src = measured_peaks()
     out = {"metric": "ms per decoder block (256 text + 1024 image tokens)", "value": round(ms, 4), "unit": "ms", "n_gpus": 1,
            "steps": reps, "warmup": warm, "higher_is_better": False, "dtype": "bf16", "data": "synthetic",
-           "config": {"workload": "block: BASELINE config 0, one decoder block, S = 1280, weights N(0,0.02) seed 1234, "
+           "config": {"workload": "block: one decoder block, 256 text + 1024 image tokens (S = 1280), weights N(0,0.02) seed 1234, "
                                   "activations N(0,1) seed 42", "l2": "256 MB written between timed launches"},
            "block_gflop": round(fl / 1e9, 1), "achieved_tflops": round(fl / ms / 1e9, 1),
            "roofline": {"bound": "tensor", "kernel": "whole block (%d launches)" % launches, "achieved": round(fl / ms / 1e9, 1),

@@ -352,7 +352,7 @@ typedef struct {
         *down_proj, *q_norm, *k_norm;
 } orc_block_weights;
 
-/* adaLN pieces of the modulated block variant (BASELINE config 0; no counterpart in o1.c, whose blocks are
+/* adaLN pieces of the modulated block variant (no counterpart in o1.c, whose blocks are
  * unmodulated -- "parity unpinned": these define the arithmetic the CUDA variant is checked against).
  * mod = [shift_msa | scale_msa | gate_msa | shift_mlp | scale_mlp | gate_mlp], each [hidden] bf16. */
 static void orc_modulate(uint16_t *x, const uint16_t *shift, const uint16_t *scale, int rows, int cols) {
