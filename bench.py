@@ -45,6 +45,30 @@ STEPS_PER_IMAGE = 28
 GUIDANCE = 5.0
 
 
+METRICS = {
+    # BASELINE's names: its 1024^2 / 2048^2 images are the 64x64 / 128x128 token grids
+    "c2": "sec/image 2048^2 28-step CFG T2I",
+    "c1": "sec/image 1024^2 28-step CFG T2I",
+    "c0": "sec/image 28-step CFG T2I at 1024 image tokens",
+    "c3": "sec/image 2048^2 28-step CFG multi-reference edit (4 references)",
+    "c4": "sec/image 1024^2 28-step CFG T2I, LoRA-merged weights",
+}
+
+
+def metric_name(workload):
+    """The headline metric is quoted on c2; the other workloads carry their own name."""
+    return METRICS[workload]
+
+
+def workload_desc(workload, layers):
+    """One string for both arms, so that their lines can be matched mechanically."""
+    T, gh, gw = WORKLOADS[workload]
+    I = gh * gw + (sum(r[0] for r in C3_REFS) if workload == "c3" else 0)
+    return (f"{workload}: {I} image tokens ({gh}x{gw}" + (" target + 4 references of 64x64" if workload == "c3" else "")
+            + f") + {T} text tokens, {layers} decoder blocks, CFG (2 forwards/step), guidance {GUIDANCE}, "
+            "flow-match Euler, Dev sigmas")
+
+
 def flops_block(S, ar):
     gemm = 385875968.0 * S
     keys = 0.5 * ar * (ar + 1.0) + (S - ar) * float(S)
@@ -166,6 +190,7 @@ def run_ours(args):
     assert lib.o1_fill_normal_bf16(pkg.ptr(z), z.numel(), 42 + 1 + (rank if is_lora else 0), 0.0, 8.0) == 0
     if is_ref:
         z[I_tgt:].mul_(0.125)               # reference pixel rows ~ N(0,1); the target latent stays ~ N(0,64)
+    z_initial = z                              # all image rows (the sharded layouts below keep their own slice)
     z_next = z.clone() if is_ref else torch.empty_like(z)
     z_host = z.cpu().pin_memory()
     z_next_host = torch.empty_like(z_host).pin_memory()
@@ -217,6 +242,18 @@ def run_ours(args):
         xp_local = torch.empty(eng.rows, 3072, dtype=torch.bfloat16, device=dev)
         xp_pair = torch.empty(2, i1 - i0, 3072, dtype=torch.bfloat16, device=dev)
         n_step_local = max(0, min(I_tgt, i1) - i0)      # local image rows that are target (stepped) rows
+        # whole step in one library call per rank (o1_denoise_step_cfg_sp): C-driven forward, predictions exchanged
+        # with the CFG partner by peer copies + a two-rank flag barrier instead of an NCCL all-gather
+        pair_link = None
+        if eng.direct and eng.peers is not None and not args.py_driver:
+            eng.c_driver = True
+            link = spmod.CfgPairLink(eng, branch, cfg_group)
+            if link.ok:
+                pair_link = link
+            else:
+                link.close()
+    else:
+        pair_link = None
     xp_both = torch.empty(2, S, 3072, dtype=torch.bfloat16, device=dev) if (pair and sp_size == 1) else None
 
     def step_device(i, zin, zout):
@@ -235,6 +272,17 @@ def run_ours(args):
             # reference rows (c3) are static: only the target rows are stepped
             rc = lib.o1_sched_cfg_flow_step(pkg.ptr(zin), pkg.ptr(xp_both[0, T:]), pkg.ptr(xp_both[1, T:]), s0, s1,
                                             GUIDANCE, pkg.ptr(zout), I_tgt * 3072)
+        elif pair_link is not None:
+            c = eng.ctx()
+            c.epoch = max(c.epoch, eng.epoch)
+            eng.timestep.fill_(1.0 - s0)
+            rc = lib.o1_denoise_step_cfg_sp(C.byref(w.binding), C.byref(c), C.byref(pair_link.pair), pkg.ptr(ids_b),
+                                            pkg.ptr(posd), pkg.ptr(zin) if zin.numel() else None, n_step_local,
+                                            pkg.ptr(eng.timestep), s0, s1, GUIDANCE, pkg.TMS_ID, pkg.ptr(xp_local),
+                                            pkg.ptr(zout) if zout.numel() else None)
+            eng.epoch = c.epoch
+            if rc != 0:
+                raise RuntimeError("o1_denoise_step_cfg_sp: " + pkg.last_error())
         else:
             eng.forward(ids_b, posd, zin if zin.numel() else None, 1.0 - s0, out_local=xp_local)
             mine = xp_local[n_text_local:]
@@ -301,7 +349,7 @@ def run_ours(args):
                            "tflops": round(wk.value / ms.value / 1e9, 1)}
 
     # ---- end to end through host buffers (H2D of the latent + D2H of the result inside the timed region)
-    e2e_steps = 0 if args.short else max(1, min(args.steps, 3))
+    e2e_steps = 0 if args.short else args.steps            # the same number of steps as the device-timed region
     e2e_ms = float("nan")
     if e2e_steps:
         step_host(0)
@@ -316,6 +364,19 @@ def run_ours(args):
         dist.all_reduce(te, op=dist.ReduceOp.MAX)
     e2e_ms = float(te.item())
 
+    # ---- parity of what was just timed (outside every timed region)
+    parity_rec = None
+    if not args.short and not args.no_parity:
+        if sp_size > 1:
+            # the sharded forward against the unsharded one on the same inputs, every rank on its own rows
+            parity_rec = sharded_vs_unsharded(pkg, dist, dev, eng, w, T, I, ar, posd, ids_u if branch else ids_c,
+                                              z_initial, xp_local, world)
+        elif world == 1 and args.workload in ("c1", "c2"):
+            parity_rec = reference_probe(T, gh, gw, local)
+    extras = None
+    if world == 1 and args.workload == "c2" and not args.short and not args.no_extras and layers == 36:
+        extras = other_workloads(pkg, w, dev)
+
     images = n_images                                # images in flight (1 unless more GPUs than one image uses)
     sec_per_image = ms_step * STEPS_PER_IMAGE / 1e3 / images
     e2e_sec = e2e_ms * STEPS_PER_IMAGE / 1e3 / images
@@ -328,18 +389,19 @@ def run_ours(args):
         per_launch_ms = top[1]["ms_total"] / top[1]["launches"]
         achieved = top[1]["tflops"]
         out = {
-            "metric": "sec/image 2048^2 28-step CFG T2I", "value": round(sec_per_image, 4), "unit": "s/image",
+            "metric": metric_name(args.workload), "value": round(sec_per_image, 4), "unit": "s/image",
             "n_gpus": world, "steps": args.steps, "warmup": warm, "ms_per_step": round(ms_step, 3),
             "higher_is_better": False, "scaling": "strong" if images == 1 else "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"{args.workload}: {I} image tokens ({gh}x{gw}"
-                                   + (" target + 4 references of 64x64" if is_ref else "") + f") + {T} text tokens, "
-                                   f"{layers} decoder blocks, CFG (2 forwards/step), guidance {GUIDANCE}, "
-                                   f"flow-match Euler, Dev sigmas",
+            "config": {"workload": workload_desc(args.workload, layers),
                        "seq_len": S, "layers": layers, "steps_per_image": STEPS_PER_IMAGE,
                        "parallelism": "1 GPU" if world == 1 else
                                       (f"dp{images} (one image per GPU)" if is_lora else f"cfg pair x ulysses sp{sp_size}"
                                        + (f" x dp{images}" if images > 1 else "")),
+                       "sp_driver": (None if sp_size == 1 else
+                                     ("one o1_denoise_step_cfg_sp call per step (C loop, peer copies of the predictions)"
+                                      if pair_link is not None else "stage functions driven from Python, NCCL all-gather of "
+                                      "the predictions")),
                        "sp_exchange": (None if sp_size == 1 else
                                        ("peer stores from the GEMM / attention epilogues + flag barriers"
                                         if args.exchange == "direct" else "NCCL all-to-all"
@@ -355,6 +417,9 @@ def run_ours(args):
                     "d2h_bytes_per_step": I * 3072 * 2 * (2 if pair else 1) * images},
             "gpu_launches": int(launches),
             "clocks": clocks,
+            # step time x median SM clock under load: compares runs (and GPU counts) whose power-capped clocks differ
+            "ms_per_step_x_sm_mhz": (round(ms_step * clocks["sm_mhz"], 1) if clocks and clocks.get("sm_mhz") else None),
+            "parity": parity_rec,
             "roofline": {"bound": "tensor", "kernel": top[0], "achieved": achieved, "peak": sustained,
                          "unit": "TFLOP/s", "frac": round(achieved / sustained, 4),
                          "traffic": NCU_TRAFFIC_BYTES.get((args.workload, top[0])) if world == 1 else None,
@@ -362,6 +427,8 @@ def run_ours(args):
                          "ms_per_launch": round(per_launch_ms, 4)},
             "kernels": kinds,
         }
+        if extras is not None:
+            out["configs"] = extras
         if lora_ms is not None:
             out["lora_merge_ms"] = round(lora_ms, 2)
             out["config"]["lora"] = "rank 64, A,B ~ N(0,0.01), alpha 64, merged into the 7 linears of every block"
@@ -373,6 +440,143 @@ def run_ours(args):
     if world > 1:
         dist.destroy_process_group()
     return out
+
+
+def reference_probe(T, gh, gw, device_index):
+    """tests/parity_probe.py as a child process: a 2-block forward at this geometry through the library and
+    through the reference's production CUDA build (when oracle/_ref holds it), x_pred compared."""
+    cmd = [sys.executable, os.path.join(ROOT, "tests", "parity_probe.py"), "--text", str(T), "--grid-h", str(gh),
+           "--grid-w", str(gw), "--layers", "2", "--device", str(device_index)]
+    try:
+        p = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+        line = [l for l in p.stdout.splitlines() if l.startswith("{")]
+        return json.loads(line[-1]) if line else {"status": "error: no output", "stderr": p.stderr[-300:]}
+    except Exception as ex:      # noqa: BLE001
+        return {"status": f"error: {type(ex).__name__}: {ex}"}
+
+
+def sharded_vs_unsharded(pkg, dist, dev, eng_sp, w, T, I, ar, posd, ids, z_full, xp_local, world):
+    """x_pred of the sequence-parallel forward against the single-GPU forward of the same branch on the same
+    (initial) latent: every rank runs the unsharded forward itself (it holds all weights) and compares its own
+    rows; the squared sums are reduced over all ranks, i.e. over both branches and all row shards."""
+    import torch
+    t = 0.5
+    z_local = z_full[eng_sp.i0:eng_sp.i1].contiguous()
+    eng_sp.forward(ids, posd, z_local if z_local.numel() else None, t, out_local=xp_local)
+    torch.cuda.synchronize()
+    eng1 = pkg.Engine(w, T, I, ar_len=ar)
+    full = eng1.forward(ids, posd, z_full, t)
+    torch.cuda.synchronize()
+    mine = xp_local.double()
+    want = full[eng_sp.row0:eng_sp.row0 + eng_sp.rows].double()
+    acc = torch.stack([((mine - want) ** 2).sum(), (want ** 2).sum(), (mine * want).sum(), (mine ** 2).sum(),
+                       (~torch.isfinite(mine)).sum().double()])
+    dist.all_reduce(acc)
+    d2, r2, gr, g2, bad = (float(v) for v in acc)
+    nrmse = (d2 / r2) ** 0.5 if r2 > 0 else 0.0
+    cos = gr / ((g2 * r2) ** 0.5) if g2 > 0 and r2 > 0 else 0.0
+    del eng1
+    return {"against": "the unsharded forward of this library on the same inputs (all ranks, both branches)",
+            "x_pred": {"nrmse": round(nrmse, 6), "cos": round(cos, 7), "nonfinite": int(bad)},
+            "status": "pass" if (nrmse <= 2e-2 and cos >= 0.995 and bad == 0) else "FAIL"}
+
+
+def other_workloads(pkg, w, dev):
+    """Short live measurements of the other BASELINE workloads on this GPU with the weights already resident
+    (3 timed steps after 2 warm-ups each, CUDA events); c4 runs last because the merge rewrites the weights."""
+    import torch
+    lib = pkg.lib
+    res = {}
+    sig = pkg.dev_sigmas()
+
+    def time_steps(fn, warm=2, n=3):
+        for i in range(warm):
+            fn(i)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for i in range(n):
+            fn(i)
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / n
+
+    def t2i(workload, seed_off):
+        T, gh, gw = WORKLOADS[workload]
+        I = gh * gw
+        pos, ar = pkg.seq_t2i(T, gh, gw)
+        eng = pkg.Engine(w, T, I, ar_len=ar)
+        g = torch.Generator().manual_seed(7)
+        ic = torch.randint(0, 151000, (T,), generator=g, dtype=torch.int64)
+        iu = torch.randint(0, 151000, (T,), generator=g, dtype=torch.int64)
+        ic[-1] = iu[-1] = pkg.TMS_ID
+        ic, iu, posd = ic.to(dev), iu.to(dev), pos.to(dev)
+        z = torch.empty(I, 3072, dtype=torch.bfloat16, device=dev)
+        lib.o1_fill_normal_bf16(pkg.ptr(z), z.numel(), 43 + seed_off, 0.0, 8.0)
+        zn = torch.empty_like(z)
+        ms = time_steps(lambda i: eng.denoise_step_cfg(ic, iu, posd, z, sig[i], sig[i + 1], GUIDANCE, zn))
+        assert bool(torch.isfinite(zn.float()).all())
+        return ms, 2 * flops_forward(T, I, w.n_layers)
+
+    try:
+        ms, fl = t2i("c1", 0)
+        res["c1"] = {"metric": metric_name("c1"), "value": round(ms * STEPS_PER_IMAGE / 1e3, 4), "unit": "s/image",
+                     "ms_per_step": round(ms, 3), "tflops": round(fl / ms / 1e9, 1),
+                     "parity": "tests/test_gpu_scale_parity.py: 36-block forward and 28-step chain at these rows "
+                               "against the reference CUDA build"}
+        # c0: one decoder block at 256 + 1024 tokens
+        T, gh, gw = WORKLOADS["c0"]
+        eng = pkg.Engine(w, T, gh * gw)
+        pos, ar = pkg.seq_t2i(T, gh, gw)
+        x = torch.empty(eng.S, pkg.HIDDEN, dtype=torch.bfloat16, device=dev)
+        lib.o1_fill_normal_bf16(pkg.ptr(x), x.numel(), 42, 0.0, 1.0)
+        posd = pos.to(dev)
+        ms = time_steps(lambda i: eng.block(x, posd, 0), warm=3, n=10)
+        res["c0"] = {"metric": "ms per decoder block (256 text + 1024 image tokens)", "value": round(ms, 4), "unit": "ms",
+                     "tflops": round(flops_block(eng.S, ar) / ms / 1e9, 1), "l2": "not flushed (back-to-back launches)",
+                     "parity": "tests/test_gpu_block.py: this shape against the oracle and the reference CUDA build"}
+        del eng
+        # c3: K = 4 references, S = 33280
+        T, gh, gw = WORKLOADS["c3"]
+        I_tgt = gh * gw
+        I = I_tgt + sum(r[0] for r in C3_REFS)
+        g = torch.Generator().manual_seed(7)
+        ic = torch.randint(0, 151000, (T,), generator=g, dtype=torch.int64)
+        iu = torch.randint(0, 151000, (T,), generator=g, dtype=torch.int64)
+        ic[-1] = iu[-1] = pkg.TMS_ID
+        for ids in (ic, iu):
+            o = 8
+            for (_, _, _, ch, cw) in C3_REFS:
+                ids[o] = 151652
+                ids[o + 1:o + 1 + ch * cw] = 151655
+                o += 1 + ch * cw + 3
+            ids[-2] = 151669
+        _, pos, ar = pkg.seq_ref(ic.tolist(), C3_REFS, gh, gw)
+        eng = pkg.Engine(w, T, I, ar_len=ar)
+        ic, iu, posd = ic.to(dev), iu.to(dev), pos.to(dev)
+        z = torch.empty(I, 3072, dtype=torch.bfloat16, device=dev)
+        lib.o1_fill_normal_bf16(pkg.ptr(z), z.numel(), 43, 0.0, 8.0)
+        z[I_tgt:].mul_(0.125)
+        zn = z.clone()
+        ms = time_steps(lambda i: eng.denoise_step_cfg_ref(ic, iu, posd, z, I_tgt, sig[i], sig[i + 1], GUIDANCE, zn),
+                        warm=1, n=2)
+        res["c3"] = {"metric": metric_name("c3"), "value": round(ms * STEPS_PER_IMAGE / 1e3, 3), "unit": "s/image",
+                     "ms_per_step": round(ms, 2), "tflops": round(2 * flops_forward(T, I, w.n_layers) / ms / 1e9, 1),
+                     "seq_len": T + I,
+                     "parity": "tests/test_gpu_forward.py: the K = 4 layout with visual conditioning against the oracle at "
+                               "small size; the reference build cannot run this size (its S x S score buffers need 142 GB)"}
+        del eng, z, zn
+        torch.cuda.empty_cache()
+        # c4: rank-64 LoRA merged into every block linear, then the c1 shapes
+        merge_ms = merge_synthetic_lora(pkg, w, w.n_layers, dev)
+        ms, fl = t2i("c4", 1)
+        res["c4"] = {"metric": metric_name("c4"), "value": round(ms * STEPS_PER_IMAGE / 1e3, 4), "unit": "s/image",
+                     "ms_per_step": round(ms, 3), "lora_merge_ms": round(merge_ms, 2), "images_per_gpu": 1,
+                     "parity": "tests/test_gpu_lora.py: merge against the reference's Python contract fixture; "
+                               "forward kernels as c1"}
+    except Exception as ex:      # noqa: BLE001 -- the headline line must survive a failure here
+        res["error"] = f"{type(ex).__name__}: {ex}"
+    return res
 
 
 def merge_synthetic_lora(pkg, w, layers, dev):
@@ -434,76 +638,46 @@ def run_reference(args):
     unchanged into oracle/_ref/libo1ref.so, driven through hd_forward x2 -> hd_sched_vcond x2 ->
     hd_sched_cfg_guided -> hd_sched_flow_match_step (the composition of src/runtime/generate.c).
     The reference has no CPU implementation of this path; if its library is unavailable or fails,
-    the C/OpenMP port is timed on the host cores instead."""
+    the C/OpenMP port is timed on the host cores instead.
+
+    This arm never loads the product library: weights are generated on the host by the oracle's generator
+    (bit-identical to the device-side fill of the other arm) and copied to the device, positions and sigmas
+    come from the oracle, and the step is driven through tests/refharness.py."""
     rank, world, local = dist_env()
     if rank != 0:
         return None
     import torch
-    import numpy as np
     import parity
-    from __graft_entry__ import load_package
-    pkg = load_package()
+    import refharness as rh
+    if args.workload not in ("c0", "c1", "c2"):
+        return {"impl": "reference", "unavailable": "the reference build cannot run this workload: its S x S score "
+                                                    "buffers exceed the GPU's memory (c3) / it has no LoRA GPU merge that "
+                                                    "is safe to run (c4: lora_merge.cu:86-93 reads beyond the adapter)"}
     T, gh, gw = WORKLOADS[args.workload]
     I, S, layers = gh * gw, T + gh * gw, args.layers
     fl_step = 2 * flops_forward(T, I, layers)
-    base = {"metric": "sec/image 2048^2 28-step CFG T2I", "unit": "s/image", "n_gpus": world, "steps": args.steps,
+    base = {"metric": metric_name(args.workload), "unit": "s/image", "n_gpus": world, "steps": args.steps,
             "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic", "impl": "reference"}
-    r = parity.reflib()
     err = None
-    if r is not None and torch.cuda.is_available():
+    if parity.reflib() is not None and torch.cuda.is_available():
         try:
             torch.cuda.set_device(local)
             dev = torch.device("cuda", local)
-            pkg.use_torch_stream()
-            w = pkg.Weights(n_layers=layers, seed=1234, weight_set="A", device=dev)
-            pos, ar = pkg.seq_t2i(T, gh, gw)
-            posd = pos.to(dev)
-            g = torch.Generator().manual_seed(7)
-            ids_c = torch.randint(0, 151000, (T,), generator=g, dtype=torch.int64)
-            ids_u = torch.randint(0, 151000, (T,), generator=g, dtype=torch.int64)
-            ids_c[-1] = ids_u[-1] = pkg.TMS_ID
-            ids_c, ids_u = ids_c.to(dev), ids_u.to(dev)
-            z = torch.empty(I, 3072, dtype=torch.bfloat16, device=dev)
-            pkg.lib.o1_fill_normal_bf16(pkg.ptr(z), z.numel(), 43, 0.0, 8.0)
+            t0 = time.perf_counter()
+            w = rh.HostFilledWeights(layers, dev, seed=1234, weight_set="A")
+            fill_s = time.perf_counter() - t0
+            reng = rh.RefEngine(w.binding, T, gh, gw, dev, production=True)
+            ids_c, ids_u = (t.to(dev) for t in rh.seeded_ids(T, 7))
+            z_host = rh.seeded_latent(I, 43, 8.0).pin_memory()
+            z = z_host.to(dev)
             zn = torch.empty_like(z)
-            bs = C.c_int64(0)
-            nbytes = r.hd_forward_workspace_bytes(S, I, 32, 8, 4096, 12288, 128, C.byref(bs))
-            buf = torch.empty(nbytes + 256, dtype=torch.uint8, device=dev)
-            ws = pkg.ForwardWorkspace()
-            ws.hidden_a, ws.block_scratch_bytes = buf.data_ptr(), bs.value
-            rt = r.hd_gemm_runtime_init(local, 64 << 20)
-            if not rt:
-                raise RuntimeError("hd_gemm_runtime_init failed")
-            r.hd_gemm_set_backend(1)
-            plan = C.c_void_p()
-            if r.hd_sdpa_create_prod(C.byref(plan), 1, 32, 8, S, ar, 128, 128 ** -0.5) != 0:
-                raise RuntimeError("hd_sdpa_create_prod failed: %s" % r.hd_cuda_last_error())
-            ws.sdpa = plan
-            # prefix-causal mask tensor [S,S] bf16 (only row structure matters to the split plan)
-            rows = torch.arange(S, device=dev)
-            mask = ((rows[None, :] > rows[:, None]) & (rows[:, None] < ar)).to(torch.int16) * -129
-            sec = torch.tensor([24, 20, 20], dtype=torch.int64, device=dev)
-            tt = torch.zeros(1, device=dev)
-            xc = torch.empty(S, 3072, dtype=torch.bfloat16, device=dev)
-            xu = torch.empty_like(xc)
-            mc, mu, mo = (torch.empty(I * 3072, device=dev) for _ in range(3))
-            sig = pkg.dev_sigmas()
+            z_stage = torch.empty_like(z)
+            zn_host = torch.empty_like(z_host).pin_memory()
+            sig = rh.dev_sigmas()
 
             def step(i, zin, zout):
-                s0, s1 = sig[i % 28], sig[i % 28 + 1]
-                tt.fill_(1.0 - s0)
-                for ids, xo in ((ids_c, xc), (ids_u, xu)):
-                    rc = r.hd_forward(C.byref(w.binding), C.byref(ws), pkg.ptr(ids), T, pkg.ptr(posd), pkg.ptr(mask),
-                                      pkg.ptr(zin), I, None, pkg.ptr(tt), pkg.ptr(sec), S, 32, 8, 4096, 12288, 128,
-                                      pkg.TMS_ID, None, pkg.ptr(xo), None)
-                    if rc != 0:
-                        raise RuntimeError("reference hd_forward failed: %s" % r.hd_last_error())
-                n = I * 3072
-                r.hd_sched_vcond(pkg.ptr(zin), pkg.ptr(xc[T:]), s0, pkg.ptr(mc), n)
-                r.hd_sched_vcond(pkg.ptr(zin), pkg.ptr(xu[T:]), s0, pkg.ptr(mu), n)
-                r.hd_sched_cfg_guided(pkg.ptr(mc), pkg.ptr(mu), GUIDANCE, pkg.ptr(mo), n)
-                r.hd_sched_flow_match_step(pkg.ptr(zin), pkg.ptr(mo), s0, s1, pkg.ptr(zout), n)
+                reng.cfg_step(ids_c, ids_u, zin, zout, sig[i % 28], sig[i % 28 + 1], GUIDANCE)
 
             warm = max(3, args.warmup)
             cur, nxt = z, zn
@@ -511,6 +685,9 @@ def run_reference(args):
                 step(i, cur, nxt)
                 cur, nxt = nxt, cur
             torch.cuda.synchronize()
+            sampler = ClockSampler(local if "CUDA_VISIBLE_DEVICES" not in os.environ else
+                                   int(os.environ["CUDA_VISIBLE_DEVICES"].split(",")[local]))
+            sampler.start()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
             for i in range(args.steps):
@@ -518,26 +695,45 @@ def run_reference(args):
                 cur, nxt = nxt, cur
             e1.record()
             torch.cuda.synchronize()
+            clocks = sampler.stop()
             ms_step = e0.elapsed_time(e1) / args.steps
+            assert bool(torch.isfinite(cur.float()).all()), "latent went non-finite"
+            # end to end: the step's latent comes from pinned host memory and the result goes back, every step
+            t0 = time.perf_counter()
+            for i in range(args.steps):
+                z_stage.copy_(z_host, non_blocking=True)
+                step(i, z_stage, zn)
+                zn_host.copy_(zn, non_blocking=True)
+                torch.cuda.synchronize()
+            e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+            reng.close()
             val = ms_step * STEPS_PER_IMAGE / 1e3
             base.update({
                 "value": round(val, 4), "warmup": warm, "ms_per_step": round(ms_step, 3),
-                "config": {"workload": f"{args.workload}: {I} image tokens + {T} text tokens, {layers} blocks, CFG",
-                           "seq_len": S, "layers": layers,
-                           "backend": "reference CUDA build on this GPU: cuBLASLt GEMM + cuDNN SDPA (two-pass)"},
+                "config": {"workload": workload_desc(args.workload, layers), "seq_len": S, "layers": layers,
+                           "steps_per_image": STEPS_PER_IMAGE,
+                           "backend": "reference CUDA build on this GPU: cuBLASLt GEMM + cuDNN SDPA (two-pass)",
+                           "weights": "random-init N(0,0.02) bf16, seed 1234 (generated on the host by the oracle's "
+                                      "generator in %.1f s, the same bytes as the other arm's device fill)" % fill_s,
+                           "product_library_loaded": "libo1b200" in open("/proc/self/maps").read()},
                 "achieved_tflops": round(fl_step / ms_step / 1e9, 1),
+                "clocks": clocks,
+                "ms_per_step_x_sm_mhz": (round(ms_step * clocks["sm_mhz"], 1) if clocks.get("sm_mhz") else None),
                 "cpu_baseline": {"value": round(val, 4), "unit": "s/image", "cores": 0, "kind": "reference",
                                  "sample": "the reference has no CPU implementation of this path; this is its own "
                                            "CUDA build (oracle/_ref) on the same GPU, full workload"},
-                "e2e": {"value": round(val, 4), "unit": "s/image", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "e2e": {"value": round(e2e_ms * STEPS_PER_IMAGE / 1e3, 4), "unit": "s/image",
+                        "h2d_bytes_per_step": I * 3072 * 2, "d2h_bytes_per_step": I * 3072 * 2},
             })
             return base
         except Exception as ex:      # noqa: BLE001 -- report and fall through to the CPU port
             err = f"{type(ex).__name__}: {ex}"
-    # CPU port of the path on the host cores
-    cb = cpu_baseline(pkg, fl_step)
+    # CPU port of the path on the host cores (the oracle is test infrastructure; this is the one place besides
+    # cpu_baseline() where the bench executes it)
+    from __graft_entry__ import load_package
+    cb = cpu_baseline(load_package(), fl_step)
     base.update({"value": cb["value"], "warmup": 0, "ms_per_step": round(cb["value"] / STEPS_PER_IMAGE * 1e3, 1),
-                 "config": {"workload": f"{args.workload}: {I} image tokens + {T} text tokens, {layers} blocks, CFG",
+                 "config": {"workload": workload_desc(args.workload, layers),
                             "backend": "C/OpenMP port on host cores" + (f" (reference CUDA build failed: {err})" if err else "")},
                  "cpu_baseline": cb,
                  "e2e": {"value": cb["value"], "unit": "s/image", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}})
@@ -818,9 +1014,15 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + sorted(VISION_GRIDS) + ["elementwise", "block"])
     ap.add_argument("--layers", type=int, default=36)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-parity", action="store_true", help="skip the parity check that follows the timed region")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the short measurements of the other workloads that follow the c2 run on one GPU")
     ap.add_argument("--exchange", choices=("direct", "nccl"), default="direct",
                     help="Ulysses exchanges at 4 / 8 GPUs: stores into the peers' buffers from the producing "
                          "kernels (default) or NCCL all-to-all between the stage kernels")
+    ap.add_argument("--py-driver", action="store_true",
+                    help="sharded runs: drive the stage functions from Python and all-gather the predictions with NCCL "
+                         "instead of one o1_denoise_step_cfg_sp call per step")
     ap.add_argument("--short", action="store_true",
                     help="profiler runs only: take --warmup literally, skip the end-to-end and CPU legs "
                          "(a number from such a run is not a benchmark value)")

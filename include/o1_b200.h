@@ -530,6 +530,27 @@ hd_status o1_denoise_step_cfg_ref(const hd_forward_binding *bw, hd_forward_works
                                   float sigma, float sigma_next, float guidance, void *xp_scratch, void *z_next,
                                   int heads, int kv_heads, int hidden, int ff_hidden, int head_dim,
                                   int tms_token_id);
+/* The same step with a sequence of its own per branch, as the reference's CFG loop has it: the unconditional
+ * prompt is tokenised separately and is normally shorter (src/runtime/generate.c:1111-1206 seq_text_len[1],
+ * posd[1], seq_S_uncond; :1340-1356 runs and slices that branch at its own text length).  Padding the shorter
+ * prompt instead would let image rows attend to the pad rows.  Each branch: ids [text_len] int64, pos_f32
+ * [3, text_len + img_tokens], ar_len (text_len - 1 for T2I), visual (may be NULL).  ws (one workspace, used by
+ * both branches in turn) must come from hd_forward_workspace_bytes of the LONGER sequence; xp_scratch holds
+ * (S_cond + S_uncond) * 3072 bf16.  The scheduler update is the flow-match Euler step; the reference's own
+ * CFG path steps with FlowUniPC (generate.c:1362-1416), which a host composes from hd_forward, hd_sched_vcond,
+ * hd_sched_cfg_guided and hd_unipc_* exactly as there. */
+typedef struct {
+    const int64_t *ids;
+    int text_len;
+    const float *pos_f32;
+    int ar_len;
+    const hd_visual_cond *visual;
+} o1_cfg_branch;
+hd_status o1_denoise_step_cfg_branches(const hd_forward_binding *bw, hd_forward_workspace *ws,
+                                       const o1_cfg_branch *cond, const o1_cfg_branch *uncond, const void *z,
+                                       int img_tokens, int target_tokens, const float *timestep_dev, float sigma,
+                                       float sigma_next, float guidance, void *xp_scratch, void *z_next, int heads,
+                                       int kv_heads, int hidden, int ff_hidden, int head_dim, int tms_token_id);
 /* Same step with HOST latents: copies z_host -> device, runs the step, copies
  * z_next back and synchronises.  z_dev / z_next_dev are caller-owned staging. */
 hd_status o1_denoise_step_cfg_host(const hd_forward_binding *bw, hd_forward_workspace *ws,
@@ -585,7 +606,9 @@ hd_status o1_decode_to_rgb(const void *z_dev, int grid_h, int grid_w, int patch,
  *   gath [S][C]               row block s = slab received from rank s   (C = (heads+2*kv_heads)*128/sp_size)
  *   attn [S][Hc]              row block d = slab sent to rank d          (Hc = heads*128/sp_size)
  *   recv [sp_size][rows][Hc]  slab s = this rank's rows of the heads rank s owns.
- * With sp_size == 1, send == gath and attn == recv may alias and no exchange is needed. */
+ * With sp_size == 1, send == gath and attn == recv may alias and no exchange is needed.
+ * sp_size is at most O1_SP_MAX_RANKS (the peer tables below and the kernels' destination tables hold that many). */
+#define O1_SP_MAX_RANKS 8
 typedef struct {
     int sp_size, sp_rank;
     int S, T;          /* global token count, text token count */
@@ -616,19 +639,20 @@ hd_status o1_sp_deepstack(const o1_sp_ws *w, const uint8_t *mask_global, const v
 
 /* Direct form of the two exchanges: no collective call and no staging copy.  Each rank maps its peers' gath
  * [S][C] and recv [P][rows][Hc] buffers and a small flag array (CUDA IPC: o1_peer_*; in a C host
- * cudaIpcGetMemHandle / cudaIpcOpenMemHandle directly).  o1_sp_block_pre_direct's q/k/v GEMM epilogues store head
- * group p straight into rank p's gath; o1_sp_block_attn_direct applies the per-head norm + rope on the received
- * rows and its attention epilogue stores row block p straight into rank p's recv; o1_sp_block_post is unchanged.
+ * cudaIpcGetMemHandle / cudaIpcOpenMemHandle directly).  o1_sp_block_pre_direct's q/k/v GEMM epilogues apply the
+ * per-head norm + rope to their own rows (cos|sin from o1_sp_rope_table) and store head group p straight into
+ * rank p's gath; o1_sp_block_attn_direct's attention epilogue stores row block p straight into rank p's recv;
+ * o1_sp_block_post is unchanged.
  * Results are bit-identical to the staged form.  Call order per block on every rank:
  *   pre_direct, barrier(e), attn_direct, barrier(e+1), post      (e grows by 2 per block, never reused)
  * The barrier is a kernel on the current stream that release-stores the epoch into every peer's flag array and
  * polls its own; its wait is bounded (device error code 30 after about two seconds).  Ranks must be on different
  * GPUs (two ranks' barrier kernels on one GPU would wait for each other without being co-scheduled). */
 typedef struct {
-    void *gath[8];      /* rank p's gath buffer as mapped in this process ([sp_rank] = the local one)   */
-    void *recv[8];      /* rank p's recv buffer                                                         */
-    void *flags[8];     /* rank p's flag array: 8 x uint32, zero-initialised                            */
-    void *rope_full;    /* local: cos|sin table of all S rows, fp32 [S,128]                             */
+    void *gath[O1_SP_MAX_RANKS];      /* rank p's gath buffer as mapped in this process ([sp_rank] = the local one)   */
+    void *recv[O1_SP_MAX_RANKS];      /* rank p's recv buffer                                                         */
+    void *flags[O1_SP_MAX_RANKS];     /* rank p's flag array: 8 x uint32, zero-initialised                            */
+    void *rope_full;    /* optional: cos|sin table of all S rows (o1_sp_rope_table_full); the forward does not need it */
 } o1_sp_peers;
 int o1_peer_alloc(void **dev_ptr, size_t bytes);                 /* cudaMalloc + zero fill */
 int o1_peer_free(void *dev_ptr);
@@ -639,6 +663,47 @@ hd_status o1_sp_rope_table_full(const o1_sp_ws *w, const o1_sp_peers *pt, const 
 hd_status o1_sp_block_pre_direct(const hd_block_binding *bw, const o1_sp_ws *w, const o1_sp_peers *pt, const void *in);
 hd_status o1_sp_block_attn_direct(const hd_block_binding *bw, const o1_sp_ws *w, const o1_sp_peers *pt);
 hd_status o1_sp_barrier(const o1_sp_ws *w, const o1_sp_peers *pt, unsigned epoch);
+
+
+/* The whole sharded forward of one rank in one call (direct form): what a C host would otherwise loop over the
+ * stage functions above -- the counterpart, for a multi-GPU host, of the single hd_forward call in
+ * src/runtime/generate.c:1323-1327.  ctx carries the workspace, the peer table, two [rows, hidden] buffers, the
+ * scratch of o1_sp_forward_begin and the barrier epoch (start at 0; the library advances it).  Visual
+ * conditioning: visual_mask [S] uint8 on the device, image_embeds / deepstack [V, hidden], embed_row0 = marked rows
+ * before this rank's rows, visual_rows = marked rows among this rank's rows (0: nothing to do here). */
+typedef struct {
+    o1_sp_ws ws;
+    o1_sp_peers peers;
+    void *hid[2];
+    void *small, *xe_stage;
+    unsigned epoch;
+    const uint8_t *visual_mask;
+    const void *image_embeds;
+    const void *deepstack[3];
+    int embed_row0, visual_rows;
+} o1_sp_ctx;
+hd_status o1_sp_forward(const hd_forward_binding *bw, o1_sp_ctx *ctx, const int64_t *ids_global,
+                        const float *pos_global, const void *vin_local, const float *timestep_dev, int tms_token_id,
+                        void *out_local /* [rows, 3072] */);
+/* One CFG step of a rank of a (CFG pair) x (SP group) layout: o1_sp_forward of this rank's branch, the partner's
+ * prediction rows through peer copies + a two-rank flag barrier, the fused scheduler update
+ * (src/runtime/generate.c:1340-1360 with the flow-match update of :900-905) on n_step_rows local target rows.
+ * xp_local[p] / xp_partner[p] (p = step parity): [2][local image rows][3072] bf16 here and on the partner (mapped);
+ * flags_*: 2 x uint32 each, zero-initialised; step starts at 0.  xp_scratch: [rows, 3072] bf16. */
+typedef struct {
+    int branch;                 /* 0 = conditional, 1 = unconditional */
+    void *xp_local[2], *xp_partner[2];
+    void *flags_local, *flags_partner;
+    unsigned step;
+} o1_cfg_pair;
+hd_status o1_denoise_step_cfg_sp(const hd_forward_binding *bw, o1_sp_ctx *ctx, o1_cfg_pair *pair,
+                                 const int64_t *ids_global, const float *pos_global, const void *z_local,
+                                 int n_step_rows, const float *timestep_dev, float sigma, float sigma_next,
+                                 float guidance, int tms_token_id, void *xp_scratch, void *z_next_local);
+/* rank -> (image, CFG branch or -1, sp_rank) and sp_size for `world` GPUs; returns the number of images in flight,
+ * -1 for an impossible combination.  O1_GPUS, O1_CFG_SPLIT, O1_SP_DEGREE in the environment override the defaults
+ * (1 GPU: both branches; 2: CFG pair; 4: pair x SP2; 8: pair x SP4). */
+int o1_parallel_layout(int world, int rank, int *image, int *branch, int *sp_rank, int *sp_size);
 
 #ifdef __cplusplus
 }

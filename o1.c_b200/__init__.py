@@ -73,6 +73,12 @@ class VisualCond(C.Structure):
                 ("visual_mask", c_void_p), ("v_tokens", c_int)]
 
 
+class CfgBranch(C.Structure):
+    """o1_cfg_branch (include/o1_b200.h): one CFG branch's own sequence."""
+    _fields_ = [("ids", c_void_p), ("text_len", c_int), ("pos_f32", c_void_p), ("ar_len", c_int),
+                ("visual", C.POINTER(VisualCond))]
+
+
 class LoraEntry(C.Structure):
     """hd_lora_entry (include/hd_lora.h:32-45)."""
     _fields_ = [("lora_prefix", C.c_char * 256), ("base_tensor", C.c_char * 256),
@@ -189,6 +195,7 @@ _sig("hd_sdpa_create_split", c_int, C.POINTER(_P), c_int, c_int, c_int, c_int, c
 _sig("hd_sdpa_create_prod", c_int, C.POINTER(_P), c_int, c_int, c_int, c_int, c_int, c_int, c_float)
 _sig("hd_sdpa_execute", c_int, _P, _P, _P, _P, _P, _P, _P)
 _sig("hd_sdpa_execute_split", c_int, _P, _P, _P, _P, _P, _P)
+_sig("hd_sdpa_execute_split_pass", c_int, _P, c_int, _P, _P, _P, _P, _P)
 _sig("hd_sdpa_destroy", None, _P)
 _sig("hd_decoder_block_scratch_bytes", c_int64, c_int64, c_int, c_int, c_int, c_int, c_int)
 _sig("hd_decoder_block", c_int, _P, _P, _P, C.POINTER(BlockBinding), _P, _P, c_int64,
@@ -256,6 +263,9 @@ _sig("o1_denoise_step_cfg", c_int, C.POINTER(ForwardBinding), C.POINTER(ForwardW
      c_int, c_int)
 _sig("o1_denoise_step_cfg_ref", c_int, C.POINTER(ForwardBinding), C.POINTER(ForwardWorkspace), _P, _P,
      c_int, _P, c_int, _P, c_int, c_int, C.POINTER(VisualCond), _P, c_float, c_float, c_float, _P, _P, c_int,
+     c_int, c_int, c_int, c_int, c_int)
+_sig("o1_denoise_step_cfg_branches", c_int, C.POINTER(ForwardBinding), C.POINTER(ForwardWorkspace),
+     C.POINTER(CfgBranch), C.POINTER(CfgBranch), _P, c_int, c_int, _P, c_float, c_float, c_float, _P, _P, c_int,
      c_int, c_int, c_int, c_int, c_int)
 _sig("o1_denoise_step_cfg_host", c_int, C.POINTER(ForwardBinding), C.POINTER(ForwardWorkspace), _P,
      _P, c_int, _P, c_int, _P, _P, c_int, c_float, c_float, c_float, _P, _P, _P, _P, c_int, c_int,

@@ -33,7 +33,9 @@ def _stale(out, deps):
 
 
 def build(verbose=False, force=False):
+    """O1_NVCC_EXTRA (environment): extra nvcc flags, e.g. -DO1_ATTN_P_F16=0; changing it needs force."""
     nvcc = _nvcc()
+    extra = os.environ.get("O1_NVCC_EXTRA", "").split()
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh"))]
     headers.append(os.path.join(HERE, "..", "include", "o1_b200.h"))
     objs = []
@@ -43,7 +45,7 @@ def build(verbose=False, force=False):
         o = os.path.join(CSRC, src.replace(".cu", ".o"))
         objs.append(o)
         if force or _stale(o, [s] + headers):
-            cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", s, "-o", o]
+            cmd = [nvcc] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose else []) + ["-c", s, "-o", o]
             procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
     failed = False
     for src, p in procs:

@@ -44,6 +44,7 @@ struct AttnArgs {
     uint16_t* out;
     int ldo;
     int S, heads, kv_heads, ar_len;
+    int row_lo, row_hi; // only query rows in [row_lo, row_hi) are computed and written (whole range: 0, S)
     float scale_log2;   // scale * log2(e)
     // head h of q sits at TMA coordinates (h*q_hc + d, h*q_hr + s); same for k/v with
     // the kv head.  seq-major [S, H*128]: hc = 128, hr = 0; head-major [H,S,128]: hc = 0, hr = S.
@@ -99,6 +100,32 @@ __device__ __forceinline__ uint32_t cvt_bf16x2(float lo, float hi) {
     return r;
 }
 
+// P = exp2(s * scale - m) for this thread's 64 scores, rounded to bf16 pairs and written to 32 tensor-memory
+// columns at t_p; returns the fp32 sum of the unrounded values.
+__device__ __forceinline__ float softmax_exp_store(const uint32_t (&r)[2][32], uint64_t scale2, uint64_t negm2, uint32_t t_p) {
+    uint64_t lsa = pack_f32x2(0.f, 0.f), lsb = lsa;     // two independent chains of pair sums
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const uint64_t x2 = fma_f32x2(pack_f32x2(__uint_as_float(r[c][2 * i]), __uint_as_float(r[c][2 * i + 1])),
+                                          scale2, negm2);
+            float x0, x1;
+            unpack_f32x2(x2, x0, x1);
+            const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
+            if (i & 1) lsb = add_f32x2(lsb, pack_f32x2(p0, p1));
+            else lsa = add_f32x2(lsa, pack_f32x2(p0, p1));
+            pk[i] = cvt_bf16x2(p0, p1);
+        }
+        tmem_st16(t_p + c * 16, pk);
+    }
+    tmem_st_wait();
+    float s0, s1;
+    unpack_f32x2(add_f32x2(lsa, lsb), s0, s1);
+    return s0 + s1;
+}
+
 __global__ void __launch_bounds__(ATTN_THREADS, 1)
 flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const AttnArgs a) {
@@ -133,6 +160,7 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     const int h = item / a.nqb;
     const int q0 = (item - h * a.nqb) * AQ2;
     const int kh = h / (a.heads / a.kv_heads);
+    if (q0 + AQ2 <= a.row_lo || q0 >= a.row_hi) return;   // no row of this block is wanted (whole CTA, before any set-up)
 
     // keys this pair of query tiles can see (the second tile's range covers the first's)
     int kv_end = a.S;
@@ -283,6 +311,7 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         float* x_mine = xch + (grp * 2 + half) * 128 + row;
         const float* x_other = xch + (grp * 2 + (half ^ 1)) * 128 + row;
         const int bar_id = 1 + grp;              // named barrier of the group's 256 threads
+        constexpr int BAR_THREADS = 256;
         float m_used = -INFINITY;                // max the stored P / l / O of this row are relative to
         float l = 0.f;                           // this thread's share of the row sum
         bool ok = true;
@@ -323,7 +352,7 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             // is rewritten one tile later, after the partner has arrived on p_ready and a new s_full
             // has come round, so one barrier per tile is enough.
             *x_mine = mx;
-            asm volatile("bar.sync %0, 256;" ::"r"(bar_id) : "memory");
+            asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "n"(BAR_THREADS) : "memory");
             mx = fmaxf(mx, *x_other);
             const float m_tile = mx * a.scale_log2;
             const bool grow = (m_tile - m_used) > 8.0f;      // also true while m_used == -inf
@@ -357,28 +386,7 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             // then and every score is masked; 0 keeps exp2(-inf + 0) = 0 instead of exp2(-inf + inf)
             const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
             const uint64_t scale2 = pack_f32x2(a.scale_log2, a.scale_log2), negm2 = pack_f32x2(neg_m, neg_m);
-            uint64_t lsa = pack_f32x2(0.f, 0.f), lsb = lsa;     // two independent chains of pair sums
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                uint32_t pk[16];
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    float x0, x1;
-                    unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(r[c][2 * i]), __uint_as_float(r[c][2 * i + 1])),
-                                           scale2, negm2), x0, x1);
-                    const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
-                    if (i & 1) lsb = add_f32x2(lsb, pack_f32x2(p0, p1));
-                    else lsa = add_f32x2(lsa, pack_f32x2(p0, p1));
-                    pk[i] = cvt_bf16x2(p0, p1);
-                }
-                tmem_st16(t_s + half * 32 + c * 16, pk);
-            }
-            tmem_st_wait();
-            {
-                float s0, s1;
-                unpack_f32x2(add_f32x2(lsa, lsb), s0, s1);
-                l += s0 + s1;
-            }
+            l += softmax_exp_store(r, scale2, negm2, t_s + half * 32);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&p_ready[grp]);
@@ -391,7 +399,7 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         // the row sum is the two threads' shares together (same exchange slots; every thread of the
         // group reaches this barrier: a failed wait above fails for the whole group alike)
         *x_mine = l;
-        asm volatile("bar.sync %0, 256;" ::"r"(bar_id) : "memory");
+        asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "n"(BAR_THREADS) : "memory");
         l += *x_other;
         if (ok && ways > 1) {
             // partial result of a key range: accumulator as it is (relative to m_used), max and row sum
@@ -440,7 +448,7 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 const int rr = k * 4 + (lane >> 3);
                 const uint4 v = *reinterpret_cast<const uint4*>(stg + rr * 128 + ((ch ^ (rr & 7)) * 16));
                 const int rg = qg0 + qd * 32 + rr;
-                if (rg < a.S) {
+                if (rg < a.row_hi && rg >= a.row_lo) {
                     const int blk = rg / a.out_rows;
                     uint16_t* dst = a.out_tab[blk] + (size_t)(rg - blk * a.out_rows) * a.ldo + (size_t)h * a.out_hoff +
                                     half * 64 + ch * 8;
@@ -455,7 +463,7 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 uint32_t o[32];
                 tmem_ld32(t_o + c * 32, o);
                 tmem_ld_wait();
-                if (row_g < a.S) {
+                if (row_g < a.row_hi && row_g >= a.row_lo) {
                     uint4* d4 = reinterpret_cast<uint4*>(dst + c * 32);
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
@@ -541,7 +549,7 @@ static bool flash_attention_impl(const void* q, int ldq, const void* k, int ldk,
                                  int ldv, void* out, int ldo, int S, int heads, int kv_heads,
                                  int ar_len, float scale, bool in_head_major, bool out_head_major,
                                  cudaStream_t st, void* const* out_tab = nullptr, int out_rows = 0,
-                                 void* scratch = nullptr, size_t scratch_bytes = 0) {
+                                 void* scratch = nullptr, size_t scratch_bytes = 0, int row_lo = 0, int row_hi = -1) {
     if (out_tab) {
         if (out_rows <= 0 || (S + out_rows - 1) / out_rows > 8 || out_head_major) { set_error("attention: bad output table"); return false; }
         for (int i = 0; i < (S + out_rows - 1) / out_rows; ++i)
@@ -555,27 +563,27 @@ static bool flash_attention_impl(const void* q, int ldq, const void* k, int ldk,
     if ((ldo % 8) != 0 || (((uintptr_t)out) & 15)) { set_error("attention: output not 16-byte aligned"); return false; }
     if (ar_len < 0) ar_len = 0;
     if (ar_len > S) ar_len = S;
-    const CUtensorMap *tq, *tk, *tv;
+    CUtensorMap mq, mk, mv;
+    bool maps_ok;
     if (in_head_major) {
-        tq = cached_tmap(q, (uint64_t)heads * S, AD, AD, 128);
-        tk = cached_tmap(k, (uint64_t)kv_heads * S, AD, AD, 128);
-        tv = cached_tmap(v, (uint64_t)kv_heads * S, AD, AD, 128);
+        maps_ok = cached_tmap(&mq, q, (uint64_t)heads * S, AD, AD, 128) &&
+                  cached_tmap(&mk, k, (uint64_t)kv_heads * S, AD, AD, 128) &&
+                  cached_tmap(&mv, v, (uint64_t)kv_heads * S, AD, AD, 128);
     } else {
-        tq = cached_tmap(q, S, (uint64_t)heads * AD, ldq, 128);
-        tk = cached_tmap(k, S, (uint64_t)kv_heads * AD, ldk, 128);
-        tv = cached_tmap(v, S, (uint64_t)kv_heads * AD, ldv, 128);
+        maps_ok = cached_tmap(&mq, q, S, (uint64_t)heads * AD, ldq, 128) &&
+                  cached_tmap(&mk, k, S, (uint64_t)kv_heads * AD, ldk, 128) &&
+                  cached_tmap(&mv, v, S, (uint64_t)kv_heads * AD, ldv, 128);
     }
-    if (!tq || !tk || !tv) return false;
-    static bool attr_done = false;
-    if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(flash_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             ATTN_SMEM);
-        if (e != cudaSuccess) { set_error("attention: smem attribute: %s", cudaGetErrorString(e)); return false; }
-        attr_done = true;
-    }
+    if (!maps_ok) return false;
+    const CUtensorMap *tq = &mq, *tk = &mk, *tv = &mv;
+    static std::atomic<uint64_t> attr_done{0};
+    if (!func_attr_once(attr_done, (const void*)flash_attn_kernel, ATTN_SMEM, "attention")) return false;
     AttnArgs a;
     a.out = (uint16_t*)out; a.ldo = ldo;
     a.S = S; a.heads = heads; a.kv_heads = kv_heads; a.ar_len = ar_len;
+    a.row_lo = row_lo < 0 ? 0 : row_lo;
+    a.row_hi = (row_hi < 0 || row_hi > S) ? S : row_hi;
+    if (a.row_lo != 0 || a.row_hi != S) { scratch = nullptr; scratch_bytes = 0; }   // a row range never splits its tail items
     a.scale_log2 = scale * 1.4426950408889634f;
     a.q_hc = in_head_major ? 0 : AD;  a.q_hr = in_head_major ? S : 0;
     a.kv_hc = a.q_hc;                 a.kv_hr = a.q_hr;
@@ -638,9 +646,10 @@ bool flash_attention_tab(const void* q, int ldq, const void* k, int ldk, const v
 }
 // q [heads,S,128], k/v [kv_heads,S,128]; out head-major [heads,S,128] or seq-major [S, heads*128]
 bool flash_attention_hm(const void* q, const void* k, const void* v, void* out, int S, int heads,
-                        int kv_heads, int ar_len, float scale, bool out_head_major, cudaStream_t st) {
+                        int kv_heads, int ar_len, float scale, bool out_head_major, cudaStream_t st,
+                        int row_lo, int row_hi) {
     return flash_attention_impl(q, AD, k, AD, v, AD, out, heads * AD, S, heads, kv_heads, ar_len,
-                                scale, true, out_head_major, st);
+                                scale, true, out_head_major, st, nullptr, 0, nullptr, 0, row_lo, row_hi);
 }
 
 }  // namespace o1

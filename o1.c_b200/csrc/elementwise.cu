@@ -139,6 +139,83 @@ bool rmsnorm_mod(const void* x, const void* w, const void* scale, const void* sh
     return true;
 }
 
+// ------------------------------------------------------------------ materialising attention (small / odd shapes)
+// The path of o1.c's hd_attention_eager (src/cuda/attn.cu:22-174) for what the flash kernel does not cover: a head
+// dimension other than 128 or an additive mask that is not prefix-causal.  One block per (head, query row): scores
+// s_t = (q . k_t) * scaling + mask[s,t] in fp32 (stored as bf16), fp32 softmax with the row maximum subtracted,
+// probabilities rounded to bf16 (and stored), out = sum_t p_t v_t accumulated in fp32 over the ROUNDED
+// probabilities, written seq-major [seq, heads, dim].  O(seq^2) memory and time: meant for tests and small inputs.
+__global__ void __launch_bounds__(128)
+attention_rows_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ k, const uint16_t* __restrict__ v,
+                      const uint16_t* __restrict__ mask, uint16_t* __restrict__ scores, uint16_t* __restrict__ probs,
+                      uint16_t* __restrict__ out, int heads, int kv_heads, int seq, int dim, float scaling) {
+    const int s = blockIdx.x, h = blockIdx.y, kh = h / (heads / kv_heads);
+    const uint16_t* qr = q + ((size_t)h * seq + s) * dim;
+    uint16_t* sc = scores + ((size_t)h * seq + s) * seq;
+    uint16_t* pr = probs + ((size_t)h * seq + s) * seq;
+    __shared__ float red[128];
+    float mx = -INFINITY;
+    for (int t = threadIdx.x; t < seq; t += blockDim.x) {
+        const uint16_t* kr = k + ((size_t)kh * seq + t) * dim;
+        float acc = 0.f;
+        for (int i = 0; i < dim; ++i) acc += bf16_to_f32(qr[i]) * bf16_to_f32(kr[i]);
+        acc = acc * scaling + bf16_to_f32(mask[(size_t)s * seq + t]);
+        sc[t] = f32_to_bf16(acc);
+        mx = fmaxf(mx, acc);          // the fp32 score itself is recomputed in the passes below
+    }
+    red[threadIdx.x] = mx;
+    __syncthreads();
+    for (int o = 64; o > 0; o >>= 1) {
+        if (threadIdx.x < o) red[threadIdx.x] = fmaxf(red[threadIdx.x], red[threadIdx.x + o]);
+        __syncthreads();
+    }
+    mx = red[0];
+    __syncthreads();
+    float sum = 0.f;
+    for (int t = threadIdx.x; t < seq; t += blockDim.x) {
+        const uint16_t* kr = k + ((size_t)kh * seq + t) * dim;
+        float acc = 0.f;
+        for (int i = 0; i < dim; ++i) acc += bf16_to_f32(qr[i]) * bf16_to_f32(kr[i]);
+        acc = acc * scaling + bf16_to_f32(mask[(size_t)s * seq + t]);
+        sum += expf(acc - mx);
+    }
+    red[threadIdx.x] = sum;
+    __syncthreads();
+    for (int o = 64; o > 0; o >>= 1) {
+        if (threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o];
+        __syncthreads();
+    }
+    const float inv = 1.0f / red[0];
+    __syncthreads();
+    for (int t = threadIdx.x; t < seq; t += blockDim.x) {
+        const uint16_t* kr = k + ((size_t)kh * seq + t) * dim;
+        float acc = 0.f;
+        for (int i = 0; i < dim; ++i) acc += bf16_to_f32(qr[i]) * bf16_to_f32(kr[i]);
+        acc = acc * scaling + bf16_to_f32(mask[(size_t)s * seq + t]);
+        pr[t] = f32_to_bf16(expf(acc - mx) * inv);
+    }
+    __syncthreads();
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+        float acc = 0.f;
+        for (int t = 0; t < seq; ++t) acc += bf16_to_f32(pr[t]) * bf16_to_f32(v[((size_t)kh * seq + t) * dim + d]);
+        out[((size_t)s * heads + h) * dim + d] = f32_to_bf16(acc);
+    }
+}
+bool attention_materialised(const void* q, const void* k, const void* v, const void* mask, void* scores, void* probs,
+                            void* out, int heads, int kv_heads, int seq, int dim, float scaling, cudaStream_t st) {
+    if (!q || !k || !v || !mask || !scores || !probs || !out || heads <= 0 || kv_heads <= 0 || (heads % kv_heads) != 0 ||
+        seq <= 0 || dim <= 0 || heads > 65535) {
+        set_error("attention_eager: bad args");
+        return false;
+    }
+    dim3 grid(seq, heads);
+    attention_rows_kernel<<<grid, 128, 0, st>>>((const uint16_t*)q, (const uint16_t*)k, (const uint16_t*)v,
+                                                (const uint16_t*)mask, (uint16_t*)scores, (uint16_t*)probs,
+                                                (uint16_t*)out, heads, kv_heads, seq, dim, scaling);
+    O1_LAUNCH_CHECK("attention_eager");
+    return true;
+}
+
 // ------------------------------------------------------------------ pointwise
 template <int OP>  // 0 silu, 1 swiglu, 2 residual add
 __global__ void pointwise_kernel(const uint16_t* __restrict__ a, const uint16_t* __restrict__ b,

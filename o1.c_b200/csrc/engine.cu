@@ -51,7 +51,7 @@ static void set_model_error(const char* fmt, ...) {
 }
 
 struct DevState {
-    int* err_word = nullptr;
+    int* err_word = nullptr;   // [0] error word of the bounded waits, [1] result slot of the mask probe
     int sms = 0;
 };
 static DevState& dev_state() {
@@ -62,7 +62,7 @@ static DevState& dev_state() {
     std::lock_guard<std::mutex> lk(mu);
     DevState& s = states[dev];
     if (!s.err_word) {
-        if (cudaMalloc(&s.err_word, sizeof(int)) == cudaSuccess) cudaMemset(s.err_word, 0, sizeof(int));
+        if (cudaMalloc(&s.err_word, 2 * sizeof(int)) == cudaSuccess) cudaMemset(s.err_word, 0, 2 * sizeof(int));
         cudaDeviceGetAttribute(&s.sms, cudaDevAttrMultiProcessorCount, dev);
         if (s.sms <= 0) s.sms = 148;
     }
@@ -108,7 +108,6 @@ struct hd_gemm_runtime {
 struct hd_sdpa_plan {
     int q_heads, kv_heads, seq, ar_len, head_dim;
     float scale;
-    const void* probed_mask;   // mask pointer ar_len was last derived from
 };
 
 extern "C" {
@@ -203,9 +202,37 @@ void hd_linear_reference(const void* x, const void* w, const void* bias, void* y
 void hd_timestep_embed(const float* t, float* y, int N, int dim) {
     if (timestep_embed(t, y, N, dim, g_stream)) count();
 }
+// true when the GPU cannot dereference p: plain (unregistered) host memory on a machine without unified addressing
+// of pageable memory.  o1.c is developed on a unified-memory part, where its own tests hand malloc'd arrays to
+// kernels (tests/unit/test_primitives.c:366-372); here such a pointer would fault the kernel.
+static bool is_plain_host_pointer(const void* p) {
+    cudaPointerAttributes a;
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) { cudaGetLastError(); return false; }
+    if (a.type != cudaMemoryTypeUnregistered) return false;
+    int dev = 0, pageable = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&pageable, cudaDevAttrPageableMemoryAccess, dev);
+    return pageable == 0;
+}
 void hd_mrope_cos_sin(const float* pos, int bs, int seq, const int64_t* section, int n_section,
                       int head_dim, float theta, float attention_scaling, int interleaved,
                       float* cosd, float* sind) {
+    if (cosd && sind && seq > 0 && head_dim > 0 && bs > 0 && (is_plain_host_pointer(cosd) || is_plain_host_pointer(sind))) {
+        // host output arrays: compute into a device buffer and copy back (this entry point is not on the forward's
+        // path, which builds its own table once per forward)
+        const size_t n = (size_t)bs * seq * head_dim;
+        float* tmp = nullptr;
+        if (cudaMalloc(&tmp, 2 * n * sizeof(float)) != cudaSuccess) { set_error("mrope: staging allocation failed"); return; }
+        if (mrope_cos_sin(pos, bs, seq, section, n_section, head_dim, theta, attention_scaling, interleaved, tmp, tmp + n,
+                          g_stream)) {
+            count();
+            cudaMemcpyAsync(cosd, tmp, n * sizeof(float), cudaMemcpyDeviceToHost, g_stream);
+            cudaMemcpyAsync(sind, tmp + n, n * sizeof(float), cudaMemcpyDeviceToHost, g_stream);
+            cudaStreamSynchronize(g_stream);
+        }
+        cudaFree(tmp);
+        return;
+    }
     if (mrope_cos_sin(pos, bs, seq, section, n_section, head_dim, theta, attention_scaling,
                       interleaved, cosd, sind, g_stream))
         count();
@@ -320,23 +347,19 @@ __global__ void mask_probe_kernel(const uint16_t* __restrict__ mask, int S, int*
     }
 }
 
-static int probe_ar_len(const void* mask_dev, int S) {
-    static std::map<std::pair<const void*, int>, int> cache;
-    auto key = std::make_pair(mask_dev, S);
-    auto it = cache.find(key);
-    if (it != cache.end()) return it->second;
+// Probed on every call: a caller may free and re-allocate, or rewrite in place, a mask at the same address
+// with another causal prefix (o1.c allocates its mask per request, src/runtime/generate.c:1202-1209), so
+// nothing about a mask pointer may be remembered.  Costs O(S) reads and one stream synchronisation; callers
+// that pass an hd_sdpa_plan created with ar_len never come here.
+static int probe_ar_len(const void* mask_dev, int S, cudaStream_t st) {
     int* w = device_error_word();
     if (!w) return -1;
-    // reuse a second int next to nothing: allocate a tiny result slot once
-    static int* slot = nullptr;
-    if (!slot && cudaMalloc(&slot, sizeof(int)) != cudaSuccess) return -1;
-    mask_probe_kernel<<<1, 1024, 0, g_stream>>>((const uint16_t*)mask_dev, S, slot);
+    int* slot = w + 1;
+    mask_probe_kernel<<<1, 1024, 0, st>>>((const uint16_t*)mask_dev, S, slot);
     count();
     int v = -1;
-    if (cudaMemcpyAsync(&v, slot, sizeof(int), cudaMemcpyDeviceToHost, g_stream) != cudaSuccess) return -1;
-    if (cudaStreamSynchronize(g_stream) != cudaSuccess) return -1;
-    if (cache.size() > 64) cache.clear();
-    cache[key] = v;
+    if (cudaMemcpyAsync(&v, slot, sizeof(int), cudaMemcpyDeviceToHost, st) != cudaSuccess) return -1;
+    if (cudaStreamSynchronize(st) != cudaSuccess) return -1;
     return v;
 }
 
@@ -352,7 +375,7 @@ static int sdpa_new(hd_sdpa_plan** out, int batch, int qh, int kvh, int seq, int
     hd_sdpa_plan* p = (hd_sdpa_plan*)calloc(1, sizeof(*p));
     if (!p) { set_error("sdpa: out of host memory"); return 1; }
     p->q_heads = qh; p->kv_heads = kvh; p->seq = seq; p->ar_len = ar_len; p->head_dim = hd;
-    p->scale = scale; p->probed_mask = nullptr;
+    p->scale = scale;
     *out = p;
     return 0;
 }
@@ -371,19 +394,19 @@ int hd_sdpa_create_prod(hd_sdpa_plan** out, int batch, int qh, int kvh, int seq,
     if (ar_len < 0 || ar_len >= seq) ar_len = -1;  // reference falls back to the masked plan
     return sdpa_new(out, batch, qh, kvh, seq, ar_len, hd, scale);
 }
-static int sdpa_ar_len(hd_sdpa_plan* p, const void* mask) {
+static int sdpa_ar_len(hd_sdpa_plan* p, const void* mask, cudaStream_t st) {
     if (p->ar_len >= 0) return p->ar_len;
     if (!mask) return 0;
-    const int ar = probe_ar_len(mask, p->seq);
+    const int ar = probe_ar_len(mask, p->seq, st);
     if (ar < 0) set_error("sdpa: mask is not prefix-causal");
     return ar;
 }
 int hd_sdpa_execute(hd_sdpa_plan* plan, const void* q, const void* k, const void* v,
                     const void* mask, void* out, void* stream) {
     if (!plan || !q || !k || !v || !out) { set_error("sdpa: null argument"); return 1; }
-    const int ar = sdpa_ar_len(plan, mask);
-    if (ar < 0) return 1;
     cudaStream_t st = stream ? (cudaStream_t)stream : g_stream;
+    const int ar = sdpa_ar_len(plan, mask, st);
+    if (ar < 0) return 1;
     if (!flash_attention_hm(q, k, v, out, plan->seq, plan->q_heads, plan->kv_heads, ar, plan->scale,
                             true, st))
         return 1;
@@ -397,22 +420,38 @@ int hd_sdpa_execute_split(hd_sdpa_plan* plan, const void* q, const void* k, cons
 }
 int hd_sdpa_execute_split_pass(hd_sdpa_plan* plan, int which, const void* q, const void* k,
                                const void* v, void* out, void* stream) {
-    // One kernel covers both query ranges; running it for either pass writes the
-    // complete output, which contains that pass's rows.
-    (void)which;
-    return hd_sdpa_execute_split(plan, q, k, v, out, stream);
+    // pass 0 = the causal rows [0, ar_len), pass 1 = the rows [ar_len, seq) that see every key
+    // (include/hd_cudnn_sdpa.h:77-82); the same kernel, restricted to that pass's query rows
+    if (!plan || plan->ar_len < 0) { set_error("sdpa: not a split plan"); return 1; }
+    if (!q || !k || !v || !out || (which != 0 && which != 1)) { set_error("sdpa: bad argument"); return 1; }
+    const int lo = which == 0 ? 0 : plan->ar_len, hi = which == 0 ? plan->ar_len : plan->seq;
+    if (lo >= hi) return 0;
+    cudaStream_t st = stream ? (cudaStream_t)stream : g_stream;
+    if (!flash_attention_hm(q, k, v, out, plan->seq, plan->q_heads, plan->kv_heads, plan->ar_len, plan->scale, true,
+                            st, lo, hi))
+        return 1;
+    count();
+    return 0;
 }
 void hd_sdpa_destroy(hd_sdpa_plan* plan) { free(plan); }
 
 void hd_attention_eager(const void* q, const void* k, const void* v, const void* mask, void* scores,
                         void* probs, void* out, int heads, int kv_heads, int seq, int dim,
                         float scaling) {
-    (void)scores; (void)probs;
-    if (!q || !k || !v || !out || dim != 128) { set_error("attention: bad args (head_dim must be 128)"); return; }
+    // head_dim 128 with a prefix-causal (or no) mask runs the flash kernel and leaves scores / probs untouched
+    // (they are O(S^2) buffers this path exists to avoid).  Anything else -- another head_dim, an arbitrary
+    // additive mask -- runs the materialising kernels, which need and fill both buffers as the reference does.
+    if (!q || !k || !v || !out) { set_error("attention: bad args"); return; }
     int ar = 0;
-    if (mask) {
-        ar = probe_ar_len(mask, seq);
-        if (ar < 0) { set_error("attention: mask is not prefix-causal"); return; }
+    if (mask && dim == 128) ar = probe_ar_len(mask, seq, g_stream);
+    if (dim != 128 || ar < 0) {
+        if (!mask || !scores || !probs) {
+            set_error(dim != 128 ? "attention: head_dim != 128 needs the mask, scores and probs buffers"
+                                 : "attention: mask is not prefix-causal (the general path needs scores and probs buffers)");
+            return;
+        }
+        if (attention_materialised(q, k, v, mask, scores, probs, out, heads, kv_heads, seq, dim, scaling, g_stream)) count();
+        return;
     }
     if (flash_attention_hm(q, k, v, out, seq, heads, kv_heads, ar, scaling, false, g_stream)) count();
 }
@@ -578,7 +617,7 @@ static hd_status decoder_block_entry(const void* in_dev, const float* pos_dev, c
     int ar_len;
     if (sdpa && sdpa->ar_len >= 0) ar_len = sdpa->ar_len;
     else {
-        ar_len = mask_dev ? probe_ar_len(mask_dev, (int)seq) : 0;
+        ar_len = mask_dev ? probe_ar_len(mask_dev, (int)seq, g_stream) : 0;
         if (ar_len < 0) { hd_set_error("block: mask is not prefix-causal"); return HD_ERR_UNSUPPORTED; }
     }
     BlockScratch b = carve_block((void*)(((uintptr_t)scratch + 255) & ~(uintptr_t)255), seq, heads,
@@ -818,13 +857,13 @@ hd_status hd_forward(const hd_forward_binding* bw, hd_forward_workspace* ws, con
         hd_set_error("forward: unsupported dims");
         return HD_ERR_UNSUPPORTED;
     }
+    cudaStream_t st = stream ? (cudaStream_t)stream : g_stream;
     int ar_len;
     if (ws->sdpa && ws->sdpa->ar_len >= 0) ar_len = ws->sdpa->ar_len;
     else {
-        ar_len = mask_dev ? probe_ar_len(mask_dev, seq) : 0;
+        ar_len = mask_dev ? probe_ar_len(mask_dev, seq, st) : 0;
         if (ar_len < 0) { hd_set_error("forward: mask is not prefix-causal"); return HD_ERR_UNSUPPORTED; }
     }
-    cudaStream_t st = stream ? (cudaStream_t)stream : g_stream;
     return forward_impl(bw, ws, input_ids, text_len, pos_f32, ar_len, vinputs, img_tokens, visual,
                         timestep, seq, heads, kv_heads, hidden, ff_hidden, head_dim, tms_token_id, diag,
                         out_dev, st);
@@ -882,6 +921,7 @@ int o1_fill_normal_f32(float* dst, size_t n, uint64_t seed, float mean, float st
     return 0;
 }
 
+// Both branches with the same text length, positions and causal prefix (BASELINE's CFG definition).
 hd_status o1_denoise_step_cfg(const hd_forward_binding* bw, hd_forward_workspace* ws,
                               const int64_t* ids_cond, const int64_t* ids_uncond, int text_len,
                               const float* pos_f32, int ar_len, const void* z, int img_tokens,
@@ -900,12 +940,29 @@ hd_status o1_denoise_step_cfg_ref(const hd_forward_binding* bw, hd_forward_works
                                   float sigma, float sigma_next, float guidance, void* xp_scratch, void* z_next,
                                   int heads, int kv_heads, int hidden, int ff_hidden, int head_dim,
                                   int tms_token_id) {
+    o1_cfg_branch c = {ids_cond, text_len, pos_f32, ar_len, visual};
+    o1_cfg_branch u = {ids_uncond, text_len, pos_f32, ar_len, visual};
+    return o1_denoise_step_cfg_branches(bw, ws, &c, &u, z, img_tokens, target_tokens, timestep_dev, sigma,
+                                        sigma_next, guidance, xp_scratch, z_next, heads, kv_heads, hidden,
+                                        ff_hidden, head_dim, tms_token_id);
+}
+
+// Each branch brings its own token ids, text length, positions and causal prefix, as o1.c's CFG loop does
+// (src/runtime/generate.c:1111-1206 builds a second, normally shorter, sequence for the unconditional prompt;
+// :1340-1356 runs it with seq_text_len[1], posd[1], seq_S_uncond and slices its prediction at its own text
+// length).  ws must be sized for the longer sequence; xp_scratch holds (S_cond + S_uncond) * 3072 bf16.
+hd_status o1_denoise_step_cfg_branches(const hd_forward_binding* bw, hd_forward_workspace* ws,
+                                       const o1_cfg_branch* cond, const o1_cfg_branch* uncond, const void* z,
+                                       int img_tokens, int target_tokens, const float* timestep_dev, float sigma,
+                                       float sigma_next, float guidance, void* xp_scratch, void* z_next, int heads,
+                                       int kv_heads, int hidden, int ff_hidden, int head_dim, int tms_token_id) {
     if (target_tokens <= 0 || target_tokens > img_tokens) {
         hd_set_error("denoise_step: target_tokens out of range");
         return HD_ERR_MISSING;
     }
-    if (!bw || !ws || !ws->hidden_a || !ids_cond || !ids_uncond || !pos_f32 || !z || !timestep_dev ||
-        !xp_scratch || !z_next) {
+    if (!bw || !ws || !ws->hidden_a || !cond || !uncond || !cond->ids || !uncond->ids || !cond->pos_f32 ||
+        !uncond->pos_f32 || cond->text_len <= 0 || uncond->text_len <= 0 || !z || !timestep_dev || !xp_scratch ||
+        !z_next) {
         hd_set_error("denoise_step: null argument");
         return HD_ERR_MISSING;
     }
@@ -913,20 +970,21 @@ hd_status o1_denoise_step_cfg_ref(const hd_forward_binding* bw, hd_forward_works
         hd_set_error("denoise_step: unsupported dims");
         return HD_ERR_UNSUPPORTED;
     }
-    const int S = text_len + img_tokens;
+    const int Sc = cond->text_len + img_tokens, Su = uncond->text_len + img_tokens;
     uint16_t* xc = (uint16_t*)xp_scratch;
-    uint16_t* xu = xc + (size_t)S * 3072;
-    hd_status s = forward_impl(bw, ws, ids_cond, text_len, pos_f32, ar_len, z, img_tokens, visual,
-                               timestep_dev, S, heads, kv_heads, hidden, ff_hidden, head_dim,
+    uint16_t* xu = xc + (size_t)Sc * 3072;
+    hd_status s = forward_impl(bw, ws, cond->ids, cond->text_len, cond->pos_f32, cond->ar_len, z, img_tokens,
+                               cond->visual, timestep_dev, Sc, heads, kv_heads, hidden, ff_hidden, head_dim,
                                tms_token_id, nullptr, xc, g_stream);
     if (s != HD_OK) return s;
-    s = forward_impl(bw, ws, ids_uncond, text_len, pos_f32, ar_len, z, img_tokens, visual, timestep_dev,
-                     S, heads, kv_heads, hidden, ff_hidden, head_dim, tms_token_id, nullptr, xu, g_stream);
+    s = forward_impl(bw, ws, uncond->ids, uncond->text_len, uncond->pos_f32, uncond->ar_len, z, img_tokens,
+                     uncond->visual, timestep_dev, Su, heads, kv_heads, hidden, ff_hidden, head_dim, tms_token_id,
+                     nullptr, xu, g_stream);
     if (s != HD_OK) return s;
-    // target rows start at row text_len of each prediction (generate.c:1330 slices them by a copy);
+    // target rows start at row text_len of each prediction (generate.c:1330, :1352 slice them by a copy);
     // reference rows that follow the target in z are inputs only and are not stepped
     const size_t n = (size_t)target_tokens * 3072;
-    if (!sched_cfg_flow_step(z, xc + (size_t)text_len * 3072, xu + (size_t)text_len * 3072, sigma,
+    if (!sched_cfg_flow_step(z, xc + (size_t)cond->text_len * 3072, xu + (size_t)uncond->text_len * 3072, sigma,
                              sigma_next, guidance, z_next, n, g_stream)) {
         hd_set_error("denoise_step: scheduler: %s", g_cuda_err);
         return HD_ERR_RUNTIME;

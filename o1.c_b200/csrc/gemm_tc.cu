@@ -18,6 +18,7 @@
 #include "ptx.cuh"
 #include "kernels.h"
 
+#include <atomic>
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -59,7 +60,7 @@ struct GemmCfg {
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int STAGES = (BN == 256) ? 4 : 6;
-    static constexpr int STORE_STAGE_BYTES = 4 * 32 * 128;   // per epilogue warp 32 rows x 128 B (peer stores)
+    static constexpr int STORE_STAGE_BYTES = 4 * 2 * 32 * 128;   // per epilogue warp two slices of 32 rows x 128 B (peer stores)
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/ + STORE_STAGE_BYTES;
     static constexpr int TMEM_COLS = 2 * BN;
 };
@@ -258,7 +259,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 // pieces of 32 different rows into every store instruction; over NVLink each piece is a
                 // packet of its own.  So 64 columns at a time go through a swizzled shared-memory slice of
                 // this warp and leave as full 128-byte row segments (4 rows per instruction).
-                uint8_t* stg = store_stage + q * (32 * 128);
+                uint8_t* stg = store_stage + q * (2 * 32 * 128);
 #pragma unroll 1
                 for (int c2 = 0; c2 < BN / 64; ++c2) {
                     uint32_t r0[32], r1[32];
@@ -322,7 +323,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         const float inv = rsqrtf(sq / 128.0f + g.scale);
                         const int col = nb * BN + hb * 128;
                         const size_t ocol = g.o_cb ? (size_t)(col / g.o_cb) * g.o_cb_stride + (col % g.o_cb) : (size_t)col;
-                        uint16_t* orow = g.out + (size_t)row * g.ldo + ocol;
+                        uint16_t* orow = g.o_tab_n ? nullptr : g.out + (size_t)row * g.ldo + ocol;
+                        uint8_t* stg_row = store_stage + q * (2 * 32 * 128) + lane * 128;
                         const float* cs = g.rope + (size_t)row * 128;
 #pragma unroll
                         for (int t = 0; t < 8; ++t) {
@@ -354,9 +356,35 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                             po.z = pack_bf16x2(ol[4], ol[5]); po.w = pack_bf16x2(ol[6], ol[7]);
                             ph.x = pack_bf16x2(oh[0], oh[1]); ph.y = pack_bf16x2(oh[2], oh[3]);
                             ph.z = pack_bf16x2(oh[4], oh[5]); ph.w = pack_bf16x2(oh[6], oh[7]);
-                            *reinterpret_cast<uint4*>(orow + 8 * t) = po;
-                            *reinterpret_cast<uint4*>(orow + 64 + 8 * t) = ph;
+                            if (g.o_tab_n) {
+                                // destination rows live in another GPU's memory: both 64-column halves of the
+                                // head go through this warp's two swizzled shared-memory slices first
+                                *reinterpret_cast<uint4*>(stg_row + ((t ^ (lane & 7)) * 16)) = po;
+                                *reinterpret_cast<uint4*>(stg_row + 32 * 128 + ((t ^ (lane & 7)) * 16)) = ph;
+                            } else {
+                                *reinterpret_cast<uint4*>(orow + 8 * t) = po;
+                                *reinterpret_cast<uint4*>(orow + 64 + 8 * t) = ph;
+                            }
                         }
+                    }
+                    if (g.o_tab_n) {
+                        // leave as full 128-byte row segments, 4 rows per store instruction (a head never straddles
+                        // a destination block: o_cb % 128 == 0)
+                        __syncwarp();
+                        const int col = nb * BN + hb * 128;
+                        uint16_t* obase = g.o_tab[col / g.o_cb] + (col % g.o_cb);
+                        const uint8_t* stg = store_stage + q * (2 * 32 * 128);
+                        const int ch = lane & 7;
+#pragma unroll
+                        for (int hf = 0; hf < 2; ++hf)
+#pragma unroll
+                            for (int k = 0; k < 8; ++k) {
+                                const int rr = k * 4 + (lane >> 3);
+                                const uint4 o = *reinterpret_cast<const uint4*>(stg + hf * (32 * 128) + rr * 128 + ((ch ^ (rr & 7)) * 16));
+                                const int grow = mb * BM + q * 32 + rr;
+                                if (grow < g.M) *reinterpret_cast<uint4*>(obase + (size_t)grow * g.ldo + hf * 64 + ch * 8) = o;
+                            }
+                        __syncwarp();
                     }
                 }
             } else if (EPI == EPI_LORA) {
@@ -567,32 +595,41 @@ struct TmapKey {
 };
 // Encoding a tensor map costs a few microseconds on the host; weights and
 // workspace buffers repeat every block and step, so cache by (ptr, shape).
-const CUtensorMap* cached_tmap(const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
-                               uint32_t box_rows) {
+// The map is copied out under the lock: the cache may be emptied by a later
+// call (or another thread) while the caller still holds its copy.
+bool cached_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                 uint32_t box_rows) {
     static std::map<TmapKey, CUtensorMap> cache;
     static std::mutex mu;
     std::lock_guard<std::mutex> lk(mu);
     TmapKey k{base, rows, cols, ld, box_rows};
     auto it = cache.find(k);
-    if (it != cache.end()) return &it->second;
+    if (it != cache.end()) { *out = it->second; return true; }
     if (cache.size() > 8192) cache.clear();
-    CUtensorMap m;
-    if (!make_tmap_bf16(&m, base, rows, cols, ld, box_rows)) return nullptr;
-    return &cache.emplace(k, m).first->second;
+    if (!make_tmap_bf16(out, base, rows, cols, ld, box_rows)) return false;
+    cache.emplace(k, *out);
+    return true;
+}
+
+// cudaFuncSetAttribute is per device: remember, per kernel instantiation, on which devices it was done.
+bool func_attr_once(std::atomic<uint64_t>& done, const void* func, int smem_bytes, const char* what) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const uint64_t bit = 1ull << (dev & 63);
+    if (done.load(std::memory_order_acquire) & bit) return true;
+    cudaError_t e = cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    if (e != cudaSuccess) { set_error("%s: smem attribute: %s", what, cudaGetErrorString(e)); return false; }
+    done.fetch_or(bit, std::memory_order_release);
+    return true;
 }
 
 template <int EPI, int BN>
 static bool launch_tc(const CUtensorMap* tA, const CUtensorMap* tB, const CUtensorMap* tB2,
                       GemmArgs& g, cudaStream_t st) {
     using Cfg = GemmCfg<BN>;
-    static bool attr_done = false;
+    static std::atomic<uint64_t> attr_done{0};
     auto kern = gemm_tc_kernel<EPI, BN>;
-    if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             Cfg::SMEM_BYTES);
-        if (e != cudaSuccess) { set_error("gemm: smem attribute: %s", cudaGetErrorString(e)); return false; }
-        attr_done = true;
-    }
+    if (!func_attr_once(attr_done, (const void*)kern, Cfg::SMEM_BYTES, "gemm")) return false;
     const int tiles = g.num_m * g.num_n;
     int grid = sm_count();
     if (grid > tiles) grid = tiles;
@@ -630,8 +667,8 @@ bool gemm_bf16_ex(const void* x, int ldx, const void* w, const void* w2, void* y
                   int K, int epi, const void* bias, const void* resid, int ldr, float scale, int force_bn,
                   int o_cb, long o_cb_stride, int a_kblk, int a_rows, cudaStream_t st, void* const* o_tab) {
     if (!x || !w || (!y && !o_tab) || M <= 0 || N <= 0 || K <= 0) { set_error("gemm: bad args"); return false; }
-    if (o_tab && (!o_cb || N / o_cb > 8 || epi != EPI_STORE)) {
-        set_error("gemm: an output table needs column blocks (at most 8) and the plain epilogue");
+    if (o_tab && (!o_cb || N / o_cb > 8 || (epi != EPI_STORE && epi != EPI_QKNORM))) {
+        set_error("gemm: an output table needs column blocks (at most 8) and the plain or per-head norm epilogue");
         return false;
     }
     if ((o_cb || a_kblk) && !gemm_tc_supported(M, N, K, epi)) {
@@ -674,7 +711,7 @@ bool gemm_bf16_ex(const void* x, int ldx, const void* w, const void* w2, void* y
     g.rope = nullptr;
     if (epi == EPI_QKNORM) {
         // resid carries the cos|sin table, bias the norm weight; every 128 output columns are one head
-        if (!bias || !resid || (N % 128) != 0 || (o_cb && (o_cb % 128) != 0) || o_tab || (((uintptr_t)bias) & 15) ||
+        if (!bias || !resid || (N % 128) != 0 || (o_cb && (o_cb % 128) != 0) || (((uintptr_t)bias) & 15) ||
             (((uintptr_t)resid) & 15)) {
             set_error("gemm: per-head norm epilogue needs norm weight, cos|sin table and whole heads");
             return false;
@@ -702,11 +739,14 @@ bool gemm_bf16_ex(const void* x, int ldx, const void* w, const void* w2, void* y
     }
     g.a_kblk = a_kblk; g.a_rows = a_rows;
 
-    const CUtensorMap* tA = a_kblk ? cached_tmap(x, (uint64_t)(K / a_kblk) * a_rows, a_kblk, ldx, 128)
-                                   : cached_tmap(x, M, K, ldx, 128);
-    const CUtensorMap* tB = cached_tmap(w, N, K, K, 128);
-    const CUtensorMap* tB2 = (epi == EPI_SWIGLU) ? cached_tmap(w2, N, K, K, 128) : tB;
-    if (!tA || !tB || !tB2) return false;
+    CUtensorMap mA, mB, mB2;
+    if (!(a_kblk ? cached_tmap(&mA, x, (uint64_t)(K / a_kblk) * a_rows, a_kblk, ldx, 128)
+                 : cached_tmap(&mA, x, M, K, ldx, 128)))
+        return false;
+    if (!cached_tmap(&mB, w, N, K, K, 128)) return false;
+    if (epi == EPI_SWIGLU) { if (!cached_tmap(&mB2, w2, N, K, K, 128)) return false; }
+    else mB2 = mB;
+    const CUtensorMap *tA = &mA, *tB = &mB, *tB2 = &mB2;
 
     if (epi == EPI_SWIGLU) {
         g.num_n = N / 128;

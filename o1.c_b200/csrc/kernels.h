@@ -6,6 +6,8 @@
 #include <stddef.h>
 #include <stdint.h>
 
+#include <atomic>
+
 namespace o1 {
 
 // EPI_QKNORM: per-head RMSNorm + rotary of a q / k projection inside the GEMM epilogue (every 128 output columns
@@ -38,8 +40,11 @@ bool gemm_bf16_ex(const void* x, int ldx, const void* w, const void* w2, void* y
                   int K, int epi, const void* bias, const void* resid, int ldr, float scale, int force_bn,
                   int o_cb, long o_cb_stride, int a_kblk, int a_rows, cudaStream_t st, void* const* o_tab = nullptr);
 bool gemm_tc_supported(int M, int N, int K, int epi);
-const CUtensorMap* cached_tmap(const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
-                               uint32_t box_rows);
+// copies the (cached) tensor map of a row-major bf16 matrix into *out; false + error text on failure
+bool cached_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                 uint32_t box_rows);
+// sets a kernel's dynamic shared-memory limit once per device (`done`: one bit per device ordinal)
+bool func_attr_once(std::atomic<uint64_t>& done, const void* func, int smem_bytes, const char* what);
 
 // ---- attn_tc.cu
 // q [S, ldq] (heads*128 columns used), k/v [S, ldk]/[S, ldv] (kv_heads*128),
@@ -50,8 +55,10 @@ bool flash_attention(const void* q, int ldq, const void* k, int ldk, const void*
                      void* out, int ldo, int S, int heads, int kv_heads, int ar_len, float scale,
                      cudaStream_t st, void* scratch = nullptr, size_t scratch_bytes = 0);
 
+// [row_lo, row_hi): the query rows to compute and write (row_hi < 0: all rows)
 bool flash_attention_hm(const void* q, const void* k, const void* v, void* out, int S, int heads,
-                        int kv_heads, int ar_len, float scale, bool out_head_major, cudaStream_t st);
+                        int kv_heads, int ar_len, float scale, bool out_head_major, cudaStream_t st,
+                        int row_lo = 0, int row_hi = -1);
 // tail split policy of flash_attention*: 0 = automatic, 1 = never, n = n key-range parts when they fit
 void attention_tail_ways(int ways);
 // seq-major operands; output rows [b*out_rows, (b+1)*out_rows) go to out_tab[b] (row-major, leading
@@ -61,6 +68,10 @@ bool flash_attention_tab(const void* q, int ldq, const void* k, int ldk, const v
                          int ar_len, float scale, cudaStream_t st, void* scratch = nullptr, size_t scratch_bytes = 0);
 
 // ---- elementwise.cu
+// O(seq^2) attention that stores bf16 scores and probabilities: any head_dim, any additive bf16 mask [seq,seq]
+// (q [heads,seq,dim], k/v [kv_heads,seq,dim] head-major; out [seq,heads,dim])
+bool attention_materialised(const void* q, const void* k, const void* v, const void* mask, void* scores, void* probs,
+                            void* out, int heads, int kv_heads, int seq, int dim, float scaling, cudaStream_t st);
 bool rmsnorm(const void* x, const void* w, void* y, int rows, int cols, float eps, cudaStream_t st);
 bool rmsnorm_mod(const void* x, const void* w, const void* scale, const void* shift, void* y, int rows, int cols,
                  float eps, cudaStream_t st);

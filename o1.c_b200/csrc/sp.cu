@@ -22,6 +22,7 @@
 #include "../../include/o1_b200.h"
 
 #include <math.h>
+#include <stdlib.h>
 #include <string.h>
 
 using namespace o1;
@@ -35,7 +36,7 @@ using namespace o1;
 extern "C" void o1_launch_count_add(int n);
 
 static bool sp_ok(const o1_sp_ws* w) {
-    return w && w->sp_size >= 1 && w->sp_rank >= 0 && w->sp_rank < w->sp_size && w->head_dim == 128 &&
+    return w && w->sp_size >= 1 && w->sp_size <= O1_SP_MAX_RANKS && w->sp_rank >= 0 && w->sp_rank < w->sp_size && w->head_dim == 128 &&
            w->heads % w->sp_size == 0 && w->kv_heads % w->sp_size == 0 && w->S == w->rows * w->sp_size &&
            w->row0 == w->sp_rank * w->rows && (w->hidden % 256) == 0 && (w->ff % 128) == 0 &&
            ((w->heads / w->sp_size) * 128) % 128 == 0;
@@ -63,7 +64,7 @@ static bool peers_ok(const o1_sp_ws* w, const o1_sp_peers* pt) {
     if (!pt) return false;
     for (int p = 0; p < w->sp_size; ++p)
         if (!pt->gath[p] || !pt->recv[p] || !pt->flags[p]) return false;
-    return pt->rope_full != nullptr;
+    return true;
 }
 
 extern "C" {
@@ -112,29 +113,31 @@ hd_status o1_sp_rope_table_full(const o1_sp_ws* w, const o1_sp_peers* pt, const 
 }
 
 // in [rows, hidden] -> every rank's gath rows [rank*rows, (rank+1)*rows): RMSNorm, then q/k/v projections whose
-// epilogues store head group p of the output into rank p's gath (raw values: norm + rope follow after the barrier)
+// epilogues store head group p of the output into rank p's gath.  The per-head RMSNorm + rotary of q and k
+// (block.c:266-289) run in the SENDER's epilogue, on its own rows' cos|sin table (w->rope, o1_sp_rope_table): what
+// arrives is ready for attention, exactly as on one GPU.
 hd_status o1_sp_block_pre_direct(const hd_block_binding* bw, const o1_sp_ws* w, const o1_sp_peers* pt, const void* in) {
-    if (!sp_ok(w) || !peers_ok(w, pt) || !bw || !in) { hd_set_error("sp: bad arguments"); return HD_ERR_MISSING; }
+    if (!sp_ok(w) || !peers_ok(w, pt) || !bw || !in || !w->rope) { hd_set_error("sp: bad arguments"); return HD_ERR_MISSING; }
     cudaStream_t st = current_stream();
     const int P = w->sp_size, R = w->rows, H = w->hidden;
     const int qc = w->heads * 128, kc = w->kv_heads * 128;
     const int qcp = qc / P, kcp = kc / P, C = qcp + 2 * kcp;
-    void* tq[8]; void* tk[8]; void* tv[8];
+    void* tq[O1_SP_MAX_RANKS]; void* tk[O1_SP_MAX_RANKS]; void* tv[O1_SP_MAX_RANKS];
     for (int p = 0; p < P; ++p) {
         uint16_t* base = (uint16_t*)pt->gath[p] + (size_t)w->sp_rank * R * C;
         tq[p] = base; tk[p] = base + qcp; tv[p] = base + qcp + kcp;
     }
     SP_TRY(rmsnorm(in, bw->input_ln, w->ln, R, H, 1e-6f, st), "input_norm");
-    SP_TRY(gemm_bf16_ex(w->ln, H, bw->q_proj, nullptr, nullptr, C, R, qc, H, EPI_STORE, nullptr, nullptr, 0, 0.f, 0,
-                        qcp, 0, 0, 0, st, tq), "q_proj");
-    SP_TRY(gemm_bf16_ex(w->ln, H, bw->k_proj, nullptr, nullptr, C, R, kc, H, EPI_STORE, nullptr, nullptr, 0, 0.f, 0,
-                        kcp, 0, 0, 0, st, tk), "k_proj");
+    SP_TRY(gemm_bf16_ex(w->ln, H, bw->q_proj, nullptr, nullptr, C, R, qc, H, EPI_QKNORM, bw->q_norm, w->rope, 0, 1e-6f, 0,
+                        qcp, 0, 0, 0, st, tq), "q_proj+norm+rope");
+    SP_TRY(gemm_bf16_ex(w->ln, H, bw->k_proj, nullptr, nullptr, C, R, kc, H, EPI_QKNORM, bw->k_norm, w->rope, 0, 1e-6f, 0,
+                        kcp, 0, 0, 0, st, tk), "k_proj+norm+rope");
     SP_TRY(gemm_bf16_ex(w->ln, H, bw->v_proj, nullptr, nullptr, C, R, kc, H, EPI_STORE, nullptr, nullptr, 0, 0.f, 0,
                         kcp, 0, 0, 0, st, tv), "v_proj");
     return HD_OK;
 }
 
-// own gath [S][C] (all rows, this rank's heads; complete after the barrier) -> per-head norm + rope in place ->
+// own gath [S][C] (all rows, this rank's heads, normed and rotated by their senders; complete after the barrier) ->
 // attention whose epilogue stores row block p into rank p's recv slab [rank]
 hd_status o1_sp_block_attn_direct(const hd_block_binding* bw, const o1_sp_ws* w, const o1_sp_peers* pt) {
     if (!sp_ok(w) || !peers_ok(w, pt) || !bw) { hd_set_error("sp: bad arguments"); return HD_ERR_MISSING; }
@@ -142,10 +145,7 @@ hd_status o1_sp_block_attn_direct(const hd_block_binding* bw, const o1_sp_ws* w,
     const int P = w->sp_size, R = w->rows;
     const int qcp = w->heads * 128 / P, kcp = w->kv_heads * 128 / P, C = qcp + 2 * kcp;
     uint16_t* g = (uint16_t*)pt->gath[w->sp_rank];
-    const float* rope = (const float*)pt->rope_full;
-    SP_TRY(qk_norm_rope(g, C, w->S, w->heads / P, bw->q_norm, rope, 1e-6f, st), "q_norm_rope");
-    SP_TRY(qk_norm_rope(g + qcp, C, w->S, w->kv_heads / P, bw->k_norm, rope, 1e-6f, st), "k_norm_rope");
-    void* to[8];
+    void* to[O1_SP_MAX_RANKS];
     for (int p = 0; p < P; ++p) to[p] = (uint16_t*)pt->recv[p] + (size_t)w->sp_rank * R * qcp;
     SP_TRY(flash_attention_tab(g, C, g + qcp, C, g + qcp + kcp, C, to, R, qcp, w->S, w->heads / P, w->kv_heads / P,
                                w->ar_len, (float)(1.0 / sqrt(128.0)), st, w->swi, (size_t)w->rows * w->ff * 2),
@@ -277,6 +277,124 @@ hd_status o1_sp_forward_end(const hd_forward_binding* bw, const o1_sp_ws* w, con
     SP_TRY(gemm_bf16(norm_scratch, bw->fl_w, nullptr, out_local, w->rows, 3072, w->hidden, EPI_BIAS, bw->fl_b, nullptr,
                      0.f, 0, st), "head");
     return HD_OK;
+}
+
+// ------------------------------------------------------------------ whole sharded forward / CFG step in one call
+// The loop a C host would otherwise write around the stage functions (direct form):
+//   rope table of own rows, embedding, then per block  pre_direct, barrier, attn_direct, barrier, post
+//   (DeepStack add after blocks 0..2 on ranks that own <image_pad> rows), final norm + head.
+// Everything is enqueued on the current stream; nothing synchronises or allocates.
+hd_status o1_sp_forward(const hd_forward_binding* bw, o1_sp_ctx* c, const int64_t* ids_global, const float* pos_global,
+                        const void* vin_local, const float* timestep_dev, int tms_token_id, void* out_local) {
+    if (!c || !bw || !ids_global || !pos_global || !timestep_dev || !out_local || !c->hid[0] || !c->hid[1] || !c->small) {
+        hd_set_error("sp_forward: null argument");
+        return HD_ERR_MISSING;
+    }
+    const o1_sp_ws* w = &c->ws;
+    if (!sp_ok(w) || !peers_ok(w, &c->peers)) { hd_set_error("sp_forward: bad workspace or peer table"); return HD_ERR_MISSING; }
+    hd_status s = o1_sp_rope_table(w, pos_global);
+    if (s != HD_OK) return s;
+    s = o1_sp_forward_begin(bw, w, ids_global, vin_local, timestep_dev, c->small, c->xe_stage, tms_token_id, c->hid[0]);
+    if (s != HD_OK) return s;
+    void* cur = c->hid[0];
+    void* nxt = c->hid[1];
+    const bool visual = c->visual_mask && c->image_embeds && c->visual_rows > 0;
+    if (visual) {
+        s = o1_sp_visual_scatter(w, c->visual_mask, c->image_embeds, c->embed_row0, cur, nxt);
+        if (s != HD_OK) return s;
+        void* t = cur; cur = nxt; nxt = t;
+    }
+    for (int l = 0; l < bw->n_layers; ++l) {
+        const hd_block_binding* bb = &bw->blocks[l];
+        if ((s = o1_sp_block_pre_direct(bb, w, &c->peers, cur)) != HD_OK) return s;
+        if ((s = o1_sp_barrier(w, &c->peers, ++c->epoch)) != HD_OK) return s;
+        if ((s = o1_sp_block_attn_direct(bb, w, &c->peers)) != HD_OK) return s;
+        if ((s = o1_sp_barrier(w, &c->peers, ++c->epoch)) != HD_OK) return s;
+        if ((s = o1_sp_block_post(bb, w, cur, nxt)) != HD_OK) return s;
+        if (visual && l < 3 && c->deepstack[l]) {
+            // the block's output is in nxt; the sum goes back into cur, which stays the next block's input
+            if ((s = o1_sp_deepstack(w, c->visual_mask, c->deepstack[l], c->embed_row0, nxt, cur)) != HD_OK) return s;
+        } else {
+            void* t = cur; cur = nxt; nxt = t;
+        }
+    }
+    return o1_sp_forward_end(bw, w, cur, w->ln, out_local);
+}
+
+// One CFG denoise step of a rank of a (CFG pair) x (SP group) layout: this rank's branch forward, exchange of the
+// predictions with the CFG partner (same sp_rank, other branch) by plain device-to-device copies into the partner's
+// mapped buffer + a two-rank flag barrier, then the fused scheduler update on this rank's target rows.  Both
+// partners apply the identical kernel to identical inputs, so their latents stay bit-identical.  Prediction
+// buffers are double-buffered by step parity: the partner's previous read of a slot precedes its arrival at the
+// barrier this rank has already passed.
+hd_status o1_denoise_step_cfg_sp(const hd_forward_binding* bw, o1_sp_ctx* c, o1_cfg_pair* pr, const int64_t* ids_global,
+                                 const float* pos_global, const void* z_local, int n_step_rows, const float* timestep_dev,
+                                 float sigma, float sigma_next, float guidance, int tms_token_id, void* xp_local,
+                                 void* z_next_local) {
+    if (!c || !pr || !xp_local || (pr->branch != 0 && pr->branch != 1) || !pr->xp_local[0] || !pr->xp_local[1] ||
+        !pr->xp_partner[0] || !pr->xp_partner[1] || !pr->flags_local || !pr->flags_partner) {
+        hd_set_error("denoise_step_sp: null argument");
+        return HD_ERR_MISSING;
+    }
+    const o1_sp_ws* w = &c->ws;
+    hd_status s = o1_sp_forward(bw, c, ids_global, pos_global, z_local, timestep_dev, tms_token_id, xp_local);
+    if (s != HD_OK) return s;
+    cudaStream_t st = current_stream();
+    // this rank's image rows of the prediction (text rows come first on the ranks that own any)
+    const int t0 = w->row0 < w->T ? w->row0 : w->T;
+    const int t1 = (w->row0 + w->rows) < w->T ? (w->row0 + w->rows) : w->T;
+    const int n_text = t1 - t0, n_img = w->rows - n_text;
+    const int par = (int)(pr->step & 1u);
+    const size_t bytes = (size_t)n_img * 3072 * 2, slot = (size_t)pr->branch * n_img * 3072;
+    const uint16_t* mine = (const uint16_t*)xp_local + (size_t)n_text * 3072;
+    if (bytes) {
+        cudaError_t e = cudaMemcpyAsync((uint16_t*)pr->xp_local[par] + slot, mine, bytes, cudaMemcpyDeviceToDevice, st);
+        if (e == cudaSuccess)
+            e = cudaMemcpyAsync((uint16_t*)pr->xp_partner[par] + slot, mine, bytes, cudaMemcpyDeviceToDevice, st);
+        if (e != cudaSuccess) { hd_set_error("denoise_step_sp: prediction exchange: %s", cudaGetErrorString(e)); return HD_ERR_IO; }
+        o1_launch_count_add(2);
+    }
+    // two-rank barrier with the partner: rank index = branch
+    o1_sp_peers pt;
+    memset(&pt, 0, sizeof(pt));
+    pt.flags[pr->branch] = pr->flags_local;
+    pt.flags[pr->branch ^ 1] = pr->flags_partner;
+    sp_barrier_kernel<<<1, 32, 0, st>>>(pt, 2, pr->branch, ++pr->step, device_error_word());
+    o1_launch_count_add(1);
+    if (cudaGetLastError() != cudaSuccess) { hd_set_error("denoise_step_sp: barrier launch failed"); return HD_ERR_RUNTIME; }
+    if (n_step_rows > 0) {
+        const uint16_t* xc = (const uint16_t*)pr->xp_local[par];
+        const uint16_t* xu = xc + (size_t)n_img * 3072;
+        if (!sched_cfg_flow_step(z_local, xc, xu, sigma, sigma_next, guidance, z_next_local, (size_t)n_step_rows * 3072, st)) {
+            hd_set_error("denoise_step_sp: scheduler: %s", hd_cuda_last_error());
+            return HD_ERR_RUNTIME;
+        }
+        o1_launch_count_add(1);
+    }
+    return HD_OK;
+}
+
+// Layout of `world` GPUs over images, CFG branches and sequence-parallel ranks:
+//   1 GPU: both branches in turn; 2: CFG pair; 4: pair x SP2; 8: pair x SP4; more: several images.
+// Environment overrides (read on every call): O1_GPUS (world), O1_CFG_SPLIT (0: both branches on every GPU,
+// 1: split the pair), O1_SP_DEGREE (ranks per forward; must divide the 8 KV heads).
+int o1_parallel_layout(int world, int rank, int* image, int* branch, int* sp_rank, int* sp_size) {
+    const char* e;
+    if ((e = getenv("O1_GPUS")) && atoi(e) > 0) world = atoi(e);
+    if (world <= 0 || rank < 0 || rank >= world) return -1;
+    int cfg_split = world >= 2 ? 1 : 0;
+    if ((e = getenv("O1_CFG_SPLIT"))) cfg_split = atoi(e) != 0 && world >= 2;
+    int sp = cfg_split ? world / 2 : world;
+    if (sp > O1_SP_MAX_RANKS) sp = O1_SP_MAX_RANKS;
+    if ((e = getenv("O1_SP_DEGREE")) && atoi(e) > 0) sp = atoi(e);
+    if (sp < 1 || (8 % sp) != 0) return -1;                    // must divide the KV heads
+    const int per_image = (cfg_split ? 2 : 1) * sp;
+    if (per_image > world || (world % per_image) != 0) return -1;
+    if (image) *image = rank / per_image;
+    if (branch) *branch = cfg_split ? (rank % per_image) / sp : -1;
+    if (sp_rank) *sp_rank = rank % sp;
+    if (sp_size) *sp_size = sp;
+    return world / per_image;                                  // images in flight
 }
 
 }  // extern "C"

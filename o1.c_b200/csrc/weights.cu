@@ -99,7 +99,14 @@ bool parse_gguf(const char* path, GgufIndex* out) {
         const uint32_t nd = r.get<uint32_t>();
         if (nd > 8) { r.ok = false; break; }
         ti.numel = 1;
-        for (uint32_t d = 0; d < nd; ++d) { ti.dims.push_back(r.get<uint64_t>()); ti.numel *= ti.dims.back(); }
+        for (uint32_t d = 0; d < nd; ++d) {
+            const uint64_t dim = r.get<uint64_t>();
+            ti.dims.push_back(dim);
+            // element counts beyond 2^40 cannot be real (and their byte size could wrap 64 bits)
+            if (dim == 0 || dim > (1ull << 40) || ti.numel > (1ull << 40) / dim) { r.ok = false; break; }
+            ti.numel *= dim;
+        }
+        if (!r.ok) break;
         ti.type = r.get<uint32_t>();
         ti.offset = r.get<uint64_t>();
         if (ti.type != 0 && ti.type != 1 && ti.type != 30) {
@@ -112,7 +119,21 @@ bool parse_gguf(const char* path, GgufIndex* out) {
     if (!r.ok || out->alignment == 0) { werr("gguf: truncated or malformed header in %s", path); fclose(f); return false; }
     const uint64_t pos = (uint64_t)ftello(f);
     out->data_start = (pos + out->alignment - 1) / out->alignment * out->alignment;
+    // every tensor's payload must lie inside the file: a truncated pack or a corrupt offset fails here,
+    // before any device memory is sized from the header
+    uint64_t file_bytes = 0;
+    if (fseeko(f, 0, SEEK_END) == 0) file_bytes = (uint64_t)ftello(f);
     fclose(f);
+    for (const TensorInfo& t : out->tensors) {
+        const uint64_t bytes = t.numel * (t.type == 0 ? 4u : 2u);
+        if (t.offset > file_bytes || out->data_start > file_bytes - t.offset ||
+            bytes > file_bytes - t.offset - out->data_start) {
+            werr("gguf: tensor %s (%llu bytes at offset %llu) lies outside %s (%llu bytes)", t.name.c_str(),
+                 (unsigned long long)bytes, (unsigned long long)(out->data_start + t.offset), path,
+                 (unsigned long long)file_bytes);
+            return false;
+        }
+    }
     return true;
 }
 
@@ -189,11 +210,26 @@ static hd_status load_gguf(const char* gguf_path, int device_id, hd_weight_store
     out->device_mem_bytes = (int64_t)prop.totalGlobalMem;
 
     const size_t n = idx.tensors.size();
+    // A pack of BF16 tensors at 256-byte aligned offsets keeps the file's own layout, as the reference's loader
+    // does (src/model/weights.c:536-650: arena = payload bytes, tensor i at arena + its file offset), so a host
+    // that addresses tensors by offset finds them where it expects.  Packs with F32 / F16 tensors (converted to
+    // bf16 here, half or equal size) or unaligned offsets are laid out cumulatively instead.
     std::vector<uint64_t> arena_off(n);
     uint64_t total = 0;
-    for (size_t i = 0; i < n; ++i) {
-        arena_off[i] = total;
-        total += (idx.tensors[i].numel * 2 + 255) & ~(uint64_t)255;
+    bool file_layout = true;
+    for (size_t i = 0; i < n; ++i)
+        if (idx.tensors[i].type != 30 || (idx.tensors[i].offset & 255)) file_layout = false;
+    if (file_layout) {
+        for (size_t i = 0; i < n; ++i) {
+            arena_off[i] = idx.tensors[i].offset;
+            total = std::max<uint64_t>(total, idx.tensors[i].offset + idx.tensors[i].numel * 2);
+        }
+        total = (total + 255) & ~(uint64_t)255;
+    } else {
+        for (size_t i = 0; i < n; ++i) {
+            arena_off[i] = total;
+            total += (idx.tensors[i].numel * 2 + 255) & ~(uint64_t)255;
+        }
     }
     out->allocs = (hd_device_alloc*)calloc(n, sizeof(hd_device_alloc));
     if (!out->allocs) { werr("weights: out of host memory"); return HD_ERR_OOM; }
@@ -203,6 +239,14 @@ static hd_status load_gguf(const char* gguf_path, int device_id, hd_weight_store
         free(out->allocs); out->allocs = nullptr;
         return HD_ERR_OOM;
     }
+    // the gaps between tensors hold zeros, as in a pack's padded payload (the reference's loader copies the
+    // payload whole, src/model/weights.c:566-612)
+    if (cudaMemset(out->arena_ptr, 0, total) != cudaSuccess) {
+        werr("weights: clearing the arena failed");
+        cudaFree(out->arena_ptr); out->arena_ptr = nullptr;
+        free(out->allocs); out->allocs = nullptr;
+        return HD_ERR_RUNTIME;
+    }
     out->arena_bytes = (int64_t)total;
     out->device_bytes_allocated = (int64_t)total;
     out->n_allocations = 1;
@@ -210,7 +254,7 @@ static hd_status load_gguf(const char* gguf_path, int device_id, hd_weight_store
 
     const size_t SLOT = 64u << 20;
     uint8_t* pinned[2] = {nullptr, nullptr};
-    cudaEvent_t done[2];
+    cudaEvent_t done[2] = {nullptr, nullptr};
     cudaStream_t st = nullptr;
     FILE* f = fopen(gguf_path, "rb");
     std::vector<uint8_t> raw;
@@ -261,7 +305,10 @@ static hd_status load_gguf(const char* gguf_path, int device_id, hd_weight_store
     }
     if (st && cudaStreamSynchronize(st) != cudaSuccess && rc == HD_OK) { werr("weights: upload stream failed"); rc = HD_ERR_RUNTIME; }
     if (f) fclose(f);
-    for (int s = 0; s < 2; ++s) if (pinned[s]) { cudaFreeHost(pinned[s]); cudaEventDestroy(done[s]); }
+    for (int s = 0; s < 2; ++s) {
+        if (pinned[s]) cudaFreeHost(pinned[s]);
+        if (done[s]) cudaEventDestroy(done[s]);
+    }
     out->upload_stream = st;
     out->gemm = hd_gemm_runtime_init(device_id, 0);
     if (rc != HD_OK) hd_weight_store_free(out);

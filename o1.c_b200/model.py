@@ -290,6 +290,24 @@ class Engine:
         check(rc, "o1_denoise_step_cfg_ref")
         return z_next
 
+    def denoise_step_cfg_branches(self, cond, uncond, z, sigma, sigma_next, guidance, z_next=None):
+        """CFG step whose branches have their own sequences: cond / uncond = (ids [T_b], pos [3, T_b + I],
+        ar_len) with T_b <= the text length this engine was sized for."""
+        from . import CfgBranch
+        if z_next is None:
+            z_next = torch.empty_like(z)
+        self.timestep.fill_(1.0 - float(sigma))
+        br = []
+        for ids, pos, ar in (cond, uncond):
+            assert ids.numel() <= self.T
+            br.append(CfgBranch(ids=ids.data_ptr(), text_len=ids.numel(), pos_f32=pos.data_ptr(), ar_len=ar))
+        rc = lib.o1_denoise_step_cfg_branches(C.byref(self.w.binding), C.byref(self.ws), C.byref(br[0]),
+                                              C.byref(br[1]), ptr(z), self.I, self.I, ptr(self.timestep),
+                                              float(sigma), float(sigma_next), float(guidance), ptr(self.xp),
+                                              ptr(z_next), *self.dimargs, TMS_ID)
+        check(rc, "o1_denoise_step_cfg_branches")
+        return z_next
+
     def denoise_step_cfg_host(self, ids_c, ids_u, pos, z_host, z_dev, sigma, sigma_next, guidance,
                               z_next_dev, z_next_host):
         """Same step through host (pinned) latents: H2D, step, D2H, synchronise."""

@@ -27,6 +27,19 @@ class SpPeers(C.Structure):
     _fields_ = [("gath", c_void_p * 8), ("recv", c_void_p * 8), ("flags", c_void_p * 8), ("rope_full", c_void_p)]
 
 
+class SpCtx(C.Structure):
+    """o1_sp_ctx (include/o1_b200.h): everything o1_sp_forward needs for one rank."""
+    _fields_ = [("ws", SpWs), ("peers", SpPeers), ("hid", c_void_p * 2), ("small", c_void_p), ("xe_stage", c_void_p),
+                ("epoch", C.c_uint), ("visual_mask", c_void_p), ("image_embeds", c_void_p), ("deepstack", c_void_p * 3),
+                ("embed_row0", c_int), ("visual_rows", c_int)]
+
+
+class CfgPair(C.Structure):
+    """o1_cfg_pair (include/o1_b200.h): prediction exchange with the CFG partner."""
+    _fields_ = [("branch", c_int), ("xp_local", c_void_p * 2), ("xp_partner", c_void_p * 2), ("flags_local", c_void_p),
+                ("flags_partner", c_void_p), ("step", C.c_uint)]
+
+
 for _name, _res, _args in (("o1_peer_alloc", c_int, (C.POINTER(c_void_p), C.c_size_t)),
                            ("o1_peer_free", c_int, (c_void_p,)),
                            ("o1_peer_export", c_int, (c_void_p, C.POINTER(C.c_ubyte))),
@@ -49,20 +62,34 @@ for _name, _args in (("o1_sp_rope_table", (C.POINTER(SpWs), c_void_p)),
                      ("o1_sp_forward_begin", (C.POINTER(ForwardBinding), C.POINTER(SpWs), c_void_p, c_void_p,
                                               c_void_p, c_void_p, c_void_p, c_int, c_void_p)),
                      ("o1_sp_forward_end", (C.POINTER(ForwardBinding), C.POINTER(SpWs), c_void_p, c_void_p,
-                                            c_void_p))):
+                                            c_void_p)),
+                     ("o1_sp_forward", (C.POINTER(ForwardBinding), C.POINTER(SpCtx), c_void_p, c_void_p, c_void_p,
+                                        c_void_p, c_int, c_void_p)),
+                     ("o1_denoise_step_cfg_sp", (C.POINTER(ForwardBinding), C.POINTER(SpCtx), C.POINTER(CfgPair), c_void_p,
+                                                 c_void_p, c_void_p, c_int, c_void_p, C.c_float, C.c_float, C.c_float,
+                                                 c_int, c_void_p, c_void_p)),
+                     ("o1_parallel_layout", (c_int, c_int, C.POINTER(c_int), C.POINTER(c_int), C.POINTER(c_int),
+                                             C.POINTER(c_int)))):
     _f = getattr(lib, _name)
     _f.restype, _f.argtypes = c_int, list(_args)
 
 
 def layout(world, cfg=True, max_sp=8):
     """rank -> (image index, cfg branch, sp_rank), plus sp_size, for `world` GPUs working on ONE image
-    when possible: world 1 -> both branches on one GPU; 2 -> CFG pair; 4 -> CFG x SP2; 8 -> CFG x SP4."""
+    when possible: world 1 -> both branches on one GPU; 2 -> CFG pair; 4 -> CFG x SP2; 8 -> CFG x SP4.
+    With cfg=True this is the library's o1_parallel_layout (which honours O1_CFG_SPLIT / O1_SP_DEGREE)."""
     if world == 1 or not cfg:
         sp = min(world, max_sp)
         return {r: (r // sp, None, r % sp) for r in range(world)}, sp
-    sp = min(world // 2, max_sp)
-    per_image = 2 * sp
-    return {r: (r // per_image, (r % per_image) // sp, r % sp) for r in range(world)}, sp
+    out, sp_size = {}, None
+    for r in range(world):
+        img, br, sr, sp = c_int(), c_int(), c_int(), c_int()
+        n = lib.o1_parallel_layout(world, r, C.byref(img), C.byref(br), C.byref(sr), C.byref(sp))
+        if n < 0:
+            raise ValueError(f"no layout for {world} GPUs with the O1_CFG_SPLIT / O1_SP_DEGREE in the environment")
+        out[r] = (img.value, None if br.value < 0 else br.value, sr.value)
+        sp_size = sp.value
+    return out, sp_size
 
 
 def shard_rows(S, T, P, r):
@@ -112,7 +139,6 @@ class EngineSP:
             if lib.o1_peer_alloc(C.byref(reg), self.region_bytes) != 0:
                 raise RuntimeError("peer region allocation failed")
             self.region = reg.value
-            self.rope_full = torch.empty(S, 128, dtype=torch.float32, device=dev)
             gath_ptr, recv_ptr = self.region, self.region + self.gath_bytes
             send_ptr = attn_ptr = 0
         else:
@@ -171,7 +197,6 @@ class EngineSP:
             pt.gath[p] = base
             pt.recv[p] = base + self.gath_bytes
             pt.flags[p] = base + self.gath_bytes + self.recv_bytes
-        pt.rope_full = self.rope_full.data_ptr()
         self.peers, self._opened = pt, list(opened)
 
     def barrier(self):
@@ -210,7 +235,7 @@ class EngineSP:
 
     def _stages_direct(self, ids, pos, vin_local, out_local):
         ws, w, pt = C.byref(self.ws), self.w, C.byref(self.peers)
-        check(lib.o1_sp_rope_table_full(ws, pt, ptr(pos)), "sp_rope_table_full")
+        check(lib.o1_sp_rope_table(ws, ptr(pos)), "sp_rope_table")      # own rows: norm + rope run in the sender's epilogue
         check(lib.o1_sp_forward_begin(C.byref(w.binding), ws, ptr(ids), ptr(vin_local), ptr(self.timestep),
                                       ptr(self.small), ptr(self.xe_stage), TMS_ID, ptr(self.hid[0])), "sp_begin")
         cur, nxt = self._visual_after_embed(*self.hid)
@@ -224,10 +249,40 @@ class EngineSP:
             cur, nxt = self._visual_after_block(l, nxt, cur)
         check(lib.o1_sp_forward_end(C.byref(w.binding), ws, ptr(cur), ptr(self.ln), ptr(out_local)), "sp_end")
 
+    def ctx(self):
+        """o1_sp_ctx of this rank (direct form, after connect())."""
+        if getattr(self, "_ctx", None) is None:
+            c = SpCtx()
+            c.ws, c.peers = self.ws, self.peers
+            c.hid[0], c.hid[1] = self.hid[0].data_ptr(), self.hid[1].data_ptr()
+            c.small, c.xe_stage, c.epoch = self.small.data_ptr(), self.xe_stage.data_ptr(), self.epoch
+            if self.visual is not None:
+                mask, emb, dss, first = self.visual
+                c.visual_mask, c.image_embeds, c.embed_row0 = mask.data_ptr(), emb.data_ptr(), first
+                c.visual_rows = int(mask[self.row0:self.row0 + self.rows].sum().item())
+                for k in range(3):
+                    c.deepstack[k] = dss[k].data_ptr()
+            self._ctx = c
+        return self._ctx
+
+    def forward_c(self, ids, pos, vin_local, t, out_local=None):
+        """The same forward driven by ONE library call (o1_sp_forward) instead of the stage-by-stage loop."""
+        if out_local is None:
+            out_local = torch.empty(self.rows, PATCH_DIM, dtype=torch.bfloat16, device=self.w.device)
+        self.timestep.fill_(float(t))
+        c = self.ctx()
+        c.epoch = max(c.epoch, self.epoch)          # one monotonic epoch sequence whichever path ran before
+        check(lib.o1_sp_forward(C.byref(self.w.binding), C.byref(c), ptr(ids), ptr(pos), ptr(vin_local),
+                                ptr(self.timestep), TMS_ID, ptr(out_local)), "o1_sp_forward")
+        self.epoch = c.epoch
+        return out_local
+
     def forward(self, ids, pos, vin_local, t, out_local=None):
         """x_pred rows of this rank, [rows, 3072] bf16."""
         if out_local is None:
             out_local = torch.empty(self.rows, PATCH_DIM, dtype=torch.bfloat16, device=self.w.device)
+        if self.direct and self.peers is not None and getattr(self, "c_driver", False):
+            return self.forward_c(ids, pos, vin_local, t, out_local)
         for kind, src, dst in self.stages(ids, pos, vin_local, t, out_local):
             if self.P == 1:
                 continue
@@ -278,6 +333,51 @@ def connect_direct(engine, group):
     torch.cuda.synchronize()
     dist.barrier(group=group)      # every region is zeroed and mapped before the first store into it
     return True
+
+
+class CfgPairLink:
+    """The CFG partner's prediction buffers and flags, mapped through CUDA IPC (o1_cfg_pair).  One region per
+    rank: [parity 0 | parity 1] x [2 branches][local image rows][3072] bf16, then 256 bytes of flags."""
+
+    def __init__(self, engine, branch, group):
+        import torch.distributed as dist
+        self.n_img = engine.i1 - engine.i0
+        self.slot_bytes = 2 * self.n_img * PATCH_DIM * 2
+        self.bytes = 2 * self.slot_bytes + 256
+        reg = c_void_p()
+        if lib.o1_peer_alloc(C.byref(reg), max(self.bytes, 512)) != 0:
+            raise RuntimeError("pair region allocation failed")
+        self.region, self.partner = reg.value, None
+        h = (C.c_ubyte * 64)()
+        ok = lib.o1_peer_export(self.region, h) == 0
+        handles = [None, None]
+        dist.all_gather_object(handles, bytes(h) if ok else None, group=group)
+        other = handles[branch ^ 1]
+        q = c_void_p()
+        if ok and other is not None and lib.o1_peer_open((C.c_ubyte * 64).from_buffer_copy(other), C.byref(q)) == 0:
+            self.partner = q.value
+        flag = torch.tensor([1 if self.partner else 0], device=engine.w.device, dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+        self.ok = int(flag.item()) == 1
+        self.pair = CfgPair()
+        if self.ok:
+            p = self.pair
+            p.branch = branch
+            for k in range(2):
+                p.xp_local[k] = self.region + k * self.slot_bytes
+                p.xp_partner[k] = self.partner + k * self.slot_bytes
+            p.flags_local, p.flags_partner = self.region + 2 * self.slot_bytes, self.partner + 2 * self.slot_bytes
+            p.step = 0
+            torch.cuda.synchronize()
+            dist.barrier(group=group)
+
+    def close(self):
+        if self.partner:
+            lib.o1_peer_close(self.partner)
+            self.partner = None
+        if self.region:
+            lib.o1_peer_free(self.region)
+            self.region = None
 
 
 def run_emulated(engines, ids, pos, vin, t):

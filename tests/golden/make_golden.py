@@ -9,6 +9,12 @@ needed to RUN the tests, which only read the files written here.
   seq_t2i.npz         : hd_seq_t2i position ids and mask-derived ar_len for three geometries
   seq_ref.npz         : hd_seq_build ids / position ids / ar_len for K = 1 and K = 4 references
   sigmas_ref.json     : hd_scheduler_derive_{dev,flash,flow_match,default} outputs
+  lora_ref.npz        : merged weights from the reference's Python LoRA contract
+                        (tools/lora/tests/test_lora_formula.py merge_linear + tools/lora/merge_gguf.py
+                        f32_to_bf16_bytes, i.e. the "sequential-bf16-v1" merge of merge_gguf.py:164-171)
+  decode_ref.npz      : hd_decode_to_rgb (src/runtime/decode.c) on a seeded latent
+  ref_convert_small.gguf / .npz : a miniature model written by the reference's own converter
+                        (tools/hidream_convert.py run on a small safetensors shard) and the bf16 bits it must hold
 """
 import ctypes as C
 import json
@@ -19,7 +25,7 @@ import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REF = os.environ.get("O1_REFERENCE", "/root/reference")
+REF = os.environ.get("O1_REFERENCE", os.path.join(ROOT, "..", "reference"))
 REF_LIB = os.path.join(ROOT, "oracle", "_ref", "libo1ref.so")
 
 
@@ -157,7 +163,88 @@ def main():
             n = f(C.byref(s), 8.0)
         sig[name] = [float(np.float32(s.sigmas[i])) for i in range(n)]
     json.dump(sig, open(os.path.join(HERE, "sigmas_ref.json"), "w"))
+    lora_fixture()
+    decode_fixture(ref)
+    converter_fixture()
     print("fixtures written to", HERE)
+
+
+def _bf16_bits(a):
+    u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+def lora_fixture():
+    """W' = bf16(f32(W) + multiplier * alpha/rank * up @ down), computed by the reference's own Python:
+    merge_linear of tools/lora/tests/test_lora_formula.py:20 on fp32 arrays (what merge_gguf.py:164-171
+    evaluates) and the bf16 rounding of merge_gguf.py:44-49."""
+    sys.path.insert(0, os.path.join(REF, "tools", "lora"))
+    sys.path.insert(0, os.path.join(REF, "tools", "lora", "tests"))
+    from test_lora_formula import merge_linear
+    from merge_gguf import f32_to_bf16_bytes
+    rng = np.random.default_rng(20240607)
+    out = {}
+    cases = [(96, 160, 8, 16.0, 1.0), (256, 128, 64, 64.0, 1.0), (48, 72, 4, 2.0, 0.8), (128, 384, 16, 16.0, -0.5)]
+    for i, (N, K, R, alpha, mult) in enumerate(cases):
+        w_bits = _bf16_bits(rng.standard_normal((N, K)).astype(np.float32) * 0.02)
+        w_f32 = (w_bits.astype(np.uint32) << 16).view(np.float32).reshape(N, K)
+        up = (rng.standard_normal((N, R)) * 0.05).astype(np.float32)
+        down = (rng.standard_normal((R, K)) * 0.05).astype(np.float32)
+        merged = merge_linear(w_f32, up, down, np.float32(alpha), np.float32(R), np.float32(mult))
+        assert merged.dtype == np.float32
+        bits = np.frombuffer(f32_to_bf16_bytes(merged), dtype=np.uint16).reshape(N, K)
+        out[f"c{i}_w"], out[f"c{i}_up"], out[f"c{i}_down"], out[f"c{i}_merged"] = w_bits, up, down, bits
+        out[f"c{i}_meta"] = np.array([N, K, R, alpha, mult], dtype=np.float64)
+    out["n_cases"] = np.array(len(cases))
+    np.savez_compressed(os.path.join(HERE, "lora_ref.npz"), **out)
+
+
+def decode_fixture(ref):
+    """hd_decode_to_rgb of src/runtime/decode.c:5-27 on a seeded latent that covers values beyond [-1, 1],
+    exact .5 ties of the rounding and negative zero."""
+    rng = np.random.default_rng(77)
+    gh, gw, p = 3, 5, 32
+    z = _bf16_bits(rng.standard_normal((gh * gw, 3 * p * p)).astype(np.float32) * 0.7)
+    zf = (z.astype(np.uint32) << 16).view(np.float32)
+    zf.reshape(-1)[:6] = [-1.0, 1.0, -0.0, 0.00392156862, 1.5, -1.5]      # 0.0039..: (v+1)/2*255 = 128.0 (a tie-free probe)
+    z = _bf16_bits(zf)
+    zf = (z.astype(np.uint32) << 16).view(np.float32).copy()
+    rgb = np.zeros((gh * p, gw * p, 3), dtype=np.uint8)
+    ref.hd_decode_to_rgb.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]
+    ref.hd_decode_to_rgb.restype = None
+    ref.hd_decode_to_rgb(zf.ctypes.data_as(C.c_void_p), gh, gw, p, 3, rgb.ctypes.data_as(C.c_void_p))
+    np.savez_compressed(os.path.join(HERE, "decode_ref.npz"), z=z.reshape(gh * gw, 3 * p * p), rgb=rgb,
+                        geom=np.array([gh, gw, p]))
+
+
+def converter_fixture():
+    """A two-block miniature (tiny shapes, real tensor names) stored as one safetensors shard, converted by the
+    reference's own tools/hidream_convert.py.  F32 sources exercise its F32 -> BF16 path."""
+    import subprocess
+    import tempfile
+    from safetensors.numpy import save_file
+    rng = np.random.default_rng(5)
+    names = ["model.language_model.embed_tokens.weight", "model.language_model.norm.weight",
+             "model.t_embedder1.mlp.0.weight", "model.t_embedder1.mlp.0.bias", "model.t_embedder1.mlp.2.weight",
+             "model.t_embedder1.mlp.2.bias", "model.x_embedder.proj1.weight", "model.x_embedder.proj2.weight",
+             "model.x_embedder.proj2.bias", "model.final_layer2.linear.weight", "model.final_layer2.linear.bias"]
+    slots = ["self_attn.q_proj.weight", "self_attn.k_proj.weight", "self_attn.v_proj.weight", "self_attn.o_proj.weight",
+             "input_layernorm.weight", "post_attention_layernorm.weight", "mlp.gate_proj.weight", "mlp.up_proj.weight",
+             "mlp.down_proj.weight", "self_attn.q_norm.weight", "self_attn.k_norm.weight"]
+    for l in range(2):
+        names += [f"model.language_model.layers.{l}.{s}" for s in slots]
+    tensors = {}
+    for i, n in enumerate(names):
+        shape = (7, 24) if n.endswith("proj.weight") or "embed" in n or "linear.weight" in n or "mlp." in n else (40,)
+        tensors[n] = (rng.standard_normal(shape) * 0.3).astype(np.float32)
+    with tempfile.TemporaryDirectory() as d:
+        save_file(tensors, os.path.join(d, "model-00001-of-00001.safetensors"))
+        json.dump({"weight_map": {n: "model-00001-of-00001.safetensors" for n in names}},
+                  open(os.path.join(d, "model.safetensors.index.json"), "w"))
+        out = os.path.join(HERE, "ref_convert_small.gguf")
+        subprocess.run([sys.executable, os.path.join(REF, "tools", "hidream_convert.py"), "--source", d, "--output", out],
+                       check=True, stdout=subprocess.DEVNULL)
+    np.savez_compressed(os.path.join(HERE, "ref_convert_small.npz"), **{n: _bf16_bits(a) for n, a in tensors.items()})
 
 
 if __name__ == "__main__":

@@ -227,6 +227,35 @@ def metrics(got, ref):
     return nrmse, cos, float(np.abs(d).max()) if d.size else 0.0, bad
 
 
+def metrics_dev(got, ref):
+    """The same four numbers for two device tensors, reduced on the device in fp64 (tensors of 10^8
+    elements: the host path would copy and convert them first)."""
+    g, r = got.reshape(-1).double(), ref.reshape(-1).double()
+    bad = int((~torch.isfinite(g)).sum().item())
+    d = g - r
+    rms_ref = float(torch.sqrt(torch.mean(r * r)).item())
+    nrmse = float(torch.sqrt(torch.mean(d * d)).item()) / (rms_ref if rms_ref > 0 else 1.0)
+    den = float((torch.sqrt((g * g).sum()) * torch.sqrt((r * r).sum())).item())
+    cos = float((g * r).sum().item()) / den if den > 0 else (1.0 if not bool(d.any()) else 0.0)
+    return nrmse, cos, float(d.abs().max().item()) if d.numel() else 0.0, bad
+
+
+def bf16_ulp_of_max(ref):
+    """ULP(m) = 2^(floor(log2 m) - 7) at the tensor's largest magnitude (o1.c docs/M1_7_TOLERANCES.md:77-80)."""
+    import math
+    m = float(ref.float().abs().max().item()) if isinstance(ref, torch.Tensor) else float(np.abs(ref).max())
+    return 2.0 ** (math.floor(math.log2(m)) - 7) if m > 0 else 0.0
+
+
+def report(record):
+    """Appends one JSON line to the file named by O1_PARITY_REPORT (measured distances for the write-up)."""
+    path = os.environ.get("O1_PARITY_REPORT")
+    if path:
+        import json
+        with open(path, "a") as f:
+            f.write(json.dumps(record) + "\n")
+
+
 def assert_close(got, ref, cls, what=""):
     nrmse, cos, mx, bad = metrics(got, ref)
     lim_n, lim_c = TOL[cls]

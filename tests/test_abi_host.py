@@ -231,3 +231,71 @@ def test_bulk_and_threaded_rng_equals_the_scalar_stream(pkg):
     finally:
         lib.o1_torch_rng_free(h)
         orc.orc_rng_free(o)
+
+
+def test_gguf_header_that_points_outside_the_file_fails_closed(pkg, tmp_path):
+    """A corrupt or truncated pack must fail in the header check (HD_ERR_PARSE), before any device memory is
+    sized from it: tensor offset + size beyond the file, a dims product that wraps 64 bits, a zero dim."""
+    import struct
+    import numpy as np
+    path = str(tmp_path / "pack.gguf")
+    tensors = _small_pack(pkg, path)
+    raw = bytearray(open(path, "rb").read())
+    name0 = tensors[0][0].encode()
+    at = raw.find(name0) + len(name0)            # tensor record: n_dims u32, dims u64 x n, type u32, offset u64
+    nd = struct.unpack_from("<I", raw, at)[0]
+    off_at = at + 4 + 8 * nd + 4
+    store = pkg.WeightStore()
+
+    def probe(mutated):
+        p = tmp_path / "m.gguf"
+        p.write_bytes(bytes(mutated))
+        assert pkg.lib.o1_gguf_probe(str(p).encode(), -1, None, 0, None, None, None) == -1
+        assert pkg.lib.hd_weights_to_device_gguf(str(p).encode(), 0, C.byref(store)) == 2      # HD_ERR_PARSE
+        assert not store.arena_ptr
+        return pkg.lib.hd_weights_last_error()
+
+    m = bytearray(raw)
+    struct.pack_into("<Q", m, off_at, 1 << 40)                       # offset far beyond the file
+    assert b"lies outside" in probe(m)
+    m = bytearray(raw)
+    struct.pack_into("<Q", m, at + 4, 1 << 62)                       # dims product wraps
+    struct.pack_into("<Q", m, at + 12, 8)
+    assert b"malformed" in probe(m)
+    m = bytearray(raw)
+    struct.pack_into("<Q", m, at + 4, 0)                             # empty dimension
+    assert b"malformed" in probe(m)
+    assert b"lies outside" in probe(raw[:len(raw) - 300])            # payload cut short
+
+
+def test_sp_rejects_more_ranks_than_its_tables_hold(pkg):
+    """heads and kv_heads divisible by 16 would pass the divisibility checks; the peer tables and the kernels'
+    destination tables hold O1_SP_MAX_RANKS = 8 entries."""
+    from o1c_b200 import sp as spmod
+    ws = spmod.SpWs()
+    ws.sp_size, ws.sp_rank, ws.S, ws.T, ws.row0, ws.rows = 16, 0, 16 * 128, 16, 0, 128
+    ws.heads, ws.kv_heads, ws.hidden, ws.ff, ws.head_dim, ws.ar_len = 32, 16, 4096, 12288, 128, 15
+    bb = pkg.BlockBinding()
+    dummy = C.c_void_p(256)
+    assert pkg.lib.o1_sp_block_pre(C.byref(bb), C.byref(ws), dummy) == 6                       # HD_ERR_MISSING
+    assert pkg.lib.o1_sp_block_attn(C.byref(ws)) == 6
+    assert b"bad" in pkg.lib.hd_last_error()
+
+
+def test_reference_harness_mirrors_the_seeded_arena_rules(pkg):
+    """tests/refharness.py regenerates the product's seeded weights without loading the product library;
+    its seeds, shapes, arena offsets and sigma list must be the package's."""
+    import refharness as rh
+    assert rh.SLOT_NAMES == pkg.SLOT_NAMES and rh.GLOBAL_NAMES == pkg.GLOBAL_NAMES
+    for l, names in ((-1, pkg.GLOBAL_NAMES), (0, pkg.SLOT_NAMES), (35, pkg.SLOT_NAMES)):
+        for n in names:
+            assert rh.weight_seed(1234, l, n) == pkg.weight_seed(1234, l, n)
+            assert rh.tensor_shape(n) == pkg.tensor_shape(n)
+    assert rh.dev_sigmas() == pkg.dev_sigmas()
+    pos, ar = rh.seq_t2i(7, 3, 5)
+    pos2, ar2 = pkg.seq_t2i(7, 3, 5)
+    assert ar == ar2 and torch.equal(pos, pos2)
+    assert C.sizeof(rh.ForwardBinding) == C.sizeof(pkg.ForwardBinding)
+    assert C.sizeof(rh.ForwardWorkspace) == C.sizeof(pkg.ForwardWorkspace)
+    assert C.sizeof(rh.BlockBinding) == C.sizeof(pkg.BlockBinding)
+    assert C.sizeof(rh.ForwardDiagnostics) == C.sizeof(pkg.ForwardDiagnostics)

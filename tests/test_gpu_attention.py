@@ -174,3 +174,52 @@ def test_flash_attention_key_split_tail(pkg, orc, dev, S, H, KV, ar, ways):
                                          1024) == 0
     torch.cuda.synchronize()
     assert torch.equal(small.view(torch.int16), plain.view(torch.int16))
+
+
+def _eager_numpy(q, k, v, mask, scaling):
+    """softmax(q k^T * scaling + mask) v in fp64 with the probabilities rounded to bf16 (o1.c src/cuda/attn.cu:22-113);
+    q [H,S,D], k/v [KV,S,D] as float arrays; returns probs [H,S,S], out [S,H,D]."""
+    H, S, D = q.shape
+    g = H // k.shape[0]
+    probs = np.empty((H, S, S))
+    out = np.empty((S, H, D))
+    for h in range(H):
+        sc = (q[h].astype(np.float64) @ k[h // g].astype(np.float64).T) * scaling + mask
+        sc -= sc.max(axis=1, keepdims=True)
+        p = np.exp(sc)
+        p /= p.sum(axis=1, keepdims=True)
+        p = parity.bf16_to_f32_np(parity.f32_to_bf16_np(p.astype(np.float32))).astype(np.float64)
+        probs[h] = p
+        out[:, h] = p @ v[h // g].astype(np.float64)
+    return probs, out
+
+
+@pytest.mark.parametrize("H,KV,S,D", [(2, 1, 3, 4), (4, 2, 37, 72), (4, 4, 50, 128)])
+def test_attention_eager_general_path_fills_scores_and_probs(pkg, dev, H, KV, S, D):
+    """hd_attention_eager for what the flash kernel does not cover (another head_dim, or a mask that is not
+    prefix-causal): scores and probabilities are materialised as the reference does (src/cuda/attn.cu:129-174;
+    the analytic case of its tests/unit/test_primitives.c:484-533 has head_dim 4 and a one-key mask)."""
+    rng = np.random.default_rng(S)
+    qh, kh, vh = seeded_bf16((H, S, D), 1), seeded_bf16((KV, S, D), 2), seeded_bf16((KV, S, D), 3)
+    m = np.where(rng.random((S, S)) < 0.4, -3.3895e38, 0.0).astype(np.float32)
+    m[:, 0] = 0.0                                                   # every row keeps one visible key
+    mh = parity.f32_to_bf16_np(m)
+    qd, kd, vd, md = (u16_to_torch(a, dev) for a in (qh, kh, vh, mh))
+    scores = torch.zeros(H, S, S, dtype=torch.bfloat16, device=dev)
+    probs = torch.zeros(H, S, S, dtype=torch.bfloat16, device=dev)
+    out = torch.zeros(S, H, D, dtype=torch.bfloat16, device=dev)
+    pkg.lib.hd_attention_eager(pkg.ptr(qd), pkg.ptr(kd), pkg.ptr(vd), pkg.ptr(md), pkg.ptr(scores), pkg.ptr(probs),
+                               pkg.ptr(out), H, KV, S, D, D ** -0.5)
+    torch.cuda.synchronize()
+    pkg.check_cuda_errbuf("attention_eager")
+    f = parity.bf16_to_f32_np
+    want_p, want_o = _eager_numpy(f(qh), f(kh), f(vh), f(mh).astype(np.float64), D ** -0.5)
+    assert_close(probs.float().cpu().numpy(), want_p.astype(np.float32), "B", "probs")
+    assert_close(out.float().cpu().numpy(), want_o.astype(np.float32), "B", "out")
+    assert float(scores.float().abs().max()) > 0
+    # without the two buffers the general path cannot run: reported, nothing launched
+    pkg.lib.hd_cuda_clear_error()
+    pkg.lib.hd_attention_eager(pkg.ptr(qd), pkg.ptr(kd), pkg.ptr(vd), pkg.ptr(md), None, None, pkg.ptr(out), H, KV, S, D,
+                               D ** -0.5)
+    assert pkg.lib.hd_cuda_last_error() != b""
+    pkg.lib.hd_cuda_clear_error()

@@ -332,3 +332,76 @@ def test_cfg_step_replays_from_a_cuda_graph(pkg, dev):
     eng.denoise_step_cfg(ic, iu, posd, z2, 0.8, 0.7, 5.0, eager)
     torch.cuda.synchronize()
     assert torch.equal(out.view(torch.int16), eager.view(torch.int16))
+
+
+def test_decode_to_rgb_against_the_reference_decode(pkg, dev, golden):
+    """o1_decode_to_rgb byte for byte against hd_decode_to_rgb of o1.c src/runtime/decode.c:5-27: the committed
+    fixture (values beyond [-1, 1], negative zero), and the reference function itself on a larger latent."""
+    g = np.load(os.path.join(golden, "decode_ref.npz"))
+    gh, gw, p = (int(v) for v in g["geom"])
+
+    def run(z_bits, gh, gw):
+        rgb = torch.zeros(gh * p, gw * p, 3, dtype=torch.uint8, device=dev)
+        stats = torch.zeros(3, dtype=torch.int32, device=dev)
+        nb, mn, mx = C.c_int(), C.c_float(), C.c_float()
+        zd = u16_to_torch(z_bits, dev)
+        rc = pkg.lib.o1_decode_to_rgb(pkg.ptr(zd), gh, gw, p, 3, pkg.ptr(rgb), pkg.ptr(stats), C.byref(nb), C.byref(mn),
+                                      C.byref(mx))
+        assert rc == 0, pkg.last_error()
+        return rgb.cpu().numpy()
+
+    assert (run(np.ascontiguousarray(g["z"]), gh, gw) == g["rgb"]).all()
+    r = parity.reflib()
+    if r is not None and hasattr(r, "hd_decode_to_rgb"):
+        gh2, gw2 = 16, 24
+        z = seeded_bf16((gh2 * gw2, 3 * p * p), 78, 0.0, 0.8)
+        zf = np.ascontiguousarray(parity.bf16_to_f32_np(z))
+        want = np.zeros((gh2 * p, gw2 * p, 3), dtype=np.uint8)
+        r.hd_decode_to_rgb.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]
+        r.hd_decode_to_rgb.restype = None
+        r.hd_decode_to_rgb(zf.ctypes.data_as(C.c_void_p), gh2, gw2, p, 3, want.ctypes.data_as(C.c_void_p))
+        assert (run(z, gh2, gw2) == want).all()
+
+
+def test_loader_against_the_reference_loader_and_converter(pkg, dev, golden, tmp_path):
+    """The same pack through hd_weights_to_device_gguf of this library and of the reference's own loader
+    (o1.c src/model/weights.c:519-669 + src/io/gguf.c, inside the reference-built checker library): same tensor
+    names in the same order, same sizes, same offsets inside the arena, same device bytes.  Packs: one written by
+    the reference's converter (fixture) and one written by write_gguf."""
+    from test_abi_host import _small_pack
+    r = parity.reflib()
+    ours_path = str(tmp_path / "ours.gguf")
+    _small_pack(pkg, ours_path, n_layers=2, with_f32=False)
+    want = np.load(os.path.join(golden, "ref_convert_small.npz"))
+
+    def dev_bytes(ptr_, n):
+        return torch.as_tensor(pkg.model._DevBytes(ptr_, n), device=dev).cpu().numpy()
+
+    for path in (os.path.join(golden, "ref_convert_small.gguf"), ours_path):
+        mine = pkg.WeightStore()
+        assert pkg.lib.hd_weights_to_device_gguf(path.encode(), 0, C.byref(mine)) == 0, pkg.lib.hd_weights_last_error()
+        try:
+            if path.endswith("ref_convert_small.gguf"):
+                for i in range(mine.n_allocs):
+                    a = mine.allocs[i]
+                    bits = want[a.name.decode()]
+                    assert a.nbytes == bits.size * 2
+                    assert (dev_bytes(a.dev_ptr, a.nbytes).view(np.uint16) == bits.ravel()).all(), a.name
+            if r is None:
+                continue
+            theirs = pkg.WeightStore()
+            r.hd_weights_to_device_gguf.argtypes = [C.c_char_p, C.c_int, C.c_void_p]
+            r.hd_weights_last_error.restype = C.c_char_p
+            assert r.hd_weights_to_device_gguf(path.encode(), 0, C.byref(theirs)) == 0, r.hd_weights_last_error()
+            try:
+                assert theirs.n_allocs == mine.n_allocs and theirs.arena_bytes == mine.arena_bytes
+                for i in range(mine.n_allocs):
+                    a, b = mine.allocs[i], theirs.allocs[i]
+                    assert a.name == b.name and a.nbytes == b.nbytes
+                    assert a.dev_ptr - mine.arena_ptr == b.dev_ptr - theirs.arena_ptr
+                assert (dev_bytes(mine.arena_ptr, mine.arena_bytes) == dev_bytes(theirs.arena_ptr, theirs.arena_bytes)).all()
+            finally:
+                r.hd_weight_store_free.argtypes = [C.c_void_p]
+                r.hd_weight_store_free(C.byref(theirs))
+        finally:
+            pkg.lib.hd_weight_store_free(C.byref(mine))

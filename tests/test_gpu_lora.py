@@ -81,3 +81,22 @@ def test_lora_sequential_adapters_and_errors(pkg, orc, dev):
     check_merged(torch_to_u16(wd), ref, w0, 5e-4)
     bad = (pkg.LoraEntry * 1)(entry(pkg, wd, keep[0], keep[2], 0, K, N, 4.0, 1.0))
     assert pkg.lib.hd_lora_merge_gpu(bad, 1, None) == 5          # HD_ERR_MISMATCH
+
+
+def test_lora_merge_against_the_reference_python_contract(pkg, dev, golden):
+    """hd_lora_merge_gpu against weights merged by the reference's own Python (merge_linear of o1.c
+    tools/lora/tests/test_lora_formula.py:20 + the bf16 rounding of tools/lora/merge_gguf.py:44-49,164-171);
+    fixture tests/golden/lora_ref.npz, including a multiplier != 1 and a negative one."""
+    import os
+    g = np.load(os.path.join(golden, "lora_ref.npz"))
+    for i in range(int(g["n_cases"])):
+        N, K, R, alpha, mult = g[f"c{i}_meta"]
+        N, K, R = int(N), int(K), int(R)
+        w0 = np.ascontiguousarray(g[f"c{i}_w"])
+        wd = u16_to_torch(w0, dev)
+        upd = torch.from_numpy(np.ascontiguousarray(g[f"c{i}_up"])).to(dev)
+        dnd = torch.from_numpy(np.ascontiguousarray(g[f"c{i}_down"])).to(dev)
+        ents = (pkg.LoraEntry * 1)(entry(pkg, wd, upd, dnd, R, K, N, float(alpha), float(mult)))
+        assert pkg.lib.hd_lora_merge_gpu(ents, 1, None) == 0, pkg.last_error()
+        torch.cuda.synchronize()
+        check_merged(torch_to_u16(wd), g[f"c{i}_merged"], w0, max_frac=1e-3)

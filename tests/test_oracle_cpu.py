@@ -376,3 +376,91 @@ def test_adaln_block_variant_reduces_to_the_plain_block(pkg, orc):
     f = parity.bf16_to_f32_np
     want_ln = f(pints["ln0"]) * (1.0 + f(mod6[H:2 * H])) + f(mod6[:H])
     assert (ints["ln0"] == parity.f32_to_bf16_np(want_ln.astype(np.float32))).all()
+
+
+def _merged_close(got, ref, w0, max_frac):
+    """Bit-identical except on rounding ties of the FP32 sum (neighbouring bf16 values, a vanishing fraction)."""
+    g, r_, w = (parity.bf16_to_f32_np(a).astype(np.float64) for a in (got, ref, w0))
+    neq = got != ref
+    assert neq.mean() <= max_frac, f"{neq.mean():.2e} of the merged weights differ"
+    assert (np.abs(g - r_) <= np.maximum(np.abs(w), np.abs(r_)) * 2.0 ** -7 + 1e-30).all()
+
+
+def test_lora_oracle_against_the_reference_python_contract(orc, golden):
+    """orc_lora_merge against weights merged by the reference's own Python (merge_linear of
+    tools/lora/tests/test_lora_formula.py + the bf16 rounding of tools/lora/merge_gguf.py), fixture lora_ref.npz."""
+    g = np.load(os.path.join(golden, "lora_ref.npz"))
+    for i in range(int(g["n_cases"])):
+        N, K, R, alpha, mult = g[f"c{i}_meta"]
+        N, K, R = int(N), int(K), int(R)
+        w = g[f"c{i}_w"].copy()
+        up, down = np.ascontiguousarray(g[f"c{i}_up"]), np.ascontiguousarray(g[f"c{i}_down"])   # kept alive across the call
+        orc.orc_lora_merge(np_ptr(w), np_ptr(up), np_ptr(down), N, K, R,
+                           float(np.float32(mult) * np.float32(alpha) / np.float32(R)))
+        assert (w != g[f"c{i}_w"]).mean() > 0.05
+        _merged_close(w, g[f"c{i}_merged"], g[f"c{i}_w"], 1e-3)
+
+
+def test_pack_written_by_the_reference_converter_is_parsed(pkg, golden):
+    """Header of a pack the reference's own tools/hidream_convert.py wrote (fixture ref_convert_small.gguf):
+    names in its production order, element counts, BF16 type, payload bytes at the offsets the header gives."""
+    path = os.path.join(golden, "ref_convert_small.gguf")
+    want = np.load(os.path.join(golden, "ref_convert_small.npz"))
+    n = pkg.lib.o1_gguf_probe(path.encode(), -1, None, 0, None, None, None)
+    assert n == len(want.files) == 33
+    raw = open(path, "rb").read()
+    seen = []
+    for i in range(n):
+        buf = C.create_string_buffer(256)
+        numel, typ, off = C.c_int64(), C.c_int(), C.c_int64()
+        assert pkg.lib.o1_gguf_probe(path.encode(), i, buf, 256, C.byref(numel), C.byref(typ), C.byref(off)) == n
+        name = buf.value.decode()
+        seen.append(name)
+        bits = want[name]
+        assert numel.value == bits.size and typ.value == 30 and off.value % 256 == 0
+        assert raw[off.value:off.value + bits.size * 2] == bits.tobytes(), name
+    assert seen[0] == "model.language_model.embed_tokens.weight" and set(seen) == set(want.files)
+
+
+def test_pack_written_here_is_read_by_the_reference_reader(pkg, tmp_path):
+    """write_gguf's output through the reference's own hd_gguf_open (src/io/gguf.c:212-305, inside the
+    reference-built checker library): same tensor table, alignment, payload offsets and metadata."""
+    r = parity.reflib()
+    if r is None:
+        pytest.skip("oracle/_ref/libo1ref.so not built")
+    from test_abi_host import _small_pack
+
+    class GgufTensor(C.Structure):        # hd_gguf_tensor, src/io/gguf.h
+        _fields_ = [("name", C.c_char_p), ("n_dims", C.c_uint32), ("dims", C.c_uint64 * 8), ("type", C.c_uint32),
+                    ("offset", C.c_uint64), ("nbytes", C.c_uint64)]
+
+    class GgufFile(C.Structure):          # hd_gguf_file
+        _fields_ = [("path", C.c_char_p), ("n_tensors", C.c_int64), ("tensors", C.POINTER(GgufTensor)),
+                    ("alignment", C.c_uint64), ("tensor_data_off", C.c_uint64), ("payload_bytes", C.c_uint64),
+                    ("arch", C.c_char_p), ("name", C.c_char_p), ("profile", C.c_char_p), ("variant", C.c_char_p),
+                    ("revision", C.c_char_p), ("dtype", C.c_char_p), ("quantization", C.c_char_p),
+                    ("num_layers", C.c_int64), ("layout_version", C.c_int64)]
+
+    path = str(tmp_path / "pack.gguf")
+    tensors = _small_pack(pkg, path, n_layers=2, with_f32=False)
+    f = GgufFile()
+    r.hd_gguf_open.argtypes = [C.c_char_p, C.POINTER(GgufFile)]
+    r.hd_gguf_last_error.restype = C.c_char_p
+    assert r.hd_gguf_open(path.encode(), C.byref(f)) == 0, r.hd_gguf_last_error()
+    try:
+        assert f.n_tensors == len(tensors) and f.alignment == 256 and f.arch == b"hidream_o1" and f.profile == b"dev"
+        raw = open(path, "rb").read()
+        for i, (name, a) in enumerate(tensors):
+            t = f.tensors[i]
+            assert t.name.decode() == name and t.type == 30 and t.nbytes == a.nbytes
+            assert list(t.dims[:t.n_dims]) == list(a.shape)
+            numel, typ, off = C.c_int64(), C.c_int(), C.c_int64()
+            pkg.lib.o1_gguf_probe(path.encode(), i, None, 0, C.byref(numel), C.byref(typ), C.byref(off))
+            assert off.value == f.tensor_data_off + t.offset and numel.value == a.size
+            dst = np.empty(a.size, dtype=np.uint16)
+            r.hd_gguf_read_tensor.argtypes = [C.POINTER(GgufFile), C.POINTER(GgufTensor), C.c_void_p]
+            assert r.hd_gguf_read_tensor(C.byref(f), C.byref(t), dst.ctypes.data_as(C.c_void_p)) == 0
+            assert (dst == a.ravel()).all() and raw[off.value:off.value + a.nbytes] == a.tobytes()
+    finally:
+        r.hd_gguf_close.argtypes = [C.POINTER(GgufFile)]
+        r.hd_gguf_close(C.byref(f))
