@@ -371,7 +371,8 @@ def run_ours(args):
             # the sharded forward against the unsharded one on the same inputs, every rank on its own rows
             parity_rec = sharded_vs_unsharded(pkg, dist, dev, eng, w, T, I, ar, posd, ids_u if branch else ids_c,
                                               z_initial, xp_local, world)
-        elif world == 1 and args.workload in ("c1", "c2"):
+        elif rank == 0 and args.workload in ("c1", "c2"):
+            # one GPU, or a CFG pair (each rank runs the unsharded forward of one branch): the same kernels
             parity_rec = reference_probe(T, gh, gw, local)
     extras = None
     if world == 1 and args.workload == "c2" and not args.short and not args.no_extras and layers == 36:

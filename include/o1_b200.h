@@ -471,6 +471,12 @@ int64_t o1_launch_count(int reset);
  * anything else runs a SIMT kernel (epilogues 0 and 1 only).  Returns 0 on success. */
 int o1_gemm(const void *x, int ldx, const void *w, const void *w2, void *y, int ldy, int M, int N,
             int K, int epi, const void *bias, const void *resid, int ldr, float scale, int force_bn);
+/* The q, k and v projections of a decoder block (src/model/block.c:257-265) with the per-head RMSNorm + rotary of
+ * q and k (:266-289) as ONE launch over the three weight tensors: y [M, qc | kc | kc] (row pitch ldy) =
+ * norm_rope(x wq^T) | norm_rope(x wk^T) | x wv^T.  q_norm / k_norm [128] bf16, cs [M,128] fp32 (o1_mrope_table),
+ * qc and kc multiples of 128, M >= 8.  Bit-identical to three o1_gemm calls (epilogues 6, 6, 0). */
+int o1_gemm_qkv(const void *x, int ldx, const void *wq, const void *wk, const void *wv, void *y, int ldy, int M,
+                int qc, int kc, int K, const void *q_norm, const void *k_norm, const float *cs, float eps);
 /* Prefix-causal flash attention on seq-major operands: q [S, ldq], k [S, ldk],
  * v [S, ldv], out [S, ldo]; head h at columns [128h, 128h+128). */
 int o1_flash_attention(const void *q, int ldq, const void *k, int ldk, const void *v, int ldv,

@@ -247,6 +247,7 @@ lib.o1_profile_summary.argtypes = [c_int, C.POINTER(C.c_double), C.POINTER(c_int
 _sig("o1_launch_count", c_int64, c_int)
 _sig("o1_gemm", c_int, _P, c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P, _P, c_int,
      c_float, c_int)
+_sig("o1_gemm_qkv", c_int, _P, c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, c_float)
 _sig("o1_flash_attention", c_int, _P, c_int, _P, c_int, _P, c_int, _P, c_int, c_int, c_int, c_int,
      c_int, c_float)
 _sig("o1_attention_tail_ways", None, c_int)

@@ -524,12 +524,9 @@ static hd_status block_forward(const void* in, const float* cs, int ar_len, cons
     // (block.c:266-289) run inside the projections' epilogues where the tensor-core tiles cover the shape,
     // otherwise as one in-place kernel per tensor (no head split either way)
     if (gemm_tc_supported(S, qc, hidden, EPI_QKNORM) && gemm_tc_supported(S, kc, hidden, EPI_QKNORM)) {
-        BLK_TRY(gemm_bf16_ld(b.ln, hidden, bw->q_proj, nullptr, b.qkv, ld, S, qc, hidden, EPI_QKNORM,
-                             bw->q_norm, cs, 0, eps, 0, st), "q_proj+norm+rope");
-        BLK_TRY(gemm_bf16_ld(b.ln, hidden, bw->k_proj, nullptr, b.qkv + qc, ld, S, kc, hidden, EPI_QKNORM,
-                             bw->k_norm, cs, 0, eps, 0, st), "k_proj+norm+rope");
-        BLK_TRY(gemm_bf16_ld(b.ln, hidden, bw->v_proj, nullptr, b.qkv + qc + kc, ld, S, kc, hidden,
-                             EPI_STORE, nullptr, nullptr, 0, 0.f, 0, st), "v_proj");
+        // one launch over the three weight tensors (three launches each end in a partly filled wave of tiles)
+        BLK_TRY(gemm_qkv(b.ln, hidden, bw->q_proj, bw->k_proj, bw->v_proj, b.qkv, ld, S, qc, kc, hidden, bw->q_norm,
+                         bw->k_norm, cs, eps, 0, nullptr, nullptr, nullptr, st), "qkv_proj+norm+rope");
     } else {
         BLK_TRY(gemm_bf16_ld(b.ln, hidden, bw->q_proj, nullptr, b.qkv, ld, S, qc, hidden, EPI_STORE,
                              nullptr, nullptr, 0, 0.f, 0, st), "q_proj");
@@ -873,6 +870,13 @@ hd_status hd_forward(const hd_forward_binding* bw, hd_forward_workspace* ws, con
 int o1_gemm(const void* x, int ldx, const void* w, const void* w2, void* y, int ldy, int M, int N, int K,
             int epi, const void* bias, const void* resid, int ldr, float scale, int force_bn) {
     if (!gemm_bf16_ld(x, ldx, w, w2, y, ldy, M, N, K, epi, bias, resid, ldr, scale, force_bn, g_stream))
+        return 1;
+    count();
+    return 0;
+}
+int o1_gemm_qkv(const void* x, int ldx, const void* wq, const void* wk, const void* wv, void* y, int ldy, int M, int qc,
+                int kc, int K, const void* q_norm, const void* k_norm, const float* cs, float eps) {
+    if (!gemm_qkv(x, ldx, wq, wk, wv, y, ldy, M, qc, kc, K, q_norm, k_norm, cs, eps, 0, nullptr, nullptr, nullptr, g_stream))
         return 1;
     count();
     return 0;

@@ -51,6 +51,14 @@ struct GemmArgs {
     // Input K blocks: K columns [b*a_kblk, (b+1)*a_kblk) of row r live at x[(b*a_rows + r) * ldx + ...]
     // (a_kblk == 0: plain).  Lets a projection read the slabs an all-to-all received, one per source.
     int a_kblk, a_rows;
+    // EPI_QKV: the output columns are three segments [q | k | v] with a weight tensor each (tensor maps B, B2, B3);
+    // q and k tiles take the per-head norm + rotary epilogue (norm weights seg_norm[0], [1]), v tiles are stored as
+    // they are.  seg_n = columns of q and of k (= v).  With output tables, segment s uses o_tab[8*s ...] and its own
+    // block width seg_cb[s].
+    int seg_n[2];
+    const uint16_t* seg_norm[2];
+    int seg_cb[3];
+    uint16_t* seg_tab[16];    // tables of segments 1 and 2 (segment 0 uses o_tab)
     int* err;
 };
 
@@ -110,7 +118,7 @@ __device__ __forceinline__ void load32_bf16(const uint16_t* src, float (&v)[32])
 template <int EPI, int BN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-               const __grid_constant__ CUtensorMap tmB2, const GemmArgs g) {
+               const __grid_constant__ CUtensorMap tmB2, const __grid_constant__ CUtensorMap tmB3, const GemmArgs g) {
     using Cfg = GemmCfg<BN>;
     constexpr int STAGES = Cfg::STAGES;
     extern __shared__ uint8_t smem_raw[];
@@ -160,7 +168,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (lane == 0) {
             tma_prefetch_desc(&tmA);
             tma_prefetch_desc(&tmB);
-            if (EPI == EPI_SWIGLU) tma_prefetch_desc(&tmB2);
+            if (EPI == EPI_SWIGLU || EPI == EPI_QKV) tma_prefetch_desc(&tmB2);
+            if (EPI == EPI_QKV) tma_prefetch_desc(&tmB3);
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
@@ -183,6 +192,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         // 128 gate rows then 128 up rows of the same output columns
                         tma_load_2d(b_s, &tmB, &full[stage], kb * BK, nb * 128);
                         tma_load_2d(b_s + 128 * BK * 2, &tmB2, &full[stage], kb * BK, nb * 128);
+                    } else if (EPI == EPI_QKV) {
+                        // the weight tensor of the segment this column tile lies in, at the segment's own row
+                        const int col0 = nb * BN;
+                        const int seg = col0 >= g.seg_n[0] + g.seg_n[1] ? 2 : (col0 >= g.seg_n[0] ? 1 : 0);
+                        const int lrow = col0 - (seg == 2 ? g.seg_n[0] + g.seg_n[1] : (seg == 1 ? g.seg_n[0] : 0));
+                        const CUtensorMap* mB = seg == 0 ? &tmB : (seg == 1 ? &tmB2 : &tmB3);
+#pragma unroll
+                        for (int h = 0; h < BN / 128; ++h)
+                            tma_load_2d(b_s + h * 128 * BK * 2, mB, &full[stage], kb * BK, lrow + h * 128);
                     } else {
 #pragma unroll
                         for (int h = 0; h < BN / 128; ++h)
@@ -235,6 +253,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const int row = mb * BM + q * 32 + lane;
             const bool row_ok = row < g.M;
             const uint32_t t_row = tmem_base + as * BN + ((uint32_t)(q * 32) << 16);
+            // EPI_QKV: which segment this column tile lies in decides the epilogue (warp-uniform); everything
+            // below addresses the output through (seg_col0 + column inside the segment) or the segment's tables
+            int seg = 0, seg_col0 = 0, lcol0 = nb * BN, cb = g.o_cb;
+            uint16_t* const* tab = g.o_tab;
+            const uint16_t* norm_w = g.bias;
+            if (EPI == EPI_QKV) {
+                seg = lcol0 >= g.seg_n[0] + g.seg_n[1] ? 2 : (lcol0 >= g.seg_n[0] ? 1 : 0);
+                seg_col0 = seg == 2 ? g.seg_n[0] + g.seg_n[1] : (seg == 1 ? g.seg_n[0] : 0);
+                lcol0 -= seg_col0;
+                cb = g.seg_cb[seg];
+                if (seg > 0) tab = g.seg_tab + (seg - 1) * 8;
+                norm_w = g.seg_norm[seg == 1 ? 1 : 0];
+            }
+            const int epi_eff = (EPI == EPI_QKV) ? (seg < 2 ? (int)EPI_QKNORM : (int)EPI_STORE) : EPI;
             if (EPI == EPI_SWIGLU) {
 #pragma unroll 1
                 for (int c = 0; c < 4; ++c) {
@@ -254,7 +286,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         store32_bf16(g.out + (size_t)row * g.ldo + nb * 128 + c * 32, v);
                     }
                 }
-            } else if (EPI == EPI_STORE && g.o_tab_n) {
+            } else if (epi_eff == EPI_STORE && g.o_tab_n) {
                 // Blocks of the output live in other GPUs' memory.  One thread per row would put 16-byte
                 // pieces of 32 different rows into every store instruction; over NVLink each piece is a
                 // packet of its own.  So 64 columns at a time go through a swizzled shared-memory slice of
@@ -277,8 +309,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         *reinterpret_cast<uint4*>(stg + lane * 128 + ((j ^ (lane & 7)) * 16)) = o;
                     }
                     __syncwarp();
-                    const int col = nb * BN + c2 * 64;      // a 64-column group never straddles a block (o_cb % 128 == 0)
-                    uint16_t* obase = g.o_tab[col / g.o_cb] + (col % g.o_cb);
+                    const int col = lcol0 + c2 * 64;        // a 64-column group never straddles a block (cb % 128 == 0)
+                    uint16_t* obase = tab[col / cb] + (col % cb);
                     const int ch = lane & 7;
 #pragma unroll
                     for (int k = 0; k < 8; ++k) {
@@ -289,7 +321,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     }
                     __syncwarp();
                 }
-            } else if (EPI == EPI_QKNORM) {
+            } else if (epi_eff == EPI_QKNORM) {
                 // Per-head RMSNorm + rotary on the projection's output row (o1.c src/model/block.c:266-289 runs
                 // head split, hd_rmsnorm, hd_apply_rotary as separate passes).  This thread owns the whole row of
                 // the tile, i.e. BN/128 complete heads: the 128 values of a head are rounded to bf16 (the
@@ -321,15 +353,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         const float sq = __fadd_rn(__fadd_rn(__fadd_rn(part[0], part[1]), __fadd_rn(part[2], part[3])),
                                                    __fadd_rn(__fadd_rn(part[4], part[5]), __fadd_rn(part[6], part[7])));
                         const float inv = rsqrtf(sq / 128.0f + g.scale);
-                        const int col = nb * BN + hb * 128;
+                        const int col = seg_col0 + lcol0 + hb * 128;
                         const size_t ocol = g.o_cb ? (size_t)(col / g.o_cb) * g.o_cb_stride + (col % g.o_cb) : (size_t)col;
                         uint16_t* orow = g.o_tab_n ? nullptr : g.out + (size_t)row * g.ldo + ocol;
                         uint8_t* stg_row = store_stage + q * (2 * 32 * 128) + lane * 128;
                         const float* cs = g.rope + (size_t)row * 128;
 #pragma unroll
                         for (int t = 0; t < 8; ++t) {
-                            const uint4 wl4 = *reinterpret_cast<const uint4*>(g.bias + 8 * t);
-                            const uint4 wh4 = *reinterpret_cast<const uint4*>(g.bias + 64 + 8 * t);
+                            const uint4 wl4 = *reinterpret_cast<const uint4*>(norm_w + 8 * t);
+                            const uint4 wh4 = *reinterpret_cast<const uint4*>(norm_w + 64 + 8 * t);
                             const float wl[8] = {bf16lo(wl4.x), bf16hi(wl4.x), bf16lo(wl4.y), bf16hi(wl4.y),
                                                  bf16lo(wl4.z), bf16hi(wl4.z), bf16lo(wl4.w), bf16hi(wl4.w)};
                             const float wh[8] = {bf16lo(wh4.x), bf16hi(wh4.x), bf16lo(wh4.y), bf16hi(wh4.y),
@@ -371,8 +403,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         // leave as full 128-byte row segments, 4 rows per store instruction (a head never straddles
                         // a destination block: o_cb % 128 == 0)
                         __syncwarp();
-                        const int col = nb * BN + hb * 128;
-                        uint16_t* obase = g.o_tab[col / g.o_cb] + (col % g.o_cb);
+                        const int col = lcol0 + hb * 128;
+                        uint16_t* obase = tab[col / cb] + (col % cb);
                         const uint8_t* stg = store_stage + q * (2 * 32 * 128);
                         const int ch = lane & 7;
 #pragma unroll
@@ -625,7 +657,7 @@ bool func_attr_once(std::atomic<uint64_t>& done, const void* func, int smem_byte
 
 template <int EPI, int BN>
 static bool launch_tc(const CUtensorMap* tA, const CUtensorMap* tB, const CUtensorMap* tB2,
-                      GemmArgs& g, cudaStream_t st) {
+                      GemmArgs& g, cudaStream_t st, const CUtensorMap* tB3 = nullptr) {
     using Cfg = GemmCfg<BN>;
     static std::atomic<uint64_t> attr_done{0};
     auto kern = gemm_tc_kernel<EPI, BN>;
@@ -633,8 +665,8 @@ static bool launch_tc(const CUtensorMap* tA, const CUtensorMap* tB, const CUtens
     const int tiles = g.num_m * g.num_n;
     int grid = sm_count();
     if (grid > tiles) grid = tiles;
-    prof_before(EPI == EPI_QKNORM ? (int)EPI_STORE : (EPI == EPI_BIAS_GELU ? (int)EPI_BIAS : ((EPI == EPI_BIAS_RESID || EPI == EPI_GATE_RESID) ? (int)EPI_RESID : EPI)), 2.0 * g.M * (double)g.N * g.K * (EPI == EPI_SWIGLU ? 2.0 : 1.0), st);
-    kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, st>>>(*tA, *tB, *tB2, g);
+    prof_before((EPI == EPI_QKNORM || EPI == EPI_QKV) ? (int)EPI_STORE : (EPI == EPI_BIAS_GELU ? (int)EPI_BIAS : ((EPI == EPI_BIAS_RESID || EPI == EPI_GATE_RESID) ? (int)EPI_RESID : EPI)), 2.0 * g.M * (double)g.N * g.K * (EPI == EPI_SWIGLU ? 2.0 : 1.0), st);
+    kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, st>>>(*tA, *tB, *tB2, tB3 ? *tB3 : *tB2, g);
     prof_after(st);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) { set_error("gemm: launch: %s", cudaGetErrorString(e)); return false; }
@@ -738,6 +770,10 @@ bool gemm_bf16_ex(const void* x, int ldx, const void* w, const void* w2, void* y
         }
     }
     g.a_kblk = a_kblk; g.a_rows = a_rows;
+    g.seg_n[0] = g.seg_n[1] = 0;
+    g.seg_norm[0] = g.seg_norm[1] = nullptr;
+    g.seg_cb[0] = g.seg_cb[1] = g.seg_cb[2] = 0;
+    for (int i = 0; i < 16; ++i) g.seg_tab[i] = nullptr;
 
     CUtensorMap mA, mB, mB2;
     if (!(a_kblk ? cached_tmap(&mA, x, (uint64_t)(K / a_kblk) * a_rows, a_kblk, ldx, 128)
@@ -792,6 +828,68 @@ bool gemm_bf16_ex(const void* x, int ldx, const void* w, const void* w2, void* y
     }
     set_error("gemm: unknown epilogue %d", epi);
     return false;
+}
+
+// q | k | v projections of one activation matrix as ONE launch: y[M, qc | kc | kc] (row pitch ldy) = x wq^T | x wk^T |
+// x wv^T, the per-head RMSNorm + rotary applied to the q and k columns in the epilogue (norm weights q_norm / k_norm
+// [128], cos|sin table cs [M,128] fp32).  Three launches of 14.05 + 3.5 + 3.5 waves of tiles (at 16640 rows) become
+// one of 21.1; in the sharded forward the gain is larger (fewer rows per rank, the same three partial last waves).
+// tq / tk / tv (all or none): per destination rank the base of that rank's q / k / v columns (block widths
+// qc/P, kc/P, kc/P); rows then go to the tables instead of y.
+bool gemm_qkv(const void* x, int ldx, const void* wq, const void* wk, const void* wv, void* y, int ldy, int M, int qc,
+              int kc, int K, const void* q_norm, const void* k_norm, const float* cs, float eps, int n_dst,
+              void* const* tq, void* const* tk, void* const* tv, cudaStream_t st) {
+    const int N = qc + 2 * kc;
+    const bool tabs = n_dst > 0;
+    if (!x || !wq || !wk || !wv || (!y && !tabs) || !q_norm || !k_norm || !cs || M < 8 || (K % 8) != 0 || (qc % 128) != 0 ||
+        (kc % 128) != 0 || qc <= 0 || kc <= 0 || ((((uintptr_t)q_norm) | ((uintptr_t)k_norm) | ((uintptr_t)cs)) & 15)) {
+        set_error("gemm_qkv: bad args");
+        return false;
+    }
+    if (tabs && (n_dst > 8 || !tq || !tk || !tv || (qc % n_dst) != 0 || (kc % n_dst) != 0 || ((qc / n_dst) % 128) != 0 ||
+                 ((kc / n_dst) % 128) != 0)) {
+        set_error("gemm_qkv: bad destination tables");
+        return false;
+    }
+    GemmArgs g;
+    g.M = M; g.N = N; g.K = K;
+    g.out = (uint16_t*)y; g.ldo = ldy;
+    g.bias = (const uint16_t*)q_norm;
+    g.resid = nullptr; g.ldr = 0;
+    g.rope = cs;
+    g.scale = eps;
+    g.err = device_error_word();
+    g.num_m = (M + BM - 1) / BM;
+    {
+        long gm = (48l << 20) / ((long)BM * K * 2);
+        g.group_m = (int)(gm < 4 ? 4 : (gm > 32 ? 32 : gm));
+    }
+    g.o_cb = 0; g.o_cb_stride = 0;
+    g.o_tab_n = tabs ? n_dst : 0;
+    g.a_kblk = 0; g.a_rows = 0;
+    g.seg_n[0] = qc; g.seg_n[1] = kc;
+    g.seg_norm[0] = (const uint16_t*)q_norm; g.seg_norm[1] = (const uint16_t*)k_norm;
+    g.seg_cb[0] = tabs ? qc / n_dst : 0; g.seg_cb[1] = g.seg_cb[2] = tabs ? kc / n_dst : 0;
+    for (int i = 0; i < 8; ++i) g.o_tab[i] = nullptr;
+    for (int i = 0; i < 16; ++i) g.seg_tab[i] = nullptr;
+    for (int i = 0; i < (tabs ? n_dst : 0); ++i) {
+        if (!tq[i] || !tk[i] || !tv[i] || ((((uintptr_t)tq[i]) | ((uintptr_t)tk[i]) | ((uintptr_t)tv[i])) & 15)) {
+            set_error("gemm_qkv: destination table entry %d unusable", i);
+            return false;
+        }
+        g.o_tab[i] = (uint16_t*)tq[i]; g.seg_tab[i] = (uint16_t*)tk[i]; g.seg_tab[8 + i] = (uint16_t*)tv[i];
+    }
+    CUtensorMap mA, mQ, mK, mV;
+    if (!cached_tmap(&mA, x, M, K, ldx, 128) || !cached_tmap(&mQ, wq, qc, K, K, 128) ||
+        !cached_tmap(&mK, wk, kc, K, K, 128) || !cached_tmap(&mV, wv, kc, K, K, 128))
+        return false;
+    // 256-wide tiles need every segment (and every destination block) to be a multiple of 256 columns
+    bool wide = (qc % 256) == 0 && (kc % 256) == 0;
+    if (tabs && (((qc / n_dst) % 256) != 0 || ((kc / n_dst) % 256) != 0)) wide = false;
+    if (wide && g.num_m * (N / 256) < 2 * sm_count()) wide = false;
+    const int bn = wide ? 256 : 128;
+    g.num_n = N / bn;
+    return wide ? launch_tc<EPI_QKV, 256>(&mA, &mQ, &mK, g, st, &mV) : launch_tc<EPI_QKV, 128>(&mA, &mQ, &mK, g, st, &mV);
 }
 
 }  // namespace o1

@@ -15,8 +15,9 @@ namespace o1 {
 // EPI_BIAS_GELU: bf16(gelu(bf16(bf16(acc) + bias))), tanh form when `scale` == 0, erf form otherwise (vision tower)
 // EPI_BIAS_RESID: bf16(resid + bf16(bf16(acc) + bias)): a biased projection followed by the residual add
 // EPI_GATE_RESID: bf16(resid + bf16(gate[col] * bf16(acc))), the gate vector passed as `bias` (adaLN block variant)
+// EPI_QKV: q | k | v projections in one launch (gemm_qkv): EPI_QKNORM on the q and k column tiles, EPI_STORE on the v tiles
 enum Epi { EPI_STORE = 0, EPI_BIAS = 1, EPI_RESID = 2, EPI_SWIGLU = 3, EPI_LORA = 4, EPI_QKNORM = 6, EPI_BIAS_GELU = 7,
-           EPI_BIAS_RESID = 8, EPI_GATE_RESID = 9 };
+           EPI_BIAS_RESID = 8, EPI_GATE_RESID = 9, EPI_QKV = 10 };
 
 // ---- engine.cu: optional per-launch event timing of the tensor-core kernels.
 // kind: 0..4 = GEMM by epilogue (Epi), 5 = flash attention.  Costs two event
@@ -40,6 +41,10 @@ bool gemm_bf16_ex(const void* x, int ldx, const void* w, const void* w2, void* y
                   int K, int epi, const void* bias, const void* resid, int ldr, float scale, int force_bn,
                   int o_cb, long o_cb_stride, int a_kblk, int a_rows, cudaStream_t st, void* const* o_tab = nullptr);
 bool gemm_tc_supported(int M, int N, int K, int epi);
+// q | k | v projections + per-head norm + rotary of q and k as one launch; see gemm_tc.cu
+bool gemm_qkv(const void* x, int ldx, const void* wq, const void* wk, const void* wv, void* y, int ldy, int M, int qc,
+              int kc, int K, const void* q_norm, const void* k_norm, const float* cs, float eps, int n_dst,
+              void* const* tq, void* const* tk, void* const* tv, cudaStream_t st);
 // copies the (cached) tensor map of a row-major bf16 matrix into *out; false + error text on failure
 bool cached_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
                  uint32_t box_rows);

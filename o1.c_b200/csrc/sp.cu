@@ -128,12 +128,8 @@ hd_status o1_sp_block_pre_direct(const hd_block_binding* bw, const o1_sp_ws* w, 
         tq[p] = base; tk[p] = base + qcp; tv[p] = base + qcp + kcp;
     }
     SP_TRY(rmsnorm(in, bw->input_ln, w->ln, R, H, 1e-6f, st), "input_norm");
-    SP_TRY(gemm_bf16_ex(w->ln, H, bw->q_proj, nullptr, nullptr, C, R, qc, H, EPI_QKNORM, bw->q_norm, w->rope, 0, 1e-6f, 0,
-                        qcp, 0, 0, 0, st, tq), "q_proj+norm+rope");
-    SP_TRY(gemm_bf16_ex(w->ln, H, bw->k_proj, nullptr, nullptr, C, R, kc, H, EPI_QKNORM, bw->k_norm, w->rope, 0, 1e-6f, 0,
-                        kcp, 0, 0, 0, st, tk), "k_proj+norm+rope");
-    SP_TRY(gemm_bf16_ex(w->ln, H, bw->v_proj, nullptr, nullptr, C, R, kc, H, EPI_STORE, nullptr, nullptr, 0, 0.f, 0,
-                        kcp, 0, 0, 0, st, tv), "v_proj");
+    SP_TRY(gemm_qkv(w->ln, H, bw->q_proj, bw->k_proj, bw->v_proj, nullptr, C, R, qc, kc, H, bw->q_norm, bw->k_norm, w->rope,
+                    1e-6f, P, tq, tk, tv, st), "qkv_proj+norm+rope");
     return HD_OK;
 }
 

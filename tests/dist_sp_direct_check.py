@@ -6,7 +6,10 @@
 Every rank runs the same sharded forward twice, once with NCCL all-to-all exchanges and once with the
 direct form; rank 0 also runs the unsharded forward.  Prints one JSON line; exit code 0 only if the direct
 form equals the staged form bit for bit and the sharded forward matches the unsharded one (bit for bit with
-attention's key split off, class D with the default policy)."""
+attention's key split off, class D with the default policy).  Also checked: the forward driven by ONE library
+call (o1_sp_forward) equals the stage-by-stage loop bit for bit; with --cfg (even world size) one CFG step of the
+(CFG pair) x (SP group) layout through o1_denoise_step_cfg_sp against the single-GPU o1_denoise_step_cfg; with
+--gguf a pack read by rank 0 only and broadcast to the others (load + broadcast seconds are reported)."""
 import argparse
 import json
 import os
@@ -20,12 +23,111 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 from __graft_entry__ import load_package  # noqa: E402
 
 
+def cfg_step_check(pkg, sp, w, T, grid, idsd, posd, vin, dev, rank, world):
+    """One CFG step on the (CFG pair) x (SP group) layout through o1_denoise_step_cfg_sp (C loop, predictions
+    exchanged by peer copies + a two-rank flag barrier) against o1_denoise_step_cfg on one GPU, same inputs.
+    Attention's key split is switched off on both sides, so the arithmetic is identical: z' must agree bit for bit."""
+    import ctypes as C
+    I = grid * grid
+    lay, sp_size = sp.layout(world, cfg=True)
+    _, branch, sp_rank = lay[rank]
+    groups = {}
+    for key in sorted({(v[0], v[2]) for v in lay.values()}):
+        members = sorted(r for r, v in lay.items() if (v[0], v[2]) == key)
+        g = dist.new_group(members)
+        if rank in members:
+            groups["cfg"] = g
+    for key in sorted({(v[0], v[1]) for v in lay.values()}):
+        members = sorted(r for r, v in lay.items() if (v[0], v[1]) == key)
+        g = dist.new_group(members)
+        if rank in members:
+            groups["sp"] = g
+    rng = np.random.default_rng(2)
+    ids_u = rng.integers(0, 151000, size=T).astype(np.int64)
+    ids_u[-1] = pkg.TMS_ID
+    ids_ud = torch.from_numpy(ids_u).to(dev)
+    pkg.lib.o1_attention_tail_ways(1)
+    eng = sp.EngineSP(w, T, I, sp_size, sp_rank, direct=True)
+    assert sp.connect_direct(eng, groups["sp"]), "peer mapping failed"
+    link = sp.CfgPairLink(eng, branch, groups["cfg"])
+    assert link.ok, "pair mapping failed"
+    z = (vin.float() * 8.0).to(torch.bfloat16)
+    zl = z[eng.i0:eng.i1].contiguous()
+    zn = torch.empty_like(zl)
+    xp = torch.empty(eng.rows, 3072, dtype=torch.bfloat16, device=dev)
+    s0, s1, g = 0.8, 0.7, 5.0
+    outs = []
+    for _ in range(2):                                    # two steps in a row: both parities of the prediction buffers
+        eng.timestep.fill_(1.0 - s0)
+        c = eng.ctx()
+        c.epoch = max(c.epoch, eng.epoch)
+        rc = pkg.lib.o1_denoise_step_cfg_sp(C.byref(w.binding), C.byref(c), C.byref(link.pair),
+                                            pkg.ptr(ids_ud if branch else idsd), pkg.ptr(posd), pkg.ptr(zl), zl.shape[0],
+                                            pkg.ptr(eng.timestep), s0, s1, g, pkg.TMS_ID, pkg.ptr(xp), pkg.ptr(zn))
+        eng.epoch = c.epoch
+        assert rc == 0, pkg.last_error()
+        torch.cuda.synchronize()
+        outs.append(zn.clone())
+    err = pkg.lib.o1_device_error()
+    want = pkg.Engine(w, T, I).denoise_step_cfg(idsd, ids_ud, posd, z, s0, s1, g)
+    torch.cuda.synchronize()
+    mine_ok = all(torch.equal(o.view(torch.int16), want[eng.i0:eng.i1].view(torch.int16)) for o in outs)
+    flag = torch.tensor([int(mine_ok and err == 0)], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    pkg.lib.o1_attention_tail_ways(0)
+    dist.barrier()
+    link.close()
+    eng.close()
+    return {"layout": f"pair x sp{sp_size}", "bit_identical_to_one_gpu_step": bool(flag.item()), "ok": bool(flag.item())}
+
+
+def gguf_broadcast_check(pkg, w, layers, T, grid, idsd, posd, vin, dev, rank):
+    """The pack is read from disk by rank 0 only; the other ranks allocate the identical arena from the header and
+    receive the bytes by one NCCL broadcast (o1.c src/model/weights.c:519-669 would read the file in every process)."""
+    import tempfile
+    import time
+    I = grid * grid
+    path = os.path.join(tempfile.gettempdir(), "o1_dist_check_pack.gguf")
+    if rank == 0:
+        tensors = []
+        for layer, names in [(-1, pkg.GLOBAL_NAMES)] + [(l, pkg.SLOT_NAMES) for l in range(layers)]:
+            for name in names:
+                bits = w.tensor(layer, name).contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+                tensors.append((pkg.gguf_tensor_name(layer, name), bits))
+        pkg.write_gguf(path, tensors, {"general.architecture": "hidream_o1", "hidream.num_layers": str(layers)})
+    dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    gw = pkg.GgufWeights(path, layers, dev, group=dist.group.WORLD, src=0)
+    torch.cuda.synchronize()
+    dist.barrier()
+    secs = time.perf_counter() - t0
+    want = pkg.Engine(w, T, I).forward(idsd, posd, vin, 0.5)
+    got = pkg.Engine(gw, T, I).forward(idsd, posd, vin, 0.5)
+    torch.cuda.synchronize()
+    same = torch.tensor([int(torch.equal(got.view(torch.int16), want.view(torch.int16)))], device=dev)
+    dist.all_reduce(same, op=dist.ReduceOp.MIN)
+    nbytes = gw.nbytes()
+    read_on_this_rank = int(gw.store.host_bytes_loaded)
+    reads = torch.tensor([float(read_on_this_rank)], device=dev, dtype=torch.float64)
+    dist.all_reduce(reads)
+    gw.close()
+    dist.barrier()
+    if rank == 0:
+        os.remove(path)
+    return {"arena_bytes": nbytes, "bytes_read_from_disk_all_ranks": int(reads.item()), "load_plus_broadcast_s": round(secs, 3),
+            "forward_identical_on_every_rank": bool(same.item()),
+            "ok": bool(same.item()) and int(reads.item()) == nbytes}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--text", type=int, default=64)
     ap.add_argument("--grid", type=int, default=32)          # image tokens = grid * grid
     ap.add_argument("--layers", type=int, default=2)
     ap.add_argument("--time", action="store_true")
+    ap.add_argument("--cfg", action="store_true")
+    ap.add_argument("--gguf", action="store_true")
     args = ap.parse_args()
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
@@ -77,10 +179,15 @@ def main():
     direct = run(direct_eng)
     direct2 = run(direct_eng)
     ms_direct = timed(direct_eng) if args.time else None
+    direct_eng.c_driver = True                     # the same forward as one o1_sp_forward call per rank
+    direct_c = run(direct_eng)
+    ms_direct_c = timed(direct_eng) if args.time else None
+    direct_eng.c_driver = False
     torch.cuda.synchronize()
     err = pkg.lib.o1_device_error()
     same = bool(torch.equal(direct.view(torch.int16), staged.view(torch.int16)) and
-                torch.equal(direct2.view(torch.int16), staged.view(torch.int16)))
+                torch.equal(direct2.view(torch.int16), staged.view(torch.int16)) and
+                torch.equal(direct_c.view(torch.int16), staged.view(torch.int16)))
     ok = torch.tensor([int(same and err == 0)], device=dev)
     dist.all_reduce(ok, op=dist.ReduceOp.MIN)
     # Against the unsharded forward.  Attention cuts the items of a partly filled last wave along the keys
@@ -99,12 +206,18 @@ def main():
     pkg.lib.o1_attention_tail_ways(0)
     dist.barrier()
     direct_eng.close()
+    extra = {}
+    if args.cfg and world % 2 == 0:
+        extra["cfg_step"] = cfg_step_check(pkg, sp, w, T, args.grid, idsd, posd, vin, dev, rank, world)
+    if args.gguf:
+        extra["gguf_broadcast"] = gguf_broadcast_check(pkg, w, args.layers, T, args.grid, idsd, posd, vin, dev, rank)
     if rank == 0:
-        good = bool(ok.item()) and rel_unsplit == 0.0 and rel < 1e-2
+        good = bool(ok.item()) and rel_unsplit == 0.0 and rel < 1e-2 and all(v.get("ok", True) for v in extra.values())
         print(json.dumps({"world": world, "S": S, "layers": args.layers, "direct_equals_staged": bool(ok.item()),
+                          "c_driver_equals_staged": bool(ok.item()),
                           "rel_l2_vs_unsharded": rel, "rel_l2_vs_unsharded_without_key_split": rel_unsplit,
                           "device_error": err, "ms_forward_staged": ms_staged,
-                          "ms_forward_direct": ms_direct, "ok": good}))
+                          "ms_forward_direct": ms_direct, "ms_forward_direct_one_call": ms_direct_c, "ok": good, **extra}))
         dist.destroy_process_group()
         sys.exit(0 if good else 1)
     dist.destroy_process_group()

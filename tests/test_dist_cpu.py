@@ -178,6 +178,33 @@ def test_layout_table():
     assert p == 1 and lay == {0: (0, 0, 0), 1: (0, 1, 0)}
     lay, p = sp.layout(1)
     assert p == 1 and lay == {0: (0, None, 0)}
+    lay, p = sp.layout(4)
+    assert p == 2 and lay[1] == (0, 0, 1) and lay[2] == (0, 1, 0)
+    lay, p = sp.layout(16)
+    assert p == 8 and lay[15] == (0, 1, 7)
+    # the library's environment knobs (a C host reads the same function: o1_parallel_layout)
+    import ctypes as C
+    import os
+    lib = sp.lib
+
+    def c_layout(world, rank):
+        a, b, c, d = C.c_int(), C.c_int(), C.c_int(), C.c_int()
+        n = lib.o1_parallel_layout(world, rank, C.byref(a), C.byref(b), C.byref(c), C.byref(d))
+        return n, a.value, b.value, c.value, d.value
+    try:
+        os.environ["O1_SP_DEGREE"] = "2"
+        assert c_layout(8, 5) == (2, 1, 0, 1, 2)            # two images in flight: pair x SP2 each
+        os.environ["O1_CFG_SPLIT"] = "0"
+        assert c_layout(8, 5) == (4, 2, -1, 1, 2)           # both branches on every GPU, SP2, four images
+        os.environ["O1_SP_DEGREE"] = "3"
+        assert c_layout(8, 0)[0] == -1                      # does not divide the KV heads
+        del os.environ["O1_SP_DEGREE"]
+        os.environ["O1_GPUS"] = "2"
+        assert c_layout(8, 1) == (1, 0, -1, 1, 2) and c_layout(8, 2)[0] == -1
+    finally:
+        for k in ("O1_SP_DEGREE", "O1_CFG_SPLIT", "O1_GPUS"):
+            os.environ.pop(k, None)
+    assert c_layout(1, 0) == (1, 0, -1, 0, 1)
     assert sp.shard_rows(16640, 256, 8, 0) == ((0, 2080), (0, 256), (0, 1824))
     assert sp.shard_rows(16640, 256, 8, 7) == ((14560, 16640), (256, 256), (14304, 16384))
     with pytest.raises(ValueError):

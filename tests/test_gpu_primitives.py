@@ -404,3 +404,28 @@ def test_projection_with_norm_and_rope_in_the_epilogue(pkg, dev, M, N, K, ldy, b
     # shapes the tensor-core tiles do not cover refuse the fused epilogue instead of falling back silently
     assert pkg.lib.o1_gemm(pkg.ptr(x), K, pkg.ptr(w), None, pkg.ptr(y_fused), ldy, 4, N, K, 6, pkg.ptr(nw), pkg.ptr(tab),
                            0, 1e-6, 0) != 0
+
+
+@pytest.mark.parametrize("M,qc,kc,K", [(300, 512, 128, 256), (1280, 4096, 1024, 4096), (4115, 1024, 256, 512)])
+def test_qkv_projections_as_one_launch(pkg, dev, M, qc, kc, K):
+    """o1_gemm_qkv (one launch over the three weight tensors, norm + rope on the q and k tiles) == three separate
+    projections with the same epilogues, bit for bit; the row pitch may exceed the used columns."""
+    ld = qc + 2 * kc + 128
+    x = dv(seeded_bf16((M, K), 81), dev)
+    wq, wk, wv = (dv(seeded_bf16((n, K), 82 + i, 0.0, 0.05), dev) for i, n in enumerate((qc, kc, kc)))
+    nq, nk = dv(seeded_bf16(128, 86, 1.0, 0.1), dev), dv(seeded_bf16(128, 87, 1.0, 0.1), dev)
+    pos, _ = pkg.seq_t2i(20, 10, (M - 20 + 9) // 10)
+    tab = torch.empty(pos.shape[1], 128, device=dev)
+    pkg.lib.o1_mrope_table(pkg.ptr(pos.to(dev)), pos.shape[1], 5e6, pkg.ptr(tab))
+    fill = seeded_bf16((M, ld), 88)
+    one, three = dv(fill, dev), dv(fill, dev)
+    rc = pkg.lib.o1_gemm_qkv(pkg.ptr(x), K, pkg.ptr(wq), pkg.ptr(wk), pkg.ptr(wv), pkg.ptr(one), ld, M, qc, kc, K,
+                             pkg.ptr(nq), pkg.ptr(nk), pkg.ptr(tab), 1e-6)
+    assert rc == 0, pkg.last_error()
+    P = lambda t, off: C.c_void_p(t.data_ptr() + off * 2)
+    assert pkg.lib.o1_gemm(pkg.ptr(x), K, pkg.ptr(wq), None, P(three, 0), ld, M, qc, K, 6, pkg.ptr(nq), pkg.ptr(tab), 0, 1e-6, 0) == 0
+    assert pkg.lib.o1_gemm(pkg.ptr(x), K, pkg.ptr(wk), None, P(three, qc), ld, M, kc, K, 6, pkg.ptr(nk), pkg.ptr(tab), 0, 1e-6, 0) == 0
+    assert pkg.lib.o1_gemm(pkg.ptr(x), K, pkg.ptr(wv), None, P(three, qc + kc), ld, M, kc, K, 0, None, None, 0, 0.0, 0) == 0
+    done(pkg, "qkv")
+    assert torch.equal(one.view(torch.int16), three.view(torch.int16))
+    assert (torch_to_u16(one)[:, qc + 2 * kc:] == fill[:, qc + 2 * kc:]).all()

@@ -89,12 +89,14 @@ def test_sp_direct_form_on_real_gpus(pkg):
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", "29531",
-           os.path.join(root, "tests", "dist_sp_direct_check.py"), "--text", "64", "--grid", "32", "--layers", "2"]
-    res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=root)
+           os.path.join(root, "tests", "dist_sp_direct_check.py"), "--text", "64", "--grid", "32", "--layers", "2",
+           "--cfg", "--gguf"]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=900, cwd=root)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
     line = [l for l in res.stdout.splitlines() if l.startswith("{")][-1]
     rep = json.loads(line)
-    assert rep["ok"] and rep["direct_equals_staged"] and rep["device_error"] == 0
+    assert rep["ok"] and rep["direct_equals_staged"] and rep["c_driver_equals_staged"] and rep["device_error"] == 0
+    assert rep["cfg_step"]["bit_identical_to_one_gpu_step"] and rep["gguf_broadcast"]["forward_identical_on_every_rank"]
 
 
 @pytest.mark.parametrize("P,direct", [(2, False), (4, True)])
