@@ -100,10 +100,81 @@ layernorm_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ w,
     }
 }
 
+// The same arithmetic with the row held in registers (rows of at most NV * 256 elements: the tower's 1152 and
+// the mergers' 4608): every element is read from memory once, all NV loads of a lane are in flight together, and
+// the sums run over the lane's elements in the same order as in layernorm_kernel, so the two agree bit for bit.
+template <int NV>
+__global__ void __launch_bounds__(LN_WARPS * 32)
+layernorm_reg_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ w, const uint16_t* __restrict__ b,
+                     uint16_t* __restrict__ y, int rows, int cols, float eps) {
+    const int row = blockIdx.x * LN_WARPS + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const uint16_t* xr = x + (size_t)row * cols;
+    uint16_t* yr = y + (size_t)row * cols;
+    uint4 v[NV];
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int i = lane * 8 + k * 256;
+        v[k] = i < cols ? *reinterpret_cast<const uint4*>(xr + i) : make_uint4(0, 0, 0, 0);
+    }
+    float s = 0.f, ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        if (lane * 8 + k * 256 < cols) {
+            const float f[8] = {bf16lo(v[k].x), bf16hi(v[k].x), bf16lo(v[k].y), bf16hi(v[k].y),
+                                bf16lo(v[k].z), bf16hi(v[k].z), bf16lo(v[k].w), bf16hi(v[k].w)};
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { s += f[j]; ss += f[j] * f[j]; }
+        }
+    }
+    s = warp_sum(s);
+    ss = warp_sum(ss);
+    const float inv = 1.0f / (float)cols;
+    const float mean = s * inv;
+    const float var = ss * inv - mean * mean;
+    const float inv_std = rsqrtf(var + eps);
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int i = lane * 8 + k * 256;
+        if (i < cols) {
+            const uint4 wv = *reinterpret_cast<const uint4*>(w + i);
+            uint4 bv = make_uint4(0, 0, 0, 0);
+            if (b) bv = *reinterpret_cast<const uint4*>(b + i);
+            const float f[8] = {bf16lo(v[k].x), bf16hi(v[k].x), bf16lo(v[k].y), bf16hi(v[k].y),
+                                bf16lo(v[k].z), bf16hi(v[k].z), bf16lo(v[k].w), bf16hi(v[k].w)};
+            const float g[8] = {bf16lo(wv.x), bf16hi(wv.x), bf16lo(wv.y), bf16hi(wv.y),
+                                bf16lo(wv.z), bf16hi(wv.z), bf16lo(wv.w), bf16hi(wv.w)};
+            const float c[8] = {bf16lo(bv.x), bf16hi(bv.x), bf16lo(bv.y), bf16hi(bv.y),
+                                bf16lo(bv.z), bf16hi(bv.z), bf16lo(bv.w), bf16hi(bv.w)};
+            float o[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] = (f[j] - mean) * inv_std * g[j] + c[j];
+            uint4 ov;
+            ov.x = pack_bf16x2(o[0], o[1]); ov.y = pack_bf16x2(o[2], o[3]);
+            ov.z = pack_bf16x2(o[4], o[5]); ov.w = pack_bf16x2(o[6], o[7]);
+            *reinterpret_cast<uint4*>(yr + i) = ov;
+        }
+    }
+}
+
 bool vision_layernorm(const void* x, const void* w, const void* b, void* y, int rows, int cols, float eps,
                       cudaStream_t st) {
     if (!x || !w || !y || rows <= 0 || cols <= 0) { set_error("vision_layernorm: bad args"); return false; }
     const int vec = (cols % 8) == 0 && ((((uintptr_t)x) | ((uintptr_t)w) | ((uintptr_t)b) | ((uintptr_t)y)) & 15) == 0;
+    const int grid = (rows + LN_WARPS - 1) / LN_WARPS;
+    if (vec && cols <= 5 * 256) {
+        layernorm_reg_kernel<5><<<grid, LN_WARPS * 32, 0, st>>>((const uint16_t*)x, (const uint16_t*)w, (const uint16_t*)b,
+                                                               (uint16_t*)y, rows, cols, eps);
+        O1_VLAUNCH_CHECK("vision_layernorm");
+        return true;
+    }
+    if (vec && cols <= 18 * 256) {
+        layernorm_reg_kernel<18><<<grid, LN_WARPS * 32, 0, st>>>((const uint16_t*)x, (const uint16_t*)w, (const uint16_t*)b,
+                                                                (uint16_t*)y, rows, cols, eps);
+        O1_VLAUNCH_CHECK("vision_layernorm");
+        return true;
+    }
     layernorm_kernel<<<(rows + LN_WARPS - 1) / LN_WARPS, LN_WARPS * 32, 0, st>>>(
         (const uint16_t*)x, (const uint16_t*)w, (const uint16_t*)b, (uint16_t*)y, rows, cols, eps, vec);
     O1_VLAUNCH_CHECK("vision_layernorm");

@@ -75,6 +75,34 @@ def test_sp_direct_form_is_bit_identical_to_staged_form(pkg, dev, P):
     assert torch.equal(again.view(torch.int16), staged.view(torch.int16))
 
 
+def test_one_call_forward_on_a_single_rank(pkg, dev):
+    """o1_sp_forward (the whole sharded forward of a rank as ONE library call: the loop a C host would otherwise
+    write around the stage functions) with a single rank must equal hd_forward bit for bit; the multi-rank form of
+    the same call is checked on real GPUs by tests/dist_sp_direct_check.py."""
+    from o1c_b200 import sp
+    T, gh, gw, L = 24, 8, 13, 3
+    I = gh * gw
+    w = pkg.Weights(n_layers=L, seed=1234, weight_set="B", device=dev)
+    pos, _ = pkg.seq_t2i(T, gh, gw)
+    rng = np.random.default_rng(1)
+    ids = rng.integers(0, 151000, size=T).astype(np.int64)
+    ids[-1] = pkg.TMS_ID
+    idsd, posd = torch.from_numpy(ids).to(dev), pos.to(dev)
+    vin = u16_to_torch(seeded_bf16((I, 3072), 43), dev)
+    ref = pkg.Engine(w, T, I).forward(idsd, posd, vin, 0.5)
+    e = sp.EngineSP(w, T, I, 1, 0, direct=True)
+    try:
+        e.connect([e.region])
+        out = e.forward_c(idsd, posd, vin, 0.5)
+        again = e.forward_c(idsd, posd, vin, 0.25)
+        again = e.forward_c(idsd, posd, vin, 0.5)
+        torch.cuda.synchronize()
+    finally:
+        e.close()
+    assert torch.equal(out.view(torch.int16), ref.view(torch.int16))
+    assert torch.equal(again.view(torch.int16), ref.view(torch.int16))
+
+
 def test_sp_direct_form_on_real_gpus(pkg):
     """The same comparison with one process per GPU (CUDA IPC mappings, peer stores over NVLink, the flag
     barrier): needs at least two GPUs."""
