@@ -883,7 +883,7 @@ def run_elementwise(args):
          lambda i: lib.hd_swiglu(P(g[i]), P(u[i]), P(sw[i]), S * 3072)),
         ("cfg_flow_step_kernel 50.3 M elements", 4 * n_lat * 2,
          lambda i: lib.o1_sched_cfg_flow_step(P(z[i]), P(xc[i]), P(xu[i]), 0.7, 0.65, 5.0, P(zn[i]), n_lat)),
-        ("layernorm_kernel [16640,1152] (vision)", 2 * S * 1152 * 2,
+        ("layernorm_reg_kernel<5> [16640,1152] (vision)", 2 * S * 1152 * 2,
          lambda i: lib.hd_vision_layernorm(P(x[i]), P(w), P(lb), P(y[i]), S, 1152, 1e-6)),
     ]
     reps = args.steps if args.short else max(args.steps, 12)
