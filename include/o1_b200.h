@@ -490,6 +490,12 @@ int o1_flash_attention_ws(const void *q, int ldq, const void *k, int ldk, const 
                           size_t scratch_bytes);
 /* Policy of that split: 0 = automatic (default), 1 = never, n > 1 = n parts whenever scratch and key count allow. */
 void o1_attention_tail_ways(int ways);
+/* GEMM tile form for the large-M families (plain, bias, residual, SwiGLU, grouped q|k|v) when the problem has at least
+ * two rounds of 256 x 256 tiles: 1 (default; environment O1_GEMM_PAIR=0 turns it off) = a cluster of two CTAs per
+ * tile with cta_group::2 MMAs, each CTA holding 128 rows of A and of the accumulator and half of the B tile;
+ * 0 = one CTA per 128 x 256 tile.  Both forms add a row's K products in the same order: same bits.  No reference
+ * counterpart (cuBLASLt picks its own kernels there, src/cuda/gemm.cu:413-461). */
+void o1_gemm_pair_mode(int mode);
 /* cos|sin table [S,128] fp32 for section [24,20,20], theta 5e6 (built once per forward). */
 int o1_mrope_table(const float *pos_dev, int seq, float theta, float *cs_dev);
 /* Per-head RMSNorm + rotary, in place on [S, ld] holding `heads` heads. */

@@ -14,6 +14,7 @@
 //   SWIGLU : B tile = 128 gate rows + 128 up rows of the same columns;
 //            bf16(bf16(silu(bf16 g)) * bf16 u) (act.cu:22-34)
 //   LORA   : W = bf16(f32(W) + scale*acc)      (lora_merge.cu:26-33)
+#include <cstdlib>
 #include "common.cuh"
 #include "ptx.cuh"
 #include "kernels.h"
@@ -62,24 +63,27 @@ struct GemmArgs {
     int* err;
 };
 
-template <int BN>
+// PAIR: two CTAs (a cluster) work on one 256 x BN tile with cta_group::2 MMAs; each holds its own 128 rows of A and
+// of the accumulator and HALF of the B tile, so a stage is a third smaller and a B element is fetched into shared
+// memory once per 256 output rows instead of once per 128.
+template <int BN, bool PAIR = false>
 struct GemmCfg {
     static constexpr int A_BYTES = BM * BK * 2;
-    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int B_BYTES = (PAIR ? BN / 2 : BN) * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int STAGES = (BN == 256) ? 4 : 6;
+    static constexpr int STAGES = PAIR ? 6 : ((BN == 256) ? 4 : 6);
     static constexpr int STORE_STAGE_BYTES = 4 * 2 * 32 * 128;   // per epilogue warp two slices of 32 rows x 128 B (peer stores)
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/ + STORE_STAGE_BYTES;
     static constexpr int TMEM_COLS = 2 * BN;
 };
 
-__device__ __forceinline__ void tile_coords(int tile, const GemmArgs& g, int& mb, int& nb) {
-    const int per_group = g.group_m * g.num_n;
+__device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int group_m, int& mb, int& nb) {
+    const int per_group = group_m * num_n;
     const int grp = tile / per_group;
     const int r = tile - grp * per_group;
-    const int m_first = grp * g.group_m;
-    int gm = g.num_m - m_first;
-    if (gm > g.group_m) gm = g.group_m;
+    const int m_first = grp * group_m;
+    int gm = num_m - m_first;
+    if (gm > group_m) gm = group_m;
     mb = m_first + r % gm;
     nb = r / gm;
 }
@@ -115,11 +119,12 @@ __device__ __forceinline__ void load32_bf16(const uint16_t* src, float (&v)[32])
     }
 }
 
-template <int EPI, int BN>
+template <int EPI, int BN, bool PAIR>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmB2, const __grid_constant__ CUtensorMap tmB3, const GemmArgs g) {
-    using Cfg = GemmCfg<BN>;
+    using Cfg = GemmCfg<BN, PAIR>;
+    static_assert(!PAIR || BN == 256, "the pair form splits a 256-wide B tile");
     constexpr int STAGES = Cfg::STAGES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -138,7 +143,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     __shared__ int s_abort;
     if (threadIdx.x == 0) s_abort = *reinterpret_cast<volatile int*>(g.err);
     __syncthreads();
-    if (s_abort != 0) return;
+    if (!PAIR && s_abort != 0) return;      // (a pair decides together, after its first cluster barrier)
+    const uint32_t rank = PAIR ? cluster_rank() : 0u;    // 0: the CTA that issues the pair's MMAs
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -147,23 +153,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         for (int s = 0; s < 2; ++s) {
             mbar_init(&tfull[s], 1);
-            mbar_init(&tempty[s], 4);
+            mbar_init(&tempty[s], PAIR ? 8 : 4);    // the epilogue warps of both CTAs arrive on the first CTA's
         }
         fence_mbar_init();
     }
     if (warp == 1) {
-        tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
-        tmem_relinquish();
+        if (PAIR) { tmem_alloc_pair(tmem_slot, Cfg::TMEM_COLS); tmem_relinquish_pair(); }
+        else { tmem_alloc(tmem_slot, Cfg::TMEM_COLS); tmem_relinquish(); }
     }
     tc_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync_all();           // both CTAs' barriers exist before either signals the other's
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    bool live = true;
+    if (PAIR) live = (s_abort | ld_cluster_s32(map_to_rank(smem_u32(&s_abort), rank ^ 1u))) == 0;
 
-    const int num_tiles = g.num_m * g.num_n;
+    // the pair form walks tiles of 256 rows: row tile 2 * mb2 + rank of each belongs to this CTA
+    const int sched_m = PAIR ? (g.num_m + 1) / 2 : g.num_m;
+    const int sched_group = PAIR ? (g.group_m + 1) / 2 : g.group_m;
+    const int num_tiles = sched_m * g.num_n;
+    const int tile0 = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+    const int tile_step = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
     const int kblocks = (g.K + BK - 1) / BK;   // a ragged last K block is zero-filled by TMA in both operands
 
-    if (warp == 0) {
+    if (!live) {
+        // nothing to do: straight to the common teardown
+    } else if (warp == 0) {
         // ------------------------------------------------------ TMA producer
         if (lane == 0) {
             tma_prefetch_desc(&tmA);
@@ -173,19 +189,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            for (int tile = tile0; tile < num_tiles && ok; tile += tile_step) {
                 int mb, nb;
-                tile_coords(tile, g, mb, nb);
+                tile_coords(tile, sched_m, g.num_n, sched_group, mb, nb);
+                if (PAIR) mb = mb * 2 + (int)rank;
                 for (int kb = 0; kb < kblocks; ++kb) {
                     if (!mbar_wait(&empty[stage], phase ^ 1)) { ok = false; atomicExch(g.err, 1); break; }
                     uint8_t* a_s = smem + stage * Cfg::STAGE_BYTES;
                     uint8_t* b_s = a_s + Cfg::A_BYTES;
-                    mbar_expect_tx(&full[stage], Cfg::STAGE_BYTES);
+                    if (!PAIR) mbar_expect_tx(&full[stage], Cfg::STAGE_BYTES);
+                    else if (rank == 0) mbar_expect_tx(&full[stage], 2 * Cfg::STAGE_BYTES);   // both CTAs' halves
                     int a_c0 = kb * BK, a_c1 = mb * BM;
                     if (g.a_kblk > 0) {
                         const int blk = a_c0 / g.a_kblk;
                         a_c0 -= blk * g.a_kblk;
                         a_c1 += blk * g.a_rows;
+                    }
+                    if (PAIR) {
+                        // this CTA's 128 rows of A and its 128 of the tile's 256 B rows (second half for the second CTA)
+                        tma_load_2d_pair(a_s, &tmA, &full[stage], a_c0, a_c1);
+                        if (EPI == EPI_SWIGLU) {
+                            tma_load_2d_pair(b_s, rank == 0 ? &tmB : &tmB2, &full[stage], kb * BK, nb * 128);
+                        } else if (EPI == EPI_QKV) {
+                            const int col0 = nb * BN;
+                            const int seg = col0 >= g.seg_n[0] + g.seg_n[1] ? 2 : (col0 >= g.seg_n[0] ? 1 : 0);
+                            const int lrow = col0 - (seg == 2 ? g.seg_n[0] + g.seg_n[1] : (seg == 1 ? g.seg_n[0] : 0));
+                            const CUtensorMap* mB = seg == 0 ? &tmB : (seg == 1 ? &tmB2 : &tmB3);
+                            tma_load_2d_pair(b_s, mB, &full[stage], kb * BK, lrow + (int)rank * 128);
+                        } else {
+                            tma_load_2d_pair(b_s, &tmB, &full[stage], kb * BK, nb * BN + (int)rank * 128);
+                        }
+                        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                        continue;
                     }
                     tma_load_2d(a_s, &tmA, &full[stage], a_c0, a_c1);
                     if (EPI == EPI_SWIGLU) {
@@ -213,14 +248,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
     } else if (warp == 1) {
         // ------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, 0, 0);
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = umma_idesc_bf16(PAIR ? 2 * BM : BM, BN, 0, 0);
             int stage = 0;
             uint32_t phase = 0;
             int as = 0;
             uint32_t aphase = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            for (int tile = tile0; tile < num_tiles && ok; tile += tile_step) {
                 if (!mbar_wait(&tempty[as], aphase ^ 1)) { atomicExch(g.err, 2); break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + as * BN;
@@ -231,12 +266,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     const uint64_t ad = umma_desc_sw128(a_addr, 16, 1024);
                     const uint64_t bd = umma_desc_sw128(a_addr + Cfg::A_BYTES, 16, 1024);
 #pragma unroll
-                    for (int k = 0; k < BK / 16; ++k)   // 32 bytes per K step = 2 units of the address field
-                        umma_ss(d_tmem, ad + 2 * k, bd + 2 * k, idesc, (kb | k) != 0);
-                    umma_commit(&empty[stage]);
+                    for (int k = 0; k < BK / 16; ++k) {  // 32 bytes per K step = 2 units of the address field
+                        if (PAIR) umma_ss_pair(d_tmem, ad + 2 * k, bd + 2 * k, idesc, (kb | k) != 0);
+                        else umma_ss(d_tmem, ad + 2 * k, bd + 2 * k, idesc, (kb | k) != 0);
+                    }
+                    if (PAIR) umma_commit_pair(&empty[stage]);
+                    else umma_commit(&empty[stage]);
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
-                umma_commit(&tfull[as]);
+                if (PAIR) umma_commit_pair(&tfull[as]);
+                else umma_commit(&tfull[as]);
                 if (++as == 2) { as = 0; aphase ^= 1; }
             }
         }
@@ -245,9 +284,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int q = warp & 3;  // TMEM lane quadrant this warp may access
         int as = 0;
         uint32_t aphase = 0;
-        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+        for (int tile = tile0; tile < num_tiles; tile += tile_step) {
             int mb, nb;
-            tile_coords(tile, g, mb, nb);
+            tile_coords(tile, sched_m, g.num_n, sched_group, mb, nb);
+            if (PAIR) mb = mb * 2 + (int)rank;
             if (!mbar_wait(&tfull[as], aphase)) { atomicExch(g.err, 4); break; }
             tc_fence_after();
             const int row = mb * BM + q * 32 + lane;
@@ -534,15 +574,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&tempty[as]);
+            if (lane == 0) {
+                if (PAIR) mbar_arrive_cluster(map_to_rank(smem_u32(&tempty[as]), 0));
+                else mbar_arrive(&tempty[as]);
+            }
             if (++as == 2) { as = 0; aphase ^= 1; }
         }
     }
 
     tc_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync_all();   // neither CTA leaves (or frees tensor memory) while the other may still signal it or feed an MMA
     tc_fence_after();
-    if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    if (warp == 1) {
+        if (PAIR) tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS);
+        else tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    }
 }
 
 // ---------------------------------------------------------------- SIMT path
@@ -655,12 +702,56 @@ bool func_attr_once(std::atomic<uint64_t>& done, const void* func, int smem_byte
     return true;
 }
 
+// 0: single-CTA tiles only; 1 (default): 256-wide tiles of the large-M families run on CTA pairs
+static int g_pair_mode = -1;
+void gemm_pair_mode(int mode) { g_pair_mode = mode; }
+static bool pair_wanted() {
+    if (g_pair_mode < 0) {
+        const char* e = getenv("O1_GEMM_PAIR");
+        g_pair_mode = (e && e[0] == '0') ? 0 : 1;
+    }
+    return g_pair_mode != 0;
+}
+
+template <int EPI>
+static bool launch_tc_pair(const CUtensorMap* tA, const CUtensorMap* tB, const CUtensorMap* tB2, GemmArgs& g,
+                           cudaStream_t st, const CUtensorMap* tB3) {
+    using Cfg = GemmCfg<256, true>;
+    static std::atomic<uint64_t> attr_done{0};
+    auto kern = gemm_tc_kernel<EPI, 256, true>;
+    if (!func_attr_once(attr_done, (const void*)kern, Cfg::SMEM_BYTES, "gemm (pair)")) return false;
+    const int tiles = ((g.num_m + 1) / 2) * g.num_n;
+    int pairs = sm_count() / 2;
+    if (pairs > tiles) pairs = tiles;
+    prof_before(EPI == EPI_QKV ? (int)EPI_STORE : EPI, 2.0 * g.M * (double)g.N * g.K * (EPI == EPI_SWIGLU ? 2.0 : 1.0), st);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs);
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+    cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, *tA, *tB, *tB2, tB3 ? *tB3 : *tB2, g);
+    prof_after(st);
+    if (e == cudaSuccess) e = cudaGetLastError();
+    if (e != cudaSuccess) { set_error("gemm (pair): launch: %s", cudaGetErrorString(e)); return false; }
+    return true;
+}
+
 template <int EPI, int BN>
 static bool launch_tc(const CUtensorMap* tA, const CUtensorMap* tB, const CUtensorMap* tB2,
                       GemmArgs& g, cudaStream_t st, const CUtensorMap* tB3 = nullptr) {
+    // CTA pairs for the families that carry the large-M work, when there are at least two rounds of pair tiles.
+    // Measured at 16640 rows, stand-alone: o_proj 1306 -> 1384, down 1348 -> 1423, q|k|v 1315 -> 1391, head 1203 -> 1235
+    // TFLOP/s; gate|up + SwiGLU 1438 -> 1358, so that family keeps one CTA per tile.
+    if constexpr (BN == 256 && (EPI == EPI_STORE || EPI == EPI_BIAS || EPI == EPI_RESID || EPI == EPI_QKV)) {
+        if (pair_wanted() && ((g.num_m + 1) / 2) * g.num_n >= sm_count()) return launch_tc_pair<EPI>(tA, tB, tB2, g, st, tB3);
+    }
     using Cfg = GemmCfg<BN>;
     static std::atomic<uint64_t> attr_done{0};
-    auto kern = gemm_tc_kernel<EPI, BN>;
+    auto kern = gemm_tc_kernel<EPI, BN, false>;
     if (!func_attr_once(attr_done, (const void*)kern, Cfg::SMEM_BYTES, "gemm")) return false;
     const int tiles = g.num_m * g.num_n;
     int grid = sm_count();

@@ -429,3 +429,33 @@ def test_qkv_projections_as_one_launch(pkg, dev, M, qc, kc, K):
     done(pkg, "qkv")
     assert torch.equal(one.view(torch.int16), three.view(torch.int16))
     assert (torch_to_u16(one)[:, qc + 2 * kc:] == fill[:, qc + 2 * kc:]).all()
+
+
+@pytest.mark.parametrize("M,N,K,epi", [(4352, 4096, 512, 0), (4115, 4096, 256, 2), (4200, 3072, 320, 1), (8320, 4096, 192, 2)])
+def test_gemm_on_cta_pairs_equals_single_cta_tiles(pkg, dev, M, N, K, epi):
+    """The cta_group::2 form (two CTAs per 256 x 256 tile, each with half of the B tile) adds a row's K products in the
+    same order as the one-CTA form: same bits, for an even and an odd number of row tiles, a partly filled last row
+    tile and a ragged last K block, with the epilogues that take the pair form (plain, +bias, +residual)."""
+    x = dv(seeded_bf16((M, K), 91), dev)
+    w = dv(seeded_bf16((N, K), 92, 0.0, 0.05), dev)
+    bias = dv(seeded_bf16(N, 93, 0.0, 0.5), dev) if epi == 1 else None
+    resid = dv(seeded_bf16((M, N), 94), dev) if epi == 2 else None
+    outs = []
+    try:
+        for mode in (0, 1):
+            pkg.lib.o1_gemm_pair_mode(mode)
+            y = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
+            rc = pkg.lib.o1_gemm(pkg.ptr(x), K, pkg.ptr(w), None, pkg.ptr(y), N, M, N, K, epi,
+                                 pkg.ptr(bias) if bias is not None else None,
+                                 pkg.ptr(resid) if resid is not None else None, N, 0.0, 0)
+            assert rc == 0, pkg.last_error()
+            done(pkg, "gemm pair mode %d" % mode)
+            outs.append(y)
+    finally:
+        pkg.lib.o1_gemm_pair_mode(1)
+    assert torch.equal(outs[0].view(torch.int16), outs[1].view(torch.int16))
+    ref = x.float() @ w.float().t()
+    if epi == 1: ref = (ref.bfloat16().float() + bias.float())
+    if epi == 2: ref = (ref.bfloat16().float() + resid.float())
+    err = (outs[1].float() - ref).abs().max().item() / max(ref.abs().max().item(), 1e-6)
+    assert err < 1e-2, err     # the pair form really computed the product (fp32 reference, bf16 rounding of the result)
