@@ -39,8 +39,8 @@ WORKLOADS = {
 C3_REFS = [(4096, 64, 64, 8, 8)] * 4     # (tokens, grid_h, grid_w, cond_h, cond_w) per reference
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture summarised in
 # profiles/traffic_S16640.md (same kernels, same shapes, 2 decoder blocks instead of 36)
-NCU_TRAFFIC_BYTES = {("c2", "flash_attn"): 306200000, ("c2", "gemm_swiglu"): 1555000000,
-                     ("c2", "gemm_resid"): 2244000000}
+NCU_TRAFFIC_BYTES = {("c2", "flash_attn"): 306400000, ("c2", "gemm_swiglu"): 1558000000,
+                     ("c2", "gemm_resid"): 2950000000}
 STEPS_PER_IMAGE = 28
 GUIDANCE = 5.0
 

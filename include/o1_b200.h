@@ -496,6 +496,8 @@ void o1_attention_tail_ways(int ways);
  * 0 = one CTA per 128 x 256 tile.  Both forms add a row's K products in the same order: same bits.  No reference
  * counterpart (cuBLASLt picks its own kernels there, src/cuda/gemm.cu:413-461). */
 void o1_gemm_pair_mode(int mode);
+/* CTA pairs of the GEMM kernel the current device holds at once (the pair form never launches more); -1 on error. */
+int o1_gemm_pair_capacity(void);
 /* cos|sin table [S,128] fp32 for section [24,20,20], theta 5e6 (built once per forward). */
 int o1_mrope_table(const float *pos_dev, int seq, float theta, float *cs_dev);
 /* Per-head RMSNorm + rotary, in place on [S, ld] holding `heads` heads. */

@@ -252,6 +252,7 @@ _sig("o1_flash_attention", c_int, _P, c_int, _P, c_int, _P, c_int, _P, c_int, c_
      c_int, c_float)
 _sig("o1_attention_tail_ways", None, c_int)
 _sig("o1_gemm_pair_mode", None, c_int)
+_sig("o1_gemm_pair_capacity", c_int)
 _sig("o1_flash_attention_ws", c_int, _P, c_int, _P, c_int, _P, c_int, _P, c_int, c_int, c_int, c_int,
      c_int, c_float, _P, c_size_t)
 _sig("o1_mrope_table", c_int, _P, c_int, c_float, _P)

@@ -899,6 +899,7 @@ int o1_flash_attention_ws(const void* q, int ldq, const void* k, int ldk, const 
 }
 void o1_attention_tail_ways(int ways) { attention_tail_ways(ways); }
 void o1_gemm_pair_mode(int mode) { gemm_pair_mode(mode); }
+int o1_gemm_pair_capacity(void) { return gemm_pair_capacity(); }
 int o1_mrope_table(const float* pos, int seq, float theta, float* cs) {
     if (!mrope_table64(pos, seq, theta, cs, g_stream)) return 1;
     count();

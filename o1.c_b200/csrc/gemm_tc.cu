@@ -721,11 +721,7 @@ static bool launch_tc_pair(const CUtensorMap* tA, const CUtensorMap* tB, const C
     auto kern = gemm_tc_kernel<EPI, 256, true>;
     if (!func_attr_once(attr_done, (const void*)kern, Cfg::SMEM_BYTES, "gemm (pair)")) return false;
     const int tiles = ((g.num_m + 1) / 2) * g.num_n;
-    int pairs = sm_count() / 2;
-    if (pairs > tiles) pairs = tiles;
-    prof_before(EPI == EPI_QKV ? (int)EPI_STORE : EPI, 2.0 * g.M * (double)g.N * g.K * (EPI == EPI_SWIGLU ? 2.0 : 1.0), st);
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(2 * pairs);
     cfg.blockDim = dim3(GEMM_THREADS);
     cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
     cfg.stream = st;
@@ -733,11 +729,49 @@ static bool launch_tc_pair(const CUtensorMap* tA, const CUtensorMap* tB, const C
     at[0].id = cudaLaunchAttributeClusterDimension;
     at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
     cfg.attrs = at; cfg.numAttrs = 1;
+    // A persistent grid must be co-resident: as many pairs as the device can hold at once (a GPC with an odd number
+    // of SMs leaves one without a partner), asked once per device.
+    static std::atomic<int> max_pairs[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    int pairs = max_pairs[dev & 63].load(std::memory_order_acquire);
+    if (pairs == 0) {
+        cfg.gridDim = dim3(2 * (sm_count() / 2));
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) { cudaGetLastError(); n = sm_count() / 2; }
+        if (n > sm_count() / 2) n = sm_count() / 2;
+        pairs = n;
+        max_pairs[dev & 63].store(n, std::memory_order_release);
+    }
+    if (pairs > tiles) pairs = tiles;
+    prof_before(EPI == EPI_QKV ? (int)EPI_STORE : EPI, 2.0 * g.M * (double)g.N * g.K * (EPI == EPI_SWIGLU ? 2.0 : 1.0), st);
+    cfg.gridDim = dim3(2 * pairs);
     cudaError_t e = cudaLaunchKernelEx(&cfg, kern, *tA, *tB, *tB2, tB3 ? *tB3 : *tB2, g);
     prof_after(st);
     if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) { set_error("gemm (pair): launch: %s", cudaGetErrorString(e)); return false; }
     return true;
+}
+
+// CTA pairs of the GEMM kernel the current device can hold at once (what the pair form's grid is clamped to)
+int gemm_pair_capacity() {
+    using Cfg = GemmCfg<256, true>;
+    auto kern = gemm_tc_kernel<EPI_STORE, 256, true>;
+    if (cudaFuncSetAttribute((const void*)kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess) {
+        cudaGetLastError();
+        return -1;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * (sm_count() / 2));
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) { cudaGetLastError(); return -1; }
+    return n;
 }
 
 template <int EPI, int BN>
