@@ -493,7 +493,8 @@ void o1_attention_tail_ways(int ways);
 /* GEMM tile form for the large-M families (plain, bias, residual, SwiGLU, grouped q|k|v) when the problem has at least
  * two rounds of 256 x 256 tiles: 1 (default; environment O1_GEMM_PAIR=0 turns it off) = a cluster of two CTAs per
  * tile with cta_group::2 MMAs, each CTA holding 128 rows of A and of the accumulator and half of the B tile;
- * 0 = one CTA per 128 x 256 tile.  Both forms add a row's K products in the same order: same bits.  No reference
+ * 0 = one CTA per 128 x 256 tile; 2 = pairs for the SwiGLU family as well (measured 1.6 % slower for that family in
+ * the power-capped step, so not the default).  All forms add a row's K products in the same order: same bits.  No reference
  * counterpart (cuBLASLt picks its own kernels there, src/cuda/gemm.cu:413-461). */
 void o1_gemm_pair_mode(int mode);
 /* CTA pairs of the GEMM kernel the current device holds at once (the pair form never launches more); -1 on error. */

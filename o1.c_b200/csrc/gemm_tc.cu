@@ -702,13 +702,13 @@ bool func_attr_once(std::atomic<uint64_t>& done, const void* func, int smem_byte
     return true;
 }
 
-// 0: single-CTA tiles only; 1 (default): 256-wide tiles of the large-M families run on CTA pairs
+// 0: single-CTA tiles only; 1 (default): 256-wide tiles of the large-M families run on CTA pairs; 2: SwiGLU family too
 static int g_pair_mode = -1;
 void gemm_pair_mode(int mode) { g_pair_mode = mode; }
 static bool pair_wanted() {
     if (g_pair_mode < 0) {
         const char* e = getenv("O1_GEMM_PAIR");
-        g_pair_mode = (e && e[0] == '0') ? 0 : 1;
+        g_pair_mode = (e && e[0] == '0') ? 0 : ((e && e[0] == '2') ? 2 : 1);
     }
     return g_pair_mode != 0;
 }
@@ -782,6 +782,10 @@ static bool launch_tc(const CUtensorMap* tA, const CUtensorMap* tB, const CUtens
     // TFLOP/s; gate|up + SwiGLU 1438 -> 1358, so that family keeps one CTA per tile.
     if constexpr (BN == 256 && (EPI == EPI_STORE || EPI == EPI_BIAS || EPI == EPI_RESID || EPI == EPI_QKV)) {
         if (pair_wanted() && ((g.num_m + 1) / 2) * g.num_n >= sm_count()) return launch_tc_pair<EPI>(tA, tB, tB2, g, st, tB3);
+    }
+    // mode 2: gate|up + SwiGLU too (in the power-capped step 1403 -> 1380 TFLOP/s for that family, step time unchanged)
+    if constexpr (BN == 256 && EPI == EPI_SWIGLU) {
+        if (pair_wanted() && g_pair_mode == 2 && ((g.num_m + 1) / 2) * g.num_n >= sm_count()) return launch_tc_pair<EPI>(tA, tB, tB2, g, st, tB3);
     }
     using Cfg = GemmCfg<BN>;
     static std::atomic<uint64_t> attr_done{0};
