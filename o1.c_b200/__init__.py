@@ -251,6 +251,7 @@ _sig("o1_gemm_qkv", c_int, _P, c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int
 _sig("o1_flash_attention", c_int, _P, c_int, _P, c_int, _P, c_int, _P, c_int, c_int, c_int, c_int,
      c_int, c_float)
 _sig("o1_attention_tail_ways", None, c_int)
+_sig("o1_attention_tile_mode", None, c_int)
 _sig("o1_gemm_pair_mode", None, c_int)
 _sig("o1_gemm_pair_capacity", c_int)
 _sig("o1_flash_attention_ws", c_int, _P, c_int, _P, c_int, _P, c_int, _P, c_int, c_int, c_int, c_int,

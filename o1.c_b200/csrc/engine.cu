@@ -898,6 +898,7 @@ int o1_flash_attention_ws(const void* q, int ldq, const void* k, int ldk, const 
     return 0;
 }
 void o1_attention_tail_ways(int ways) { attention_tail_ways(ways); }
+void o1_attention_tile_mode(int mode) { attention_tile_mode(mode); }
 void o1_gemm_pair_mode(int mode) { gemm_pair_mode(mode); }
 int o1_gemm_pair_capacity(void) { return gemm_pair_capacity(); }
 int o1_mrope_table(const float* pos, int seq, float theta, float* cs) {

@@ -66,6 +66,7 @@ bool flash_attention_hm(const void* q, const void* k, const void* v, void* out, 
                         int row_lo = 0, int row_hi = -1);
 // tail split policy of flash_attention*: 0 = automatic, 1 = never, n = n key-range parts when they fit
 void attention_tail_ways(int ways);
+void attention_tile_mode(int mode);   // 0: by sequence length; 1: two query tiles per CTA; 2: one query tile per CTA
 int gemm_pair_capacity();
 void gemm_pair_mode(int mode);   // 0: single-CTA GEMM tiles only; 1: CTA pairs (cta_group::2) for the large-M families
 // seq-major operands; output rows [b*out_rows, (b+1)*out_rows) go to out_tab[b] (row-major, leading

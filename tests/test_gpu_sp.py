@@ -207,10 +207,11 @@ def test_sp_barrier_gives_up_when_a_peer_never_arrives(pkg, dev):
 
 
 def test_sp_direct_form_with_key_split_attention(pkg, dev):
-    """Two ranks at S = 2560: each rank's 160 attention items leave a tail of 12 behind the first wave, which is cut
-    along the keys (two ranges each; the partial results fit the rank's idle SwiGLU buffer) and merged; in the
-    direct form the merge kernel writes through the peer table.  Direct == staged bit for bit (same split), and
-    both agree with the unsharded forward, whose attention runs unsplit."""
+    """Two ranks at S = 2560: each rank's 320 attention items (16 heads x 20 query tiles; sequences this short take
+    the one-tile kernel) leave a tail of 24 behind the second wave, which is cut along the keys (two ranges each; the
+    partial results fit the rank's idle SwiGLU buffer) and merged; the fully causal first query tile among them has a
+    single key tile and leaves one empty partial.  In the direct form the merge kernel writes through the peer table.
+    Direct == staged bit for bit (same split), and both agree with the unsharded forward, whose attention runs unsplit."""
     from o1c_b200 import sp
     P = 2
     T, gh, gw, L = 256, 48, 48, 1
