@@ -23,6 +23,7 @@
 // An accumulator is only rescaled when its running max grows by more than 2^8 (sum and
 // accumulator share the same stale max, so the final division is still exact).
 // Short sequences, flash_attn1_kernel: one query tile per CTA with triple-buffered scores (described at the kernel).
+#include <cstdlib>
 #include "common.cuh"
 #include "ptx.cuh"
 #include "kernels.h"
@@ -922,8 +923,15 @@ static int g_tail_ways = 0;   // 0: choose; 1: never split; n > 1: n parts whene
 void attention_tail_ways(int ways) { g_tail_ways = ways < 0 ? 0 : ways; }
 // Which kernel: 0 = by sequence length (one query tile per CTA up to 8192 keys, two above), 1 = always the two-tile
 // kernel, 2 = always the one-tile kernel
-static int g_tile_mode = 0;
+static int g_tile_mode = -1;    // -1: not yet read from the environment (O1_ATTN_TILE_MODE)
 void attention_tile_mode(int mode) { g_tile_mode = (mode < 0 || mode > 2) ? 0 : mode; }
+static int tile_mode() {
+    if (g_tile_mode < 0) {
+        const char* e = getenv("O1_ATTN_TILE_MODE");
+        g_tile_mode = (e && (e[0] == '1' || e[0] == '2')) ? e[0] - '0' : 0;
+    }
+    return g_tile_mode;
+}
 
 static int choose_tail_ways(int total, int nsm, int min_tiles, size_t scratch_bytes, int rows_item) {
     const int rem = total % nsm;
@@ -976,7 +984,7 @@ static bool flash_attention_impl(const void* q, int ldq, const void* k, int ldk,
     }
     if (!maps_ok) return false;
     const CUtensorMap *tq = &mq, *tk = &mk, *tv = &mv;
-    const bool one_tile = g_tile_mode == 2 || (g_tile_mode == 0 && S <= 8192);
+    const bool one_tile = tile_mode() == 2 || (tile_mode() == 0 && S <= 8192);
     const int rows_item = one_tile ? T1_ROWS : AQ2;
     static std::atomic<uint64_t> attr_done{0}, attr1_done{0};
     if (one_tile) {
