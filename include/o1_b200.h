@@ -491,7 +491,7 @@ int o1_flash_attention_ws(const void *q, int ldq, const void *k, int ldk, const 
 /* Policy of that split: 0 = automatic (default), 1 = never, n > 1 = n parts whenever scratch and key count allow. */
 void o1_attention_tail_ways(int ways);
 /* Which attention kernel: 0 = by sequence length (default: one query tile of 128 rows per CTA with triple-buffered
- * scores for S <= 8192, two query tiles that share the K/V tiles above), 1 = always the two-tile kernel, 2 = always
+ * scores for S < 8192, two query tiles that share the K/V tiles above), 1 = always the two-tile kernel, 2 = always
  * the one-tile kernel (environment O1_ATTN_TILE_MODE sets the initial value).  Same arithmetic up to fp32 summation
  * order and the reference max of the lazy rescale. */
 void o1_attention_tile_mode(int mode);

@@ -497,7 +497,7 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// One query tile per CTA, scores triple-buffered: the form used for short sequences (S <= 8192), where work items of
+// One query tile per CTA, scores triple-buffered: the form used for short sequences (S < 8192), where work items of
 // 256 rows are too few and too coarse for 148 SMs (S = 1280: 160 items) and the serial chain of the two-tile kernel
 // has nothing to hide behind.  Tensor memory: three score buffers of 128 columns + one output accumulator.  The MMA
 // thread issues S(j+3) = Q K^T right after PV(j), so the scores of the next two key tiles are always there or on their
@@ -921,7 +921,7 @@ __global__ void __launch_bounds__(AD) attn_merge_kernel(const AttnArgs a, int n_
 // with 4 or 8 tail items after 7 or 14 waves), so it is left alone.  Every part keeps at least two key tiles.
 static int g_tail_ways = 0;   // 0: choose; 1: never split; n > 1: n parts whenever they fit
 void attention_tail_ways(int ways) { g_tail_ways = ways < 0 ? 0 : ways; }
-// Which kernel: 0 = by sequence length (one query tile per CTA up to 8192 keys, two above), 1 = always the two-tile
+// Which kernel: 0 = by sequence length (one query tile per CTA below 8192 keys, two from there on), 1 = always the two-tile
 // kernel, 2 = always the one-tile kernel
 static int g_tile_mode = -1;    // -1: not yet read from the environment (O1_ATTN_TILE_MODE)
 void attention_tile_mode(int mode) { g_tile_mode = (mode < 0 || mode > 2) ? 0 : mode; }
@@ -984,7 +984,7 @@ static bool flash_attention_impl(const void* q, int ldq, const void* k, int ldk,
     }
     if (!maps_ok) return false;
     const CUtensorMap *tq = &mq, *tk = &mk, *tv = &mv;
-    const bool one_tile = tile_mode() == 2 || (tile_mode() == 0 && S <= 8192);
+    const bool one_tile = tile_mode() == 2 || (tile_mode() == 0 && S < 8192);
     const int rows_item = one_tile ? T1_ROWS : AQ2;
     static std::atomic<uint64_t> attr_done{0}, attr1_done{0};
     if (one_tile) {

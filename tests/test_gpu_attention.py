@@ -15,7 +15,7 @@ pytestmark = pytest.mark.gpu
 @pytest.fixture(params=[1, 2], ids=["two-tile", "one-tile"])
 def tile_mode(request, pkg):
     """Both attention kernels take every case of this module: 1 = two query tiles per CTA (what long sequences get),
-    2 = one query tile per CTA with triple-buffered scores (what S <= 8192 gets by default)."""
+    2 = one query tile per CTA with triple-buffered scores (what S < 8192 gets by default)."""
     pkg.lib.o1_attention_tile_mode(request.param)
     yield request.param
     pkg.lib.o1_attention_tile_mode(0)
