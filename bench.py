@@ -713,7 +713,10 @@ def run_reference(args):
             reng.close()
             val = ms_step * STEPS_PER_IMAGE / 1e3
             base.update({
-                "value": round(val, 4), "warmup": warm, "ms_per_step": round(ms_step, 3),
+                "value": round(val, 4), "warmup": warm, "warmup_requested": args.warmup,
+                "warmup_note": "at least 8 untimed steps: the reference's cuBLASLt algorithm search (src/cuda/gemm.cu:413-461) "
+                               "runs over its first calls per shape and would otherwise fall into the timed region",
+                "ms_per_step": round(ms_step, 3),
                 "config": {"workload": workload_desc(args.workload, layers), "seq_len": S, "layers": layers,
                            "steps_per_image": STEPS_PER_IMAGE,
                            "backend": "reference CUDA build on this GPU: cuBLASLt GEMM + cuDNN SDPA (two-pass)",
