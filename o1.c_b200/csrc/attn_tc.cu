@@ -8,8 +8,8 @@
 //
 // Two kernels.  Long sequences (the benchmark's 16640 rows), flash_attn_kernel:
 // one CTA = 256 query rows of one head: two query tiles of 128 rows that share every K/V tile
-// brought into shared memory (shared-memory bandwidth is what bounds this kernel; the K/V
-// fill is its largest avoidable part).  Operands stay seq-major ([S, heads*128]); head split /
+// brought into shared memory (half the K/V fill per query row of a one-tile CTA, and the two tiles'
+// softmax and MMA phases overlap each other).  Operands stay seq-major ([S, heads*128]); head split /
 // merge (attn.cu:180-218) disappear into the TMA coordinates and the output addressing.
 //   warp 0     : TMA producer (two Q tiles once, then K tiles (2 stages) and V tiles (3 stages))
 //   warp 1     : tcgen05.mma issuer: S_g = Q_g K_j^T into TMEM, O_g += P_g V_j with P_g read from
